@@ -1,0 +1,189 @@
+"""Extract the reference's own known-answer vectors for the backward path.
+
+Run once in a container that has the apache/singa sources:
+
+    python tests/golden/make_golden.py /path/to/singa > /dev/null
+
+It READS the reference's test files as text (nothing is executed or imported)
+and writes ``tests/golden/reference_vectors.json`` next to this script.  Each
+entry records the file and line range it was taken from.  The tests replay the
+vectors against the CPU oracle (no GPU) and against the CUDA path (GPU).
+"""
+import ast
+import json
+import os
+import re
+import sys
+
+NUM = r"[-+]?(?:\d+\.\d*|\.\d+|\d+)(?:[eE][-+]?\d+)?"
+
+
+def lines(root, rel, lo, hi):
+    with open(os.path.join(root, rel)) as f:
+        return "".join(f.readlines()[lo - 1:hi])
+
+
+def c_array(text, name):
+    """Values of ``const <type> name[...] = {...};`` inside text."""
+    m = re.search(r"\b%s\s*\[[^\]]*\]\s*=\s*\{([^}]*)\}" % re.escape(name), text)
+    if not m:
+        raise KeyError(name)
+    return [float(v) for v in re.findall(NUM, m.group(1).replace("f,", ",").replace("f}", "}"))]
+
+
+def expects(text, ptr):
+    """(index -> value) from EXPECT_NEAR/EXPECT_EQ/EXPECT_FLOAT_EQ lines that
+    compare a literal with ptr[i], in either argument order."""
+    out = {}
+    pat1 = re.compile(r"EXPECT_(?:NEAR|EQ|FLOAT_EQ)\(\s*(%s)f?\s*,\s*%s\[(\d+)\]" % (NUM, re.escape(ptr)))
+    pat2 = re.compile(r"EXPECT_(?:NEAR|EQ|FLOAT_EQ)\(\s*%s\[(\d+)\]\s*,\s*(%s)f?" % (re.escape(ptr), NUM))
+    for v, i in pat1.findall(text):
+        out[int(i)] = float(v)
+    for i, v in pat2.findall(text):
+        out[int(i)] = float(v)
+    return [out[i] for i in range(len(out))]
+
+
+def py_func_literals(root, rel, func):
+    """All list/number literals assigned inside a python function, by name."""
+    with open(os.path.join(root, rel)) as f:
+        tree = ast.parse(f.read())
+    found = {}
+
+    def numeric(node):
+        try:
+            return ast.literal_eval(node)
+        except Exception:
+            return None
+
+    for node in ast.walk(tree):
+        if isinstance(node, ast.FunctionDef) and node.name == func:
+            for sub in ast.walk(node):
+                if isinstance(sub, ast.Assign) and isinstance(sub.targets[0], ast.Name):
+                    name = sub.targets[0].id
+                    val = sub.value
+                    lit = numeric(val)
+                    if lit is None:
+                        # np.array(<literal>, ...).reshape(...) -> the literal
+                        cands = [n for n in ast.walk(val)
+                                 if isinstance(n, (ast.List, ast.Tuple))
+                                 and numeric(n) is not None]
+                        if cands:   # first in source order = np.array's argument
+                            cands.sort(key=lambda n: (n.lineno, n.col_offset))
+                            lit = numeric(cands[0])
+                    if lit is not None:
+                        found.setdefault(name, lit)
+            found["_lines"] = [node.lineno, node.end_lineno]
+    return found
+
+
+def main(root):
+    g = {}
+
+    # --- softmax cross entropy (logits 0.1 everywhere -> p = 0.25) ----------
+    rel = "test/singa/test_cross_entropy.cc"
+    t = lines(root, rel, 28, 112)
+    bwd = lines(root, rel, 76, 94)
+    g["cross_entropy"] = {
+        "source": rel + ":36-38,54-56,83-90",
+        "logits": c_array(t, "pdat"), "shape": [2, 4],
+        "int_target": [int(v) for v in c_array(t, "tdat")],
+        "array_target": [int(v) for v in c_array(t, "tary")],
+        "loss_is_minus_log_of": 0.25,
+        "grad": expects(bwd, "gdat"),
+    }
+
+    # --- cuDNN batch-norm forward + backward, shape (1,2,4,4) ----------------
+    rel = "test/singa/test_cudnn_batchnorm.cc"
+    f = lines(root, rel, 44, 115)
+    b = lines(root, rel, 117, 229)
+    g["batchnorm"] = {
+        "source": rel + ":44-115 (forward), :117-229 (backward)",
+        "note": "expected values were produced with cuDNN-7 semantics: "
+                "epsilon = CUDNN_BN_MIN_EPSILON = 1e-5; tolerance 1e-4",
+        "shape": [1, 2, 4, 4], "eps": 1e-5, "tol": 1e-4,
+        "x": c_array(f, "x"), "scale": c_array(f, "alpha_"), "bias": c_array(f, "beta_"),
+        "y": expects(f, "outptr"),
+        "bwd_x": c_array(b, "x"), "bwd_dy": c_array(b, "dy"),
+        "bwd_scale": c_array(b, "alpha_"),
+        "dx": expects(b, "dxptr"), "dscale": expects(b, "dbnScaleptr"),
+        "dbias": expects(b, "dbnBiasptr"),
+    }
+
+    # --- cuDNN max pooling 2x2 stride 1 on 3x3 -------------------------------
+    rel = "test/singa/test_cudnn_pooling.cc"
+    f = lines(root, rel, 55, 85)
+    b = lines(root, rel, 87, 130)
+    g["maxpool_cudnn"] = {
+        "source": rel + ":55-85 (forward), :87-130 (backward)",
+        "x_shape": [1, 1, 3, 3], "kernel": [2, 2], "stride": [1, 1], "pad": [0, 0],
+        "x": c_array(f, "x"), "y": expects(f, "outptr1"),
+        "dy": c_array(b, "dy"), "dx": expects(b, "dx"),
+    }
+
+    # --- python API goldens: BN backward (eps 1e-5), max / avg pooling -------
+    rel = "test/python/test_api.py"
+    lit = py_func_literals(root, rel, "test_batchnorm_backward_dnnl")
+    g["batchnorm_api"] = {
+        "source": rel + ":%d-%d" % tuple(lit["_lines"]),
+        "shape": [lit["N"], lit["C"], lit["H"], lit["W"]], "eps": 1e-5,
+        "x": lit["data"], "dy": lit["data"], "scale": [1] * lit["C"],
+        "dx": lit["dx_truth"], "decimal": 6,
+    }
+    lit = py_func_literals(root, rel, "test_dnnl_pooling_max")
+    g["maxpool_api"] = {
+        "source": rel + ":%d-%d" % tuple(lit["_lines"]),
+        "x_shape": [lit["N"], lit["C"], lit["H"], lit["W"]], "kernel": [2, 2],
+        "stride": [1, 1], "pad": [0, 0], "x": lit["data"], "dy": lit["dy0"],
+        "y": lit["y1"], "dx": lit["dx1"],
+    }
+    lit = py_func_literals(root, rel, "test_dnnl_pooling_avg")
+    g["avgpool_api"] = {
+        "source": rel + ":%d-%d" % tuple(lit["_lines"]),
+        "x_shape": [lit["N"], lit["C"], lit["H"], lit["W"]], "kernel": [2, 2],
+        "stride": [1, 1], "pad": [0, 0], "x": lit["data"], "dy": lit["dy0"],
+        "y": lit["y1"], "dx": lit["dx1"],
+    }
+
+    # --- ReLU forward/backward (python operation test) -----------------------
+    rel = "test/python/test_operation.py"
+    lit = py_func_literals(root, rel, "_Relu_helper")
+    g["relu"] = {
+        "source": rel + ":%d-%d" % tuple(lit["_lines"]),
+        "x": lit["X"], "shape": [3, 2], "dy": "ones",
+        "rule": "y = max(x,0); dx = (x > 0) * dy",
+    }
+
+    # --- SGD one-step values (closed forms stated in the test) ---------------
+    g["sgd"] = {
+        "source": "test/python/test_opt.py:96-107,180-213",
+        "cases": [
+            {"name": "const_lr", "w": 0.1, "g": 0.1, "lr": 0.1, "momentum": 0.0,
+             "weight_decay": 0.0, "steps": 1, "expect": "w - 0.1*g"},
+            {"name": "momentum", "w": 0.1, "g": 0.01, "lr": 0.1, "momentum": 0.9,
+             "weight_decay": 0.0, "steps": 2,
+             "expect": "step1: w-0.1*g ; step2: w1-0.1*(g+0.9*g)"},
+            {"name": "weight_decay", "w": 0.1, "g": 0.01, "lr": 0.1, "momentum": 0.0,
+             "weight_decay": 0.2, "steps": 1, "expect": "w - 0.1*(g+0.2*w)"},
+        ],
+        "shape": [2, 3],
+    }
+
+    # --- distributed tests: constant inputs, all six modes -------------------
+    g["dist"] = {
+        "source": "test/python/test_dist.py:37-121",
+        "grad": 1.0, "param": 10.0, "lr": 0.1, "expect_param": 9.9,
+        "modes": ["all_reduce", "fused_all_reduce", "all_reduce_half",
+                  "fused_all_reduce_half", "sparsification_threshold_0.05",
+                  "sparsification_topK_1.0"],
+        "shape": [10, 10],
+    }
+
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
+    with open(out, "w") as f:
+        json.dump(g, f, indent=1)
+    print("wrote", out)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
