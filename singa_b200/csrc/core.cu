@@ -1,0 +1,51 @@
+// Library-wide state: status strings, error bookkeeping, device properties.
+#include <atomic>
+
+#include "common.cuh"
+
+namespace sgb {
+namespace {
+std::atomic<int> g_last_cuda_error{0};
+constexpr int kMaxDevices = 64;
+std::atomic<int> g_sm_count[kMaxDevices];
+}  // namespace
+
+int note_cuda_error(cudaError_t e) {
+  g_last_cuda_error.store(static_cast<int>(e));
+  return SGB_ERR_CUDA;
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int v = g_sm_count[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+    v = 148;
+  g_sm_count[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+}  // namespace sgb
+
+extern "C" {
+
+const char* sgb_status_string(int status) {
+  switch (status) {
+    case SGB_OK: return "ok";
+    case SGB_ERR_NULL: return "required pointer is NULL";
+    case SGB_ERR_SIZE: return "inconsistent or out-of-range size";
+    case SGB_ERR_CUDA: return "CUDA runtime error (see sgb_last_cuda_error)";
+    case SGB_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+    case SGB_ERR_NCCL: return "NCCL error (see sgb_last_nccl_error)";
+    case SGB_ERR_UNSUPPORTED: return "unsupported op, dtype or mode";
+    case SGB_ERR_STATE: return "call not valid in this state";
+    case SGB_ERR_CAPACITY: return "does not fit the communicator's buffers";
+    default: return "unknown status";
+  }
+}
+
+int sgb_last_cuda_error(void) { return sgb::g_last_cuda_error.load(); }
+
+int sgb_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,589 @@
+// Elementwise family of the backward path: ReLU forward/backward, gradient
+// joins, scalar scaling, fills, casts, comparisons, the one-input maths
+// family and the sparsification helpers.  One functor-driven template:
+// 128-bit loads and stores, UNROLL independent vectors in flight per thread
+// and per operand, persistent grid-stride tiles (grid = a multiple of the SM
+// count once the tensor is large).  All of it is HBM-bound: the arithmetic is
+// written exactly as the reference's so that results are bit-identical.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace sgb {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kUnroll = 4;      // 16-byte vectors in flight per operand
+constexpr int kCtasPerSm = 8;   // 2048 threads per SM
+
+// ------------------------------------------------------------------ kernels
+// IN operands and one output, all of 16-byte vectors.  The functor maps IN
+// uint4 vectors (+ the element index of the vector's first lane) to a uint4.
+template <int IN, typename F>
+__global__ void __launch_bounds__(kBlock)
+ew_vec_kernel(F f, const uint4* __restrict__ a, const uint4* __restrict__ b,
+              const uint4* __restrict__ c, uint4* __restrict__ out, size_t nvec,
+              int lanes) {
+  const size_t tile = static_cast<size_t>(kBlock) * kUnroll;
+  for (size_t base = blockIdx.x * tile; base < nvec; base += gridDim.x * tile) {
+    uint4 va[kUnroll], vb[kUnroll], vc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t i = base + u * kBlock + threadIdx.x;
+      if (i < nvec) {
+        if (IN >= 1) va[u] = ld128_stream(a + i);
+        if (IN >= 2) vb[u] = ld128_stream(b + i);
+        if (IN >= 3) vc[u] = ld128_stream(c + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t i = base + u * kBlock + threadIdx.x;
+      if (i < nvec) st128(out + i, f.vec(va[u], vb[u], vc[u], i * lanes));
+    }
+  }
+}
+
+// Scalar fallback for misaligned pointers and for the < 16-byte tail.
+template <int IN, typename F, typename TA, typename TB, typename TC, typename TO>
+__global__ void __launch_bounds__(kBlock)
+ew_scalar_kernel(F f, const TA* __restrict__ a, const TB* __restrict__ b,
+                 const TC* __restrict__ c, TO* __restrict__ out, size_t first,
+                 size_t n) {
+  for (size_t i = first + blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x;
+       i < n; i += static_cast<size_t>(gridDim.x) * kBlock) {
+    TA xa = IN >= 1 ? a[i] : TA();
+    TB xb = IN >= 2 ? b[i] : TB();
+    TC xc = IN >= 3 ? c[i] : TC();
+    out[i] = f.one(xa, xb, xc, i);
+  }
+}
+
+// Host-side driver.  LA/LB/LC/LO = elements per 16-byte vector of each
+// operand; the vector path needs equal lane counts, which every functor
+// below satisfies except the casts (handled by their own functors working on
+// two vectors at once, see CastF32F16).
+template <int IN, typename F, typename TA, typename TB, typename TC, typename TO>
+int run(F f, const TA* a, const TB* b, const TC* c, TO* out, size_t n,
+        void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!out || (IN >= 1 && !a) || (IN >= 2 && !b) || (IN >= 3 && !c))
+    return SGB_ERR_NULL;
+  cudaStream_t s = as_stream(stream);
+  constexpr int lanes = 16 / sizeof(TO);
+  static_assert(IN < 1 || sizeof(TA) == sizeof(TO), "lane mismatch");
+  static_assert(IN < 2 || sizeof(TB) == sizeof(TO), "lane mismatch");
+  static_assert(IN < 3 || sizeof(TC) == sizeof(TO), "lane mismatch");
+  const bool vec_ok = aligned16(out) && (IN < 1 || aligned16(a)) &&
+                      (IN < 2 || aligned16(b)) && (IN < 3 || aligned16(c));
+  size_t done = 0;
+  if (vec_ok && n >= static_cast<size_t>(lanes)) {
+    const size_t nvec = n / lanes;
+    unsigned grid = capped_grid(nvec, static_cast<size_t>(kBlock) * kUnroll, kCtasPerSm);
+    ew_vec_kernel<IN, F><<<grid, kBlock, 0, s>>>(
+        f, reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b),
+        reinterpret_cast<const uint4*>(c), reinterpret_cast<uint4*>(out), nvec, lanes);
+    done = nvec * lanes;
+  }
+  if (done < n) {
+    unsigned grid = capped_grid(n - done, kBlock, kCtasPerSm);
+    ew_scalar_kernel<IN, F, TA, TB, TC, TO><<<grid, kBlock, 0, s>>>(f, a, b, c, out, done, n);
+  }
+  return launch_status();
+}
+
+// ------------------------------------------------------------ functor helpers
+// fp32 functor from a per-element lambda-like struct E with
+//   float E::op(float a, float b, float c, size_t i)
+template <typename E>
+struct F32 {
+  E e;
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4 b, uint4 c, size_t i0) const {
+    Vec4f x, y, z, o;
+    x.u = a; y.u = b; z.u = c;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.f[k] = e.op(x.f[k], y.f[k], z.f[k], i0 + k);
+    return o.u;
+  }
+  __device__ __forceinline__ float one(float a, float b, float c, size_t i) const {
+    return e.op(a, b, c, i);
+  }
+};
+
+template <typename E>
+struct F16 {
+  E e;
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4 b, uint4 c, size_t i0) const {
+    Vec8h x, y, z, o;
+    x.u = a; y.u = b; z.u = c;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o.h[k] = e.op(x.h[k], y.h[k], z.h[k], i0 + k);
+    return o.u;
+  }
+  __device__ __forceinline__ __half one(__half a, __half b, __half c, size_t i) const {
+    return e.op(a, b, c, i);
+  }
+};
+
+#define SGB_E32(NAME, EXPR)                                                    \
+  struct NAME {                                                                \
+    float p0, p1;                                                              \
+    __device__ __forceinline__ float op(float a, float b, float c, size_t i)   \
+        const {                                                                \
+      (void)a; (void)b; (void)c; (void)i;                                      \
+      return (EXPR);                                                           \
+    }                                                                          \
+  };
+
+// ReLU family (math_kernel.cu:235-259)
+SGB_E32(ERelu, a > 0 ? a : 0.0f)
+SGB_E32(EReluBwd, b > 0 ? a : 0.0f)
+SGB_E32(EAddReluBwd, c > 0 ? (a + b) : 0.0f)
+// tensor (op) tensor (math_kernel.cu:111-149, 321-398, 414-487)
+SGB_E32(EAdd, a + b)
+SGB_E32(ESub, a - b)
+SGB_E32(EMul, a * b)
+SGB_E32(EDiv, a / b)
+SGB_E32(EPow, powf(a, b))
+SGB_E32(EGt, a > b ? 1.0f : 0.0f)
+SGB_E32(EGe, a >= b ? 1.0f : 0.0f)
+SGB_E32(EEq, a == b ? 1.0f : 0.0f)
+SGB_E32(ELt, a < b ? 1.0f : 0.0f)
+SGB_E32(ELe, a <= b ? 1.0f : 0.0f)
+// tensor (op) scalar p0
+SGB_E32(ESAdd, a + p0)
+SGB_E32(ESMul, a * p0)
+SGB_E32(ESRDiv, p0 / a)
+SGB_E32(ESPow, powf(a, p0))
+SGB_E32(ESGt, a > p0 ? 1.0f : 0.0f)
+SGB_E32(ESGe, a >= p0 ? 1.0f : 0.0f)
+SGB_E32(ESEq, a == p0 ? 1.0f : 0.0f)
+SGB_E32(ESLt, a < p0 ? 1.0f : 0.0f)
+SGB_E32(ESLe, a <= p0 ? 1.0f : 0.0f)
+SGB_E32(EClamp, a > p1 ? p1 : (a < p0 ? p0 : a))
+SGB_E32(ESet, p0)
+SGB_E32(ESparsAbs, fabsf(a) >= p0 ? a : 0.0f)
+// y += alpha x as one fused multiply-add per element (BLAS-1 axpy)
+SGB_E32(EAxpy, fmaf(p0, a, b))
+// one-input maths family (math_kernel.cu:150-233, 273-319, 653-675)
+SGB_E32(UAbs, fmaxf(a, -a))
+SGB_E32(USign, a > 0.0f ? 1.0f : (a < 0.0f ? -1.0f : 0.0f))
+SGB_E32(UExp, expf(a))
+SGB_E32(UErf, erff(a))
+SGB_E32(UCeil, ceilf(a))
+SGB_E32(UFloor, floorf(a))
+SGB_E32(URound, roundf(a))
+SGB_E32(URoundE, (ceilf(a * 2) == a * 2) ? roundf(a / 2) * 2 : roundf(a))
+SGB_E32(ULog, logf(a))
+SGB_E32(USqrt, sqrtf(a))
+SGB_E32(USquare, a * a)
+SGB_E32(UCos, cosf(a))
+SGB_E32(UCosh, coshf(a))
+SGB_E32(UAcos, acosf(a))
+SGB_E32(UAcosh, acoshf(a))
+SGB_E32(USin, sinf(a))
+SGB_E32(USinh, sinhf(a))
+SGB_E32(UAsin, asinf(a))
+SGB_E32(UAsinh, asinhf(a))
+SGB_E32(UTan, tanf(a))
+SGB_E32(UTanh, tanhf(a))
+SGB_E32(UAtan, atanf(a))
+SGB_E32(UAtanh, atanhf(a))
+SGB_E32(USigmoid, 1.0f / (1.0f + expf(-a)))
+SGB_E32(USoftplus, logf(1 + expf(a)))
+SGB_E32(USoftsign, a / (fmaxf(a, -a) + 1))
+
+#define SGB_E16(NAME, EXPR)                                                    \
+  struct NAME {                                                                \
+    __half p0;                                                                 \
+    __device__ __forceinline__ __half op(__half a, __half b, __half c,         \
+                                         size_t i) const {                     \
+      (void)a; (void)b; (void)c; (void)i;                                      \
+      return (EXPR);                                                           \
+    }                                                                          \
+  };
+// half rules of the reference (math_kernel.cu:243-251, 261-271, 111-117 ...)
+SGB_E16(HRelu, __hgt(a, __float2half(0.0f)) ? a : __float2half(0.0f))
+SGB_E16(HReluBwd, __hge(b, __float2half(0.0f)) ? a : __float2half(0.0f))
+SGB_E16(HAdd, __hadd(a, b))
+SGB_E16(HSub, __hsub(a, b))
+SGB_E16(HMul, __hmul(a, b))
+SGB_E16(HDiv, __hdiv(a, b))
+SGB_E16(HPow, __float2half(__powf(__half2float(a), __half2float(b))))
+SGB_E16(HSMul, __hmul(a, p0))
+SGB_E16(HSet, p0)
+
+// Functors whose operand types differ (casts, index generation).
+struct CastI32F32 {
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4, uint4, size_t) const {
+    Vec4f x, o; x.u = a;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.f[k] = static_cast<float>(x.i[k]);
+    return o.u;
+  }
+  __device__ __forceinline__ float one(int a, int, int, size_t) const {
+    return static_cast<float>(a);
+  }
+};
+struct CastF32I32 {
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4, uint4, size_t) const {
+    Vec4f x, o; x.u = a;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.i[k] = static_cast<int>(x.f[k]);
+    return o.u;
+  }
+  __device__ __forceinline__ int one(float a, float, float, size_t) const {
+    return static_cast<int>(a);
+  }
+};
+struct SparsIndex {  // in == 0 ? 0 : i + 1
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4, uint4, size_t i0) const {
+    Vec4f x, o; x.u = a;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.i[k] = x.f[k] == 0.0f ? 0 : static_cast<int>(i0 + k + 1);
+    return o.u;
+  }
+  __device__ __forceinline__ int one(float a, float, float, size_t i) const {
+    return a == 0.0f ? 0 : static_cast<int>(i + 1);
+  }
+};
+struct GenIndex {  // i + 1
+  __device__ __forceinline__ uint4 vec(uint4, uint4, uint4, size_t i0) const {
+    Vec4f o;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.i[k] = static_cast<int>(i0 + k + 1);
+    return o.u;
+  }
+  __device__ __forceinline__ int one(int, int, int, size_t i) const {
+    return static_cast<int>(i + 1);
+  }
+};
+struct AxpyDev {  // alpha read from device memory
+  const float* alpha;
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4 b, uint4, size_t) const {
+    const float al = __ldg(alpha);
+    Vec4f x, y, o; x.u = a; y.u = b;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.f[k] = fmaf(al, x.f[k], y.f[k]);
+    return o.u;
+  }
+  __device__ __forceinline__ float one(float a, float b, float, size_t) const {
+    return fmaf(__ldg(alpha), a, b);
+  }
+};
+
+// ------------------------------------------------- fp32 <-> fp16 cast kernels
+// 8 elements per thread-iteration: two 16-byte fp32 vectors <-> one 16-byte
+// fp16 vector, so both sides move in 128-bit transactions.
+template <bool SCALE>
+__global__ void __launch_bounds__(kBlock)
+cast_f16_f32_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                    size_t n8, float scale) {
+  const size_t tile = static_cast<size_t>(kBlock) * kUnroll;
+  for (size_t base = blockIdx.x * tile; base < n8; base += gridDim.x * tile) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t i = base + u * kBlock + threadIdx.x;
+      if (i < n8) v[u] = ld128_stream(in + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t i = base + u * kBlock + threadIdx.x;
+      if (i < n8) {
+        Vec8h h; h.u = v[u];
+        Vec4f lo, hi;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float a = __half2float(h.h[k]), b = __half2float(h.h[4 + k]);
+          lo.f[k] = SCALE ? a * scale : a;
+          hi.f[k] = SCALE ? b * scale : b;
+        }
+        st128(out + 2 * i, lo.u);
+        st128(out + 2 * i + 1, hi.u);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+cast_f32_f16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, size_t n8) {
+  const size_t tile = static_cast<size_t>(kBlock) * kUnroll;
+  for (size_t base = blockIdx.x * tile; base < n8; base += gridDim.x * tile) {
+    uint4 lo[kUnroll], hi[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t i = base + u * kBlock + threadIdx.x;
+      if (i < n8) {
+        lo[u] = ld128_stream(in + 2 * i);
+        hi[u] = ld128_stream(in + 2 * i + 1);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const size_t i = base + u * kBlock + threadIdx.x;
+      if (i < n8) {
+        Vec4f a, b; a.u = lo[u]; b.u = hi[u];
+        Vec8h h;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          h.h[k] = __float2half_rn(a.f[k]);
+          h.h[4 + k] = __float2half_rn(b.f[k]);
+        }
+        st128(out + i, h.u);
+      }
+    }
+  }
+}
+
+template <bool SCALE>
+__global__ void __launch_bounds__(kBlock)
+cast_f16_f32_scalar(const __half* in, float* out, size_t first, size_t n, float scale) {
+  for (size_t i = first + blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * kBlock) {
+    float a = __half2float(in[i]);
+    out[i] = SCALE ? a * scale : a;
+  }
+}
+__global__ void __launch_bounds__(kBlock)
+cast_f32_f16_scalar(const float* in, __half* out, size_t first, size_t n) {
+  for (size_t i = first + blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * kBlock)
+    out[i] = __float2half_rn(in[i]);
+}
+
+template <bool SCALE>
+int cast_h2f(const void* in, float scale, float* out, size_t n, void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!in || !out) return SGB_ERR_NULL;
+  cudaStream_t s = as_stream(stream);
+  size_t done = 0;
+  if (aligned16(in) && aligned16(out) && n >= 8) {
+    size_t n8 = n / 8;
+    unsigned grid = capped_grid(n8, static_cast<size_t>(kBlock) * kUnroll, kCtasPerSm);
+    cast_f16_f32_kernel<SCALE><<<grid, kBlock, 0, s>>>(
+        static_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), n8, scale);
+    done = n8 * 8;
+  }
+  if (done < n) {
+    unsigned grid = capped_grid(n - done, kBlock, kCtasPerSm);
+    cast_f16_f32_scalar<SCALE><<<grid, kBlock, 0, s>>>(static_cast<const __half*>(in), out, done, n, scale);
+  }
+  return launch_status();
+}
+
+// --------------------------------------------------------------- strided copy
+struct Dims {
+  int nd;
+  int shape[8];
+  int stride[8];
+};
+__global__ void __launch_bounds__(kBlock)
+strided_copy_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n, Dims d) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * kBlock) {
+    size_t accu = n, rem = i, off = 0;
+    for (int k = 0; k < d.nd; ++k) {
+      accu /= d.shape[k];
+      size_t idx = rem / accu;
+      rem -= idx * accu;
+      off += idx * static_cast<size_t>(d.stride[k]);
+    }
+    out[i] = in[off];
+  }
+}
+
+}  // namespace
+}  // namespace sgb
+
+using namespace sgb;
+
+// ------------------------------------------------------------------- C ABI
+#define RUN32_1(E, P0, P1, IN, OUT)                                            \
+  run<1, F32<E>, float, float, float, float>(F32<E>{E{P0, P1}}, IN, (const float*)nullptr, (const float*)nullptr, OUT, n, stream)
+#define RUN32_2(E, A, B, OUT)                                                  \
+  run<2, F32<E>, float, float, float, float>(F32<E>{E{0.f, 0.f}}, A, B, (const float*)nullptr, OUT, n, stream)
+
+extern "C" {
+
+int sgb_relu_f32(const float* x, float* y, size_t n, void* stream) {
+  return RUN32_1(ERelu, 0.f, 0.f, x, y);
+}
+int sgb_relu_backward_f32(const float* dy, const float* x, float* dx, size_t n, void* stream) {
+  return RUN32_2(EReluBwd, dy, x, dx);
+}
+int sgb_add_relu_backward_f32(const float* dy_a, const float* dy_b, const float* x,
+                              float* dx, size_t n, void* stream) {
+  return run<3, F32<EAddReluBwd>, float, float, float, float>(
+      F32<EAddReluBwd>{EAddReluBwd{0.f, 0.f}}, dy_a, dy_b, x, dx, n, stream);
+}
+
+#define H(p) static_cast<const __half*>(p)
+#define HO(p) static_cast<__half*>(p)
+#define RUN16_1(E, P0, IN, OUT)                                                \
+  run<1, F16<E>, __half, __half, __half, __half>(F16<E>{E{P0}}, H(IN), H(nullptr), H(nullptr), HO(OUT), n, stream)
+#define RUN16_2(E, A, B, OUT)                                                  \
+  run<2, F16<E>, __half, __half, __half, __half>(F16<E>{E{__half()}}, H(A), H(B), H(nullptr), HO(OUT), n, stream)
+
+int sgb_relu_f16(const void* x, void* y, size_t n, void* stream) {
+  return RUN16_1(HRelu, __half(), x, y);
+}
+int sgb_relu_backward_f16(const void* dy, const void* x, void* dx, size_t n, void* stream) {
+  return RUN16_2(HReluBwd, dy, x, dx);
+}
+
+int sgb_binary_f32(int op, const float* a, const float* b, float* out, size_t n, void* stream) {
+  switch (op) {
+    case SGB_ADD: return RUN32_2(EAdd, a, b, out);
+    case SGB_SUB: return RUN32_2(ESub, a, b, out);
+    case SGB_MUL: return RUN32_2(EMul, a, b, out);
+    case SGB_DIV: return RUN32_2(EDiv, a, b, out);
+    case SGB_POW: return RUN32_2(EPow, a, b, out);
+    case SGB_GT: return RUN32_2(EGt, a, b, out);
+    case SGB_GE: return RUN32_2(EGe, a, b, out);
+    case SGB_EQ: return RUN32_2(EEq, a, b, out);
+    case SGB_LT: return RUN32_2(ELt, a, b, out);
+    case SGB_LE: return RUN32_2(ELe, a, b, out);
+    default: return SGB_ERR_UNSUPPORTED;
+  }
+}
+
+int sgb_binary_f16(int op, const void* a, const void* b, void* out, size_t n, void* stream) {
+  switch (op) {
+    case SGB_ADD: return RUN16_2(HAdd, a, b, out);
+    case SGB_SUB: return RUN16_2(HSub, a, b, out);
+    case SGB_MUL: return RUN16_2(HMul, a, b, out);
+    case SGB_DIV: return RUN16_2(HDiv, a, b, out);
+    case SGB_POW: return RUN16_2(HPow, a, b, out);
+    default: return SGB_ERR_UNSUPPORTED;
+  }
+}
+
+int sgb_scalar_f32(int op, const float* in, float x, float* out, size_t n, void* stream) {
+  switch (op) {
+    case SGB_S_ADD: return RUN32_1(ESAdd, x, 0.f, in, out);
+    case SGB_S_MUL: return RUN32_1(ESMul, x, 0.f, in, out);
+    case SGB_S_RDIV: return RUN32_1(ESRDiv, x, 0.f, in, out);
+    case SGB_S_POW: return RUN32_1(ESPow, x, 0.f, in, out);
+    case SGB_S_GT: return RUN32_1(ESGt, x, 0.f, in, out);
+    case SGB_S_GE: return RUN32_1(ESGe, x, 0.f, in, out);
+    case SGB_S_EQ: return RUN32_1(ESEq, x, 0.f, in, out);
+    case SGB_S_LT: return RUN32_1(ESLt, x, 0.f, in, out);
+    case SGB_S_LE: return RUN32_1(ESLe, x, 0.f, in, out);
+    case SGB_S_THRESHOLD: return RUN32_1(ESLt, x, 0.f, in, out);
+    default: return SGB_ERR_UNSUPPORTED;
+  }
+}
+
+int sgb_scalar_mul_f16(const void* in, float x, void* out, size_t n, void* stream) {
+  return RUN16_1(HSMul, __float2half(x), in, out);
+}
+
+int sgb_unary_f32(int op, const float* in, float* out, size_t n, void* stream) {
+  switch (op) {
+#define U(CODE, E) case CODE: return RUN32_1(E, 0.f, 0.f, in, out);
+    U(SGB_ABS, UAbs) U(SGB_SIGN, USign) U(SGB_EXP, UExp) U(SGB_ERF, UErf)
+    U(SGB_CEIL, UCeil) U(SGB_FLOOR, UFloor) U(SGB_ROUND, URound)
+    U(SGB_ROUNDE, URoundE) U(SGB_LOG, ULog) U(SGB_SQRT, USqrt)
+    U(SGB_SQUARE, USquare) U(SGB_COS, UCos) U(SGB_COSH, UCosh)
+    U(SGB_ACOS, UAcos) U(SGB_ACOSH, UAcosh) U(SGB_SIN, USin) U(SGB_SINH, USinh)
+    U(SGB_ASIN, UAsin) U(SGB_ASINH, UAsinh) U(SGB_TAN, UTan) U(SGB_TANH, UTanh)
+    U(SGB_ATAN, UAtan) U(SGB_ATANH, UAtanh) U(SGB_SIGMOID, USigmoid)
+    U(SGB_SOFTPLUS, USoftplus) U(SGB_SOFTSIGN, USoftsign)
+#undef U
+    default: return SGB_ERR_UNSUPPORTED;
+  }
+}
+
+int sgb_clamp_f32(float low, float high, const float* in, float* out, size_t n, void* stream) {
+  return RUN32_1(EClamp, low, high, in, out);
+}
+
+int sgb_set_f32(float v, float* out, size_t n, void* stream) {
+  return run<0, F32<ESet>, float, float, float, float>(
+      F32<ESet>{ESet{v, 0.f}}, (const float*)nullptr, (const float*)nullptr,
+      (const float*)nullptr, out, n, stream);
+}
+int sgb_set_f16(float v, void* out, size_t n, void* stream) {
+  return run<0, F16<HSet>, __half, __half, __half, __half>(
+      F16<HSet>{HSet{__float2half_rn(v)}}, H(nullptr), H(nullptr), H(nullptr), HO(out), n, stream);
+}
+
+int sgb_cast_f32_f16(const float* in, void* out, size_t n, void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!in || !out) return SGB_ERR_NULL;
+  cudaStream_t s = as_stream(stream);
+  size_t done = 0;
+  if (aligned16(in) && aligned16(out) && n >= 8) {
+    size_t n8 = n / 8;
+    unsigned grid = capped_grid(n8, static_cast<size_t>(kBlock) * kUnroll, kCtasPerSm);
+    cast_f32_f16_kernel<<<grid, kBlock, 0, s>>>(reinterpret_cast<const uint4*>(in),
+                                                static_cast<uint4*>(out), n8);
+    done = n8 * 8;
+  }
+  if (done < n) {
+    unsigned grid = capped_grid(n - done, kBlock, kCtasPerSm);
+    cast_f32_f16_scalar<<<grid, kBlock, 0, s>>>(in, HO(out), done, n);
+  }
+  return launch_status();
+}
+int sgb_cast_f16_f32(const void* in, float* out, size_t n, void* stream) {
+  return cast_h2f<false>(in, 1.0f, out, n, stream);
+}
+int sgb_cast_f16_f32_scaled(const void* in, float scale, float* out, size_t n, void* stream) {
+  return cast_h2f<true>(in, scale, out, n, stream);
+}
+int sgb_cast_f32_i32(const float* in, int32_t* out, size_t n, void* stream) {
+  return run<1, CastF32I32, float, float, float, int>(CastF32I32{}, in, (const float*)nullptr,
+                                                      (const float*)nullptr, out, n, stream);
+}
+int sgb_cast_i32_f32(const int32_t* in, float* out, size_t n, void* stream) {
+  return run<1, CastI32F32, int, int, int, float>(CastI32F32{}, in, (const int*)nullptr,
+                                                  (const int*)nullptr, out, n, stream);
+}
+
+int sgb_axpy_f32(float alpha, const float* x, float* y, size_t n, void* stream) {
+  return run<2, F32<EAxpy>, float, float, float, float>(
+      F32<EAxpy>{EAxpy{alpha, 0.f}}, x, y, (const float*)nullptr, y, n, stream);
+}
+int sgb_axpy_dev_alpha_f32(const float* alpha_dev, const float* x, float* y, size_t n, void* stream) {
+  if (n && !alpha_dev) return SGB_ERR_NULL;
+  return run<2, AxpyDev, float, float, float, float>(AxpyDev{alpha_dev}, x, y,
+                                                     (const float*)nullptr, y, n, stream);
+}
+
+int sgb_strided_copy_f32(const float* in, float* out, size_t n, int nDim,
+                         const int* shape_host, const int* stride_host, void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!in || !out || !shape_host || !stride_host) return SGB_ERR_NULL;
+  if (nDim < 1 || nDim > 8) return SGB_ERR_SIZE;
+  Dims d;
+  d.nd = nDim;
+  size_t prod = 1;
+  for (int k = 0; k < nDim; ++k) {
+    if (shape_host[k] <= 0 || stride_host[k] < 0) return SGB_ERR_SIZE;
+    d.shape[k] = shape_host[k];
+    d.stride[k] = stride_host[k];
+    prod *= static_cast<size_t>(shape_host[k]);
+  }
+  if (prod != n) return SGB_ERR_SIZE;
+  unsigned grid = capped_grid(n, kBlock, kCtasPerSm);
+  strided_copy_kernel<<<grid, kBlock, 0, as_stream(stream)>>>(in, out, n, d);
+  return launch_status();
+}
+
+int sgb_sparsabs_f32(float thr, const float* in, float* out, size_t n, void* stream) {
+  return RUN32_1(ESparsAbs, thr, 0.f, in, out);
+}
+int sgb_sparsindex_f32(const float* in, int32_t* out, size_t n, void* stream) {
+  if (n > 0x7fffffffu) return SGB_ERR_SIZE;  // 1-based int32 indices
+  return run<1, SparsIndex, float, float, float, int>(SparsIndex{}, in, (const float*)nullptr,
+                                                      (const float*)nullptr, out, n, stream);
+}
+int sgb_generateindex_i32(int32_t* out, size_t n, void* stream) {
+  if (n > 0x7fffffffu) return SGB_ERR_SIZE;
+  return run<0, GenIndex, int, int, int, int>(GenIndex{}, (const int*)nullptr, (const int*)nullptr,
+                                              (const int*)nullptr, out, n, stream);
+}
+
+}  // extern "C"
