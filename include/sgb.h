@@ -154,6 +154,240 @@ int sgb_sparsabs_f32(float thr, const float *in, float *out, size_t n,
 int sgb_sparsindex_f32(const float *in, int32_t *out, size_t n, void *stream);
 int sgb_generateindex_i32(int32_t *out, size_t n, void *stream);
 
+/* ------------------------------------------------------------- reductions */
+/* SumRows: v[c] = sum over rows of M[r][c], M row-major nrow x ncol - the
+ * bias-gradient reduction.  Replaces SumRows (src/core/tensor/tensor.cc:
+ * 1523-1538: ones vector + cudnnSetTensor + transposed cublasSgemv via
+ * GEMV<float, lang::Cuda>, tensor_math_cuda.h:1129-1146).  Workspace: see
+ * sgb_sum_rows_workspace_bytes (0 for most shapes); sizes depend on the SM
+ * count of the current device. */
+size_t sgb_sum_rows_workspace_bytes(size_t nrow, size_t ncol);
+int sgb_sum_rows_f32(const float *M, float *v, size_t nrow, size_t ncol,
+                     void *ws, size_t ws_bytes, void *stream);
+/* SumColumns: v[r] = sum over columns of M[r][c] (tensor.cc:1508-1522). */
+int sgb_sum_columns_f32(const float *M, float *v, size_t nrow, size_t ncol,
+                        void *stream);
+/* RowMax seeded with the first element (cuda::RowMax, math_kernel.h:173-174,
+ * math_kernel.cu:488-499). */
+int sgb_row_max_f32(const float *M, float *v, size_t nrow, size_t ncol,
+                    void *stream);
+/* Convolution bias gradient db[c] = sum_{n,h,w} dy[n][c][h][w] (NCHW,
+ * HW = H*W).  Replaces GpuConvBackwardb (src/model/operation/convolution.cc:
+ * 684-702, cudnnConvolutionBackwardBias). */
+size_t sgb_conv_bias_backward_workspace_bytes(int N, int C, int HW);
+int sgb_conv_bias_backward_f32(const float *dy, float *db, int N, int C, int HW,
+                               void *ws, size_t ws_bytes, void *stream);
+/* SumAll: out[0] = sum of x (device scalar).  Replaces SumAll
+ * (tensor.cc:1242-1254: ones tensor + Dot<float, lang::Cuda>,
+ * tensor_math_cuda.h:1084-1094). */
+size_t sgb_sum_all_workspace_bytes(size_t n);
+int sgb_sum_all_f32(const float *x, float *out, size_t n, void *ws,
+                    size_t ws_bytes, void *stream);
+
+/* --------------------------------------------------- softmax / cross entropy */
+/* Row softmax exp(x - rowmax) / sum; y may alias x.  Replaces
+ * SoftMax<float, lang::Cuda> (tensor_math_cuda.h:1274-1305,
+ * CUDNN_SOFTMAX_ACCURATE / MODE_INSTANCE). */
+int sgb_softmax_rows_f32(const float *x, float *y, size_t nrow, size_t ncol,
+                         void *stream);
+/* loss[i] = -log(max(p[i][t[i]], FLT_MIN)) (int_target) or the normalised
+ * weighted sum for a batch x dim int32 target array.  Replaces
+ * cuda::ComputeCrossEntropy (math_kernel.h:160-162) behind
+ * ComputeCrossEntropy<float, lang::Cuda> (tensor_math_cuda.h:1375-1397). */
+int sgb_cross_entropy_f32(int int_target, size_t batch, size_t dim,
+                          const float *p, const int32_t *t, float *loss,
+                          void *stream);
+/* grad = p - target.  Same argument list as cuda::SoftmaxCrossEntropyBwd
+ * (math_kernel.h:166-168; SoftmaxCrossEntropyBwd<float, lang::Cuda>,
+ * tensor_math_cuda.h:1399-1425); grad may alias p (the reference edits a
+ * clone of p in place) or be a separate buffer (saves the clone). */
+int sgb_softmax_cross_entropy_bwd_f32(int int_target, size_t batch, size_t dim,
+                                      const float *p, const int32_t *t,
+                                      float *grad, void *stream);
+/* grad = (p - target) * scale: the pair SoftmaxCrossEntropyBwd + "dx /= N"
+ * of python/singa/autograd.py:1319-1322 in one pass (scale = 1/N as fp32). */
+int sgb_softmax_cross_entropy_grad_f32(int int_target, size_t batch, size_t dim,
+                                       const float *p, const int32_t *t,
+                                       float scale, float *grad, void *stream);
+
+/* --------------------------------------------------- batch-norm backward */
+/* Training-mode backward from the saved batch mean and saved INVERSE standard
+ * deviation (what the reference's forward stores in its `var` tensor).
+ * Spatial mode: x, dy, dx are N x C x HW (NCHW); per-activation mode (2-D
+ * N x D input): pass C = D, HW = 1.  dscale/dbias have C elements; dx may
+ * alias dy.  Replaces GpuBatchNormBackward (src/model/operation/batchnorm.cc:
+ * 368-404, cudnnBatchNormalizationBackward with alpha=1, beta=0).  Workspace
+ * (16-byte aligned): sgb_bn_backward_workspace_bytes. */
+size_t sgb_bn_backward_workspace_bytes(int N, int C, int HW);
+int sgb_bn_backward_f32(const float *x, const float *dy, const float *scale,
+                        const float *mean, const float *invstd, float *dx,
+                        float *dscale, float *dbias, int N, int C, int HW,
+                        void *ws, size_t ws_bytes, void *stream);
+/* Same with the backward of the ReLU that follows the BN layer folded in:
+ * dy is first masked by relu_in > 0 (relu_in = the tensor ReLU stored, i.e.
+ * the BN output).  Equals ReLUBackward + GpuBatchNormBackward bit for bit. */
+int sgb_bn_relu_backward_f32(const float *x, const float *dy,
+                             const float *relu_in, const float *scale,
+                             const float *mean, const float *invstd, float *dx,
+                             float *dscale, float *dbias, int N, int C, int HW,
+                             void *ws, size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------ pooling */
+/* Output extent (src/model/operation/pooling.cc:46-51). */
+int sgb_pool_out_size(int in, int kernel, int pad, int stride);
+/* Forward partners (GpuPoolingForward, pooling.cc:180-205). */
+int sgb_maxpool_forward_f32(const float *x, float *y, int N, int C, int H,
+                            int W, int kh, int kw, int ph, int pw, int sh,
+                            int sw, void *stream);
+int sgb_avgpool_forward_f32(const float *x, float *y, int N, int C, int H,
+                            int W, int kh, int kw, int ph, int pw, int sh,
+                            int sw, void *stream);
+/* Replaces GpuPoolingBackward (pooling.cc:207-226, cudnnPoolingBackward with
+ * y, dy, x).  Max: each window's dy goes to its FIRST maximum in raster
+ * order; avg: dy / (window cells inside the image).  Deterministic gather. */
+int sgb_maxpool_backward_f32(const float *x, const float *y, const float *dy,
+                             float *dx, int N, int C, int H, int W, int kh,
+                             int kw, int ph, int pw, int sh, int sw,
+                             void *stream);
+int sgb_avgpool_backward_f32(const float *dy, float *dx, int N, int C, int H,
+                             int W, int kh, int kw, int ph, int pw, int sh,
+                             int sw, void *stream);
+
+/* ------------------------------------------------- SGD update, multi-tensor */
+/* One fused pass of SGD.apply (python/singa/opt.py:269-310) over p, g, m:
+ *   g *= grad_scale (DistOpt.update's grad /= world, opt.py:738-746)
+ *   g += weight_decay * p ; m = m * momentum ; m += (1 - dampening) * g
+ *   p += -lr * (nesterov ? g + momentum * m : m)
+ * each step rounded once like the BLAS-1 call it replaces (Axpy<float,
+ * lang::Cuda>, tensor_math_cuda.h:1031-1049).  momentum == 0 skips m
+ * (moment may be NULL).  g is read only; its reference post-state is not
+ * produced.  params/grads/moments/sizes are HOST arrays of `count` entries. */
+int sgb_sgd_update_f32(float *param, const float *grad, float *moment, size_t n,
+                       float lr, float momentum, float dampening,
+                       float weight_decay, int nesterov, float grad_scale,
+                       void *stream);
+int sgb_sgd_update_multi_f32(void *const *params, void *const *grads,
+                             void *const *moments, const size_t *sizes,
+                             size_t count, float lr, float momentum,
+                             float dampening, float weight_decay, int nesterov,
+                             float grad_scale, void *stream);
+
+/* ------------------------------------------------ bucket pack / unpack */
+/* Gather a HOST list of fp32 tensors into a flat device buffer starting at
+ * element flat_offset, back to back (the per-tensor cudaMemcpyAsync loop of
+ * Communicator::fusedSynch, src/io/communicator.cc:235-253), optionally
+ * rounding to fp16 on the way (fusedSynchHalf's copy + float2half passes,
+ * communicator.cc:351-370).  Unpack is the reverse (communicator.cc:281-300,
+ * 393-412) with an optional multiply by `scale` after widening. */
+int sgb_pack_f32(void *const *tensors, const size_t *sizes, size_t count,
+                 float *flat, size_t flat_offset, void *stream);
+int sgb_pack_f32_to_f16(void *const *tensors, const size_t *sizes, size_t count,
+                        void *flat_f16, size_t flat_offset, void *stream);
+int sgb_unpack_f32(const float *flat, size_t flat_offset, void *const *tensors,
+                   const size_t *sizes, size_t count, float scale,
+                   void *stream);
+int sgb_unpack_f16_to_f32(const void *flat_f16, size_t flat_offset,
+                          void *const *tensors, const size_t *sizes,
+                          size_t count, float scale, void *stream);
+
+/* ------------------------------------------------- sparsification kernels */
+/* Workspace (256-byte aligned) for the two selectors below. */
+size_t sgb_sparse_workspace_bytes(size_t n);
+/* K of the top-K variant: (int)ceil(ratio * n) evaluated in fp32 exactly as
+ * Communicator::topKSparsAllReduce does (src/io/communicator.cc:744). */
+int sgb_topk_count(float ratio, size_t n);
+/* Threshold selection with residual correction, one call for the sequence
+ * add(acc) / backup / sparsabs / sub / sparsindex / removezeroidx /
+ * removezeroval of Communicator::valSparsAllReduce (communicator.cc:626-680;
+ * cuda::sparsabs, sparsindex, removezeroidx, removezeroval,
+ * math_kernel.h:180-190):  s = g + acc; kept = |s| >= thr ? s : 0;
+ * acc = s - kept; payload = (i+1, kept) for kept != 0 in ascending i.
+ * acc may be NULL (no correction).  *nnz_dev (device) receives the count.
+ * idx_out / val_out need room for n entries.  n <= 2^31-1. */
+int sgb_sparse_threshold_f32(const float *g, float *acc, size_t n, float thr,
+                             int32_t *idx_out, float *val_out,
+                             int32_t *nnz_dev, void *ws, size_t ws_bytes,
+                             void *stream);
+/* Top-K selection with residual correction; replaces generateindex +
+ * sortbykey (thrust::sort_by_key of all n pairs) + the cusparseSaxpyi
+ * residual update of Communicator::topKSparsAllReduce (communicator.cc:
+ * 721-765; math_kernel.h:184,190) by a 3-pass radix select.  s = g + acc is
+ * materialised in sum_scratch (n floats).  The k entries with the largest key
+ * are written in ascending index order, ties broken by lower index;
+ * acc = s with the selected entries zeroed.
+ * mode 0: key = |s|.  mode 1: key = |(int)s|, which is what the reference's
+ * comparator evaluates (math_kernel.cu:715-721 truncates both operands to int).
+ */
+int sgb_sparse_topk_f32(const float *g, float *acc, float *sum_scratch,
+                        size_t n, size_t k, int mode, int32_t *idx_out,
+                        float *val_out, void *ws, size_t ws_bytes,
+                        void *stream);
+/* dst[idx[j]-1] += val[j] for j < count (or < *count_dev when count_dev is
+ * not NULL); idx 0 = padding, skipped.  Replaces cusparseSaxpyi with
+ * CUSPARSE_INDEX_BASE_ONE (communicator.cc:715-717, 753-756, 803-805; the
+ * routine no longer exists in CUDA 12).  n = length of dst. */
+int sgb_scatter_add_f32(const int32_t *idx, const float *val, size_t count,
+                        const int32_t *count_dev, float *dst, size_t n,
+                        void *stream);
+
+/* ------------------------------------------------------------ communicator */
+/* Opaque handle standing in for class singa::Communicator
+ * (include/singa/io/communicator.h:76-156, src/io/communicator.cc).  One per
+ * process / GPU; creation binds to the CURRENT device, initialises the NCCL
+ * communicator (ncclCommInitRank, communicator.cc:105-107), allocates the
+ * two staging buffers of max_elems floats and three non-blocking side
+ * streams (the reference takes them from Context: s, c1, c2,
+ * src/core/device/cuda_gpu.cc:76-80).  Half and sparse buffers are allocated
+ * at first use, as halfInit / sparsInit do (communicator.cc:114-139). */
+typedef struct sgb_comm sgb_comm;
+int sgb_last_nccl_error(void);
+/* NcclIdHolder (communicator.cc:49-51): id_out receives
+ * sgb_comm_unique_id_bytes() bytes to be shipped to every rank by the host. */
+int sgb_comm_unique_id_bytes(void);
+int sgb_comm_get_unique_id(void *id_out);
+int sgb_comm_create(sgb_comm **out, int rank, int world, const void *unique_id,
+                    size_t max_elems);
+int sgb_comm_destroy(sgb_comm *c);
+int sgb_comm_rank(const sgb_comm *c);
+int sgb_comm_world_size(const sgb_comm *c);
+size_t sgb_comm_staged_elems(const sgb_comm *c);
+void *sgb_comm_stream(const sgb_comm *c, int which);
+/* 1 (default): top-K key as the reference's comparator computes it;
+ * 0: key = |value|. */
+int sgb_comm_set_topk_mode(sgb_comm *c, int mode);
+/* Communicator::wait (communicator.cc:169-186): the compute stream waits for
+ * the three side streams. */
+int sgb_comm_wait(sgb_comm *c, void *compute_stream);
+/* Communicator::synch (communicator.cc:304-328): in-place all-reduce(sum) on
+ * stream s after the compute stream's work so far. */
+int sgb_comm_synch(sgb_comm *c, void *data, size_t n, int is_half,
+                   void *compute_stream);
+/* Communicator::fusedSynch(t, send) (communicator.cc:212-302).  send == 0:
+ * append the tensors to the staging buffer (one pack launch).  send != 0:
+ * all-reduce everything staged, then scatter the result back into `tensors`
+ * (the full list staged since the last flush, in staging order).  tensors /
+ * sizes are HOST arrays.  SGB_ERR_CAPACITY if the bucket would overflow. */
+int sgb_comm_fused_synch(sgb_comm *c, void *const *tensors, const size_t *sizes,
+                         size_t count, int is_half, int send,
+                         void *compute_stream);
+/* Communicator::synchHalf / fusedSynchHalf (communicator.cc:330-467): fp32
+ * gradients are rounded to fp16, summed in fp16, widened back. */
+int sgb_comm_synch_half(sgb_comm *c, float *data, size_t n,
+                        void *compute_stream);
+int sgb_comm_fused_synch_half(sgb_comm *c, void *const *tensors,
+                              const size_t *sizes, size_t count, int send,
+                              void *compute_stream);
+/* Communicator::sparsification / fusedSparsification (communicator.cc:
+ * 469-617) -> valSparsAllReduce / topKSparsAllReduce (:619-807).  count == 1
+ * is the single-tensor form.  accumulation (device, total size) may be NULL.
+ * topk == 0: spars is the magnitude threshold; the call blocks the host until
+ * the per-rank counts have arrived (as the reference does).  topk != 0: spars
+ * is the fraction of elements sent; fully asynchronous. */
+int sgb_comm_sparsification(sgb_comm *c, void *const *tensors,
+                            const size_t *sizes, size_t count,
+                            float *accumulation, float spars, int topk,
+                            void *compute_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,356 @@
+// Data-parallel gradient communicator: dense all-reduce (direct and bucketed),
+// fp16-compressed all-reduce, and sparsified all-gather (threshold / top-K with
+// residual correction), one process per GPU over NCCL on NVLink / NVSwitch.
+//
+// It keeps the reference communicator's observable structure - a compute
+// stream plus three side streams (c1: pre-processing, s: NCCL, c2:
+// post-processing) chained by events, staging buffers of maxSize elements,
+// sum semantics (the caller divides by the world size) - and replaces the
+// per-tensor memcpy / cast / thrust / cuSPARSE passes around the collectives
+// by the fused kernels of this library:
+//   stage   = one multi-tensor pack (+ fp32->fp16 cast) launch per call
+//   flush   = collective + one multi-tensor unpack (+ fp16->fp32 cast) launch
+//   sparse  = residual + select + order-preserving compaction, radix select
+//             instead of a full sort, one scatter-add launch per rank.
+// Each cross-stream edge has its own event.  No TMA multicast and no peer
+// pointers are used: remote data reaches local HBM through NCCL only.
+#include <nccl.h>
+
+#include <atomic>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "sparse.cuh"
+
+namespace {
+std::atomic<int> g_last_nccl_error{0};
+
+int nccl_fail(ncclResult_t r) {
+  g_last_nccl_error.store(static_cast<int>(r));
+  return SGB_ERR_NCCL;
+}
+}  // namespace
+
+#define CU(call)                                            \
+  do {                                                      \
+    cudaError_t e__ = (call);                               \
+    if (e__ != cudaSuccess) return sgb::note_cuda_error(e__); \
+  } while (0)
+#define NC(call)                                   \
+  do {                                             \
+    ncclResult_t r__ = (call);                     \
+    if (r__ != ncclSuccess) return nccl_fail(r__); \
+  } while (0)
+#define OK(call)                     \
+  do {                               \
+    int s__ = (call);                \
+    if (s__ != SGB_OK) return s__;   \
+  } while (0)
+
+struct sgb_comm {
+  int rank = 0, world = 1, device = 0;
+  ncclComm_t nccl = nullptr;
+  size_t max_elems = 0;
+  float* send = nullptr;   // fusedSendBuff
+  float* recv = nullptr;   // fusedRecvBuff
+  __half* send_h = nullptr;
+  __half* recv_h = nullptr;
+  // sparse path (allocated at first use)
+  float* sum = nullptr;        // g + acc (backupBuff)
+  int* pay_send = nullptr;     // [idx | val], 2 * max_elems words
+  int* pay_recv = nullptr;     // world * 2 * max_elems words
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  int* nnz_dev = nullptr;      // [0] own count, [1 .. world] all ranks
+  int* nnz_host = nullptr;     // pinned, world entries
+  int topk_mode = 1;           // 1 = the reference comparator's key, 0 = |value|
+  cudaStream_t s = nullptr, c1 = nullptr, c2 = nullptr;
+  cudaEvent_t ev_compute = nullptr, ev_c1 = nullptr, ev_s = nullptr, ev_c2 = nullptr,
+              ev_host = nullptr;
+  size_t send_off = 0;         // elements staged since the last flush
+  bool used = false;
+};
+
+namespace {
+
+int edge(cudaEvent_t ev, cudaStream_t from, cudaStream_t to) {
+  CU(cudaEventRecord(ev, from));
+  CU(cudaStreamWaitEvent(to, ev, 0));
+  return SGB_OK;
+}
+
+int half_init(sgb_comm* c) {
+  if (c->send_h) return SGB_OK;
+  CU(cudaMalloc(&c->send_h, c->max_elems * sizeof(__half)));
+  CU(cudaMalloc(&c->recv_h, c->max_elems * sizeof(__half)));
+  return SGB_OK;
+}
+
+int sparse_init(sgb_comm* c) {
+  if (c->sum) return SGB_OK;
+  const size_t n = c->max_elems;
+  CU(cudaMalloc(&c->sum, n * sizeof(float)));
+  CU(cudaMalloc(&c->pay_send, 2 * n * sizeof(int)));
+  CU(cudaMalloc(&c->pay_recv, 2 * n * sizeof(int) * static_cast<size_t>(c->world)));
+  c->ws_bytes = sgb_sparse_workspace_bytes(n);
+  CU(cudaMalloc(&c->ws, c->ws_bytes));
+  CU(cudaMalloc(&c->nnz_dev, sizeof(int) * (c->world + 1)));
+  CU(cudaMallocHost(&c->nnz_host, sizeof(int) * c->world));
+  return SGB_OK;
+}
+
+size_t total_of(const size_t* sizes, size_t count) {
+  size_t t = 0;
+  for (size_t i = 0; i < count; ++i) t += sizes[i];
+  return t;
+}
+
+int check_list(void* const* tensors, const size_t* sizes, size_t count) {
+  if (count == 0) return SGB_ERR_SIZE;  // the reference CHECKs t.size() > 0
+  if (!tensors || !sizes) return SGB_ERR_NULL;
+  for (size_t i = 0; i < count; ++i)
+    if (sizes[i] && !tensors[i]) return SGB_ERR_NULL;
+  return SGB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sgb_last_nccl_error(void) { return g_last_nccl_error.load(); }
+
+int sgb_comm_unique_id_bytes(void) { return static_cast<int>(sizeof(ncclUniqueId)); }
+
+int sgb_comm_get_unique_id(void* id_out) {
+  if (!id_out) return SGB_ERR_NULL;
+  ncclUniqueId id;
+  NC(ncclGetUniqueId(&id));
+  std::memcpy(id_out, &id, sizeof(id));
+  return SGB_OK;
+}
+
+int sgb_comm_create(sgb_comm** out, int rank, int world, const void* unique_id, size_t max_elems) {
+  if (!out || !unique_id) return SGB_ERR_NULL;
+  if (world < 1 || rank < 0 || rank >= world || max_elems == 0) return SGB_ERR_SIZE;
+  if (max_elems > 0x7fffffffu) return SGB_ERR_SIZE;  // collective counts and 1-based indices are int32
+  sgb_comm* c = new (std::nothrow) sgb_comm();
+  if (!c) return SGB_ERR_STATE;
+  c->rank = rank;
+  c->world = world;
+  c->max_elems = max_elems;
+  *out = c;  // handed out early so a failed create can still be destroyed
+  CU(cudaGetDevice(&c->device));
+  ncclUniqueId id;
+  std::memcpy(&id, unique_id, sizeof(id));
+  NC(ncclCommInitRank(&c->nccl, world, id, rank));
+  CU(cudaMalloc(&c->send, max_elems * sizeof(float)));
+  CU(cudaMalloc(&c->recv, max_elems * sizeof(float)));
+  CU(cudaStreamCreateWithFlags(&c->s, cudaStreamNonBlocking));
+  CU(cudaStreamCreateWithFlags(&c->c1, cudaStreamNonBlocking));
+  CU(cudaStreamCreateWithFlags(&c->c2, cudaStreamNonBlocking));
+  cudaEvent_t* evs[] = {&c->ev_compute, &c->ev_c1, &c->ev_s, &c->ev_c2};
+  for (cudaEvent_t* e : evs) CU(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+  CU(cudaEventCreateWithFlags(&c->ev_host, cudaEventDisableTiming | cudaEventBlockingSync));
+  return SGB_OK;
+}
+
+int sgb_comm_destroy(sgb_comm* c) {
+  if (!c) return SGB_OK;
+  if (c->s) cudaStreamSynchronize(c->s);
+  if (c->c1) cudaStreamSynchronize(c->c1);
+  if (c->c2) cudaStreamSynchronize(c->c2);
+  if (c->nccl) ncclCommDestroy(c->nccl);
+  void* bufs[] = {c->send, c->recv, c->send_h, c->recv_h, c->sum, c->pay_send,
+                  c->pay_recv, c->ws, c->nnz_dev};
+  for (void* b : bufs)
+    if (b) cudaFree(b);
+  if (c->nnz_host) cudaFreeHost(c->nnz_host);
+  cudaEvent_t evs[] = {c->ev_compute, c->ev_c1, c->ev_s, c->ev_c2, c->ev_host};
+  for (cudaEvent_t e : evs)
+    if (e) cudaEventDestroy(e);
+  cudaStream_t ss[] = {c->s, c->c1, c->c2};
+  for (cudaStream_t st : ss)
+    if (st) cudaStreamDestroy(st);
+  delete c;
+  return SGB_OK;
+}
+
+int sgb_comm_rank(const sgb_comm* c) { return c ? c->rank : -1; }
+int sgb_comm_world_size(const sgb_comm* c) { return c ? c->world : -1; }
+size_t sgb_comm_staged_elems(const sgb_comm* c) { return c ? c->send_off : 0; }
+
+int sgb_comm_set_topk_mode(sgb_comm* c, int mode) {
+  if (!c) return SGB_ERR_NULL;
+  if (mode != 0 && mode != 1) return SGB_ERR_UNSUPPORTED;
+  c->topk_mode = mode;
+  return SGB_OK;
+}
+
+/* The three side streams, for callers that profile or order against them:
+ * which = 0 (s, NCCL), 1 (c1), 2 (c2). */
+void* sgb_comm_stream(const sgb_comm* c, int which) {
+  if (!c) return nullptr;
+  return which == 0 ? c->s : (which == 1 ? c->c1 : (which == 2 ? c->c2 : nullptr));
+}
+
+int sgb_comm_wait(sgb_comm* c, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  if (!c->used) return SGB_OK;  // nothing was synchronised yet
+  cudaStream_t cs = sgb::as_stream(compute_stream);
+  OK(edge(c->ev_s, c->s, cs));
+  OK(edge(c->ev_c1, c->c1, cs));
+  OK(edge(c->ev_c2, c->c2, cs));
+  return SGB_OK;
+}
+
+int sgb_comm_synch(sgb_comm* c, void* data, size_t n, int is_half, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  if (n == 0) return SGB_OK;
+  if (!data) return SGB_ERR_NULL;
+  if (n > 0x7fffffffu) return SGB_ERR_SIZE;
+  c->used = true;
+  OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->s));
+  NC(ncclAllReduce(data, data, n, is_half ? ncclHalf : ncclFloat, ncclSum, c->nccl, c->s));
+  return SGB_OK;
+}
+
+int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
+                         int is_half, int send, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  OK(check_list(tensors, sizes, count));
+  c->used = true;
+  const size_t esz = is_half ? sizeof(__half) : sizeof(float);
+  if (!send) {
+    const size_t total = total_of(sizes, count);
+    if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
+    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+    if (!is_half) {
+      OK(sgb_pack_f32(tensors, sizes, count, c->send, c->send_off, c->c1));
+    } else {
+      size_t off = c->send_off;
+      for (size_t i = 0; i < count; ++i) {
+        CU(cudaMemcpyAsync(reinterpret_cast<char*>(c->send) + off * esz, tensors[i],
+                           sizes[i] * esz, cudaMemcpyDeviceToDevice, c->c1));
+        off += sizes[i];
+      }
+    }
+    c->send_off += total;
+    return SGB_OK;
+  }
+  // flush: everything staged so far is reduced; `tensors` receive the result
+  const size_t total = total_of(sizes, count);
+  if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  OK(edge(c->ev_c1, c->c1, c->s));
+  if (c->send_off)
+    NC(ncclAllReduce(c->send, c->recv, c->send_off, is_half ? ncclHalf : ncclFloat, ncclSum,
+                     c->nccl, c->s));
+  c->send_off = 0;
+  OK(edge(c->ev_s, c->s, c->c1));
+  if (!is_half) {
+    OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c1));
+  } else {
+    size_t off = 0;
+    for (size_t i = 0; i < count; ++i) {
+      CU(cudaMemcpyAsync(tensors[i], reinterpret_cast<char*>(c->recv) + off * esz, sizes[i] * esz,
+                         cudaMemcpyDeviceToDevice, c->c1));
+      off += sizes[i];
+    }
+  }
+  return SGB_OK;
+}
+
+int sgb_comm_synch_half(sgb_comm* c, float* data, size_t n, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  if (n == 0) return SGB_OK;
+  if (!data) return SGB_ERR_NULL;
+  if (n > c->max_elems) return SGB_ERR_CAPACITY;
+  OK(half_init(c));
+  c->used = true;
+  OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+  OK(sgb_cast_f32_f16(data, c->send_h, n, c->c1));
+  OK(edge(c->ev_c1, c->c1, c->s));
+  NC(ncclAllReduce(c->send_h, c->recv_h, n, ncclHalf, ncclSum, c->nccl, c->s));
+  OK(edge(c->ev_s, c->s, c->c2));
+  OK(sgb_cast_f16_f32(c->recv_h, data, n, c->c2));
+  return SGB_OK;
+}
+
+int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* sizes,
+                              size_t count, int send, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  OK(check_list(tensors, sizes, count));
+  OK(half_init(c));
+  c->used = true;
+  const size_t total = total_of(sizes, count);
+  if (!send) {
+    if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
+    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+    // copy + float2half of the reference collapse into one pack-and-cast pass
+    OK(sgb_pack_f32_to_f16(tensors, sizes, count, c->send_h, c->send_off, c->c1));
+    c->send_off += total;
+    return SGB_OK;
+  }
+  if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  OK(edge(c->ev_c1, c->c1, c->s));
+  if (c->send_off)
+    NC(ncclAllReduce(c->send_h, c->recv_h, c->send_off, ncclHalf, ncclSum, c->nccl, c->s));
+  c->send_off = 0;
+  OK(edge(c->ev_s, c->s, c->c2));
+  OK(sgb_unpack_f16_to_f32(c->recv_h, 0, tensors, sizes, count, 1.0f, c->c2));
+  return SGB_OK;
+}
+
+int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
+                            float* accumulation, float spars, int topk, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  OK(check_list(tensors, sizes, count));
+  const size_t n = total_of(sizes, count);
+  if (n > c->max_elems) return SGB_ERR_CAPACITY;
+  if (n == 0) return SGB_OK;
+  OK(sparse_init(c));
+  c->used = true;
+  const int W = c->world;
+  OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+  OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
+
+  size_t nnz_max = 0;
+  if (!topk) {
+    OK(sgb::sparse_threshold_count(c->send, accumulation, n, spars, c->nnz_dev, c->ws,
+                                   c->ws_bytes, c->c1));
+    NC(ncclAllGather(c->nnz_dev, c->nnz_dev + 1, 1, ncclInt, c->nccl, c->c1));
+    CU(cudaMemcpyAsync(c->nnz_host, c->nnz_dev + 1, sizeof(int) * W, cudaMemcpyDeviceToHost, c->c1));
+    CU(cudaEventRecord(c->ev_host, c->c1));
+    // the compaction runs while the host waits for the counts
+    OK(sgb::sparse_threshold_write_packed(c->send, accumulation, n, spars, c->pay_send, c->ws, c->c1));
+    CU(cudaEventSynchronize(c->ev_host));
+    for (int r = 0; r < W; ++r) {
+      if (c->nnz_host[r] < 0 || static_cast<size_t>(c->nnz_host[r]) > n) return SGB_ERR_STATE;
+      if (static_cast<size_t>(c->nnz_host[r]) > nnz_max) nnz_max = c->nnz_host[r];
+    }
+  } else {
+    nnz_max = static_cast<size_t>(sgb_topk_count(spars, n));
+    for (int r = 0; r < W; ++r) c->nnz_host[r] = static_cast<int>(nnz_max);
+    if (nnz_max)
+      OK(sgb_sparse_topk_f32(c->send, accumulation, c->sum, n, nnz_max, c->topk_mode, c->pay_send,
+                             reinterpret_cast<float*>(c->pay_send) + nnz_max, c->ws, c->ws_bytes,
+                             c->c1));
+  }
+
+  OK(edge(c->ev_c1, c->c1, c->s));
+  if (nnz_max)
+    NC(ncclAllGather(c->pay_send, c->pay_recv, 2 * nnz_max, ncclFloat, c->nccl, c->s));
+  OK(edge(c->ev_s, c->s, c->c2));
+  CU(cudaMemsetAsync(c->recv, 0, n * sizeof(float), c->c2));
+  for (int r = 0; r < W && nnz_max; ++r) {  // ranks in ascending order, as the reference
+    const int* seg = c->pay_recv + static_cast<size_t>(r) * 2 * nnz_max;
+    const size_t cnt = static_cast<size_t>(c->nnz_host[r]);
+    OK(sgb_scatter_add_f32(seg, reinterpret_cast<const float*>(seg) + cnt, cnt, nullptr, c->recv,
+                           n, c->c2));
+  }
+  OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c2));
+  return SGB_OK;
+}
+
+}  // extern "C"

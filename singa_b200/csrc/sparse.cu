@@ -1,0 +1,540 @@
+// Gradient sparsification kernels of the communicator:
+//   * threshold selection with residual correction and ORDER-PRESERVING
+//     compaction into a [1-based index | value] payload;
+//   * top-K selection by radix select on a 32-bit key (no sort), ties broken
+//     by lower index, with the same compaction;
+//   * scatter-add of a received payload into the dense sum buffer.
+//
+// Compaction is the classic three-step form (per-tile counts, one-CTA scan of
+// the tile counts, per-tile write at the scanned offsets).  It has no waits
+// between CTAs, so nothing can spin.  All index arithmetic that reaches the
+// payload is 1-based int32, the reference's wire format.
+#include "common.cuh"
+
+namespace sgb {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kVecPerThread = 4;                       // float4 vectors per thread
+constexpr int kTile = kBlock * kVecPerThread * 4;      // 4096 elements per CTA
+constexpr int kBins1 = 4096, kBins23 = 1024;           // 12 + 10 + 10 key bits
+
+// Device-resident selection state shared by the top-K passes.
+struct SelectState {
+  unsigned prefix;       // key bits decided so far (high bits), low bits zero
+  unsigned remaining;    // how many elements are still to be taken at/below prefix
+  unsigned threshold;    // final key T
+  unsigned quota;        // number of key == T elements to take (lowest indices)
+  int nnz;               // payload length (threshold mode: count; top-K: K)
+  int pad[3];
+};
+
+// Workspace layout (all 256-byte aligned segments).
+struct Workspace {
+  unsigned* tile_counts;   // tiles entries (threshold) or packed gt<<16|eq... see below
+  unsigned* tile_gt;       // tiles
+  unsigned* tile_eq;       // tiles
+  unsigned* hist;          // kBins1
+  SelectState* state;
+};
+inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+inline size_t tiles_of(size_t n) { return ceil_div(n, kTile); }
+inline size_t workspace_bytes(size_t n) {
+  return 3 * align256(tiles_of(n) * sizeof(unsigned)) + align256(kBins1 * sizeof(unsigned)) +
+         align256(sizeof(SelectState));
+}
+inline Workspace carve(void* ws, size_t n) {
+  char* p = static_cast<char*>(ws);
+  Workspace w;
+  const size_t t = align256(tiles_of(n) * sizeof(unsigned));
+  w.tile_counts = reinterpret_cast<unsigned*>(p); p += t;
+  w.tile_gt = reinterpret_cast<unsigned*>(p); p += t;
+  w.tile_eq = reinterpret_cast<unsigned*>(p); p += t;
+  w.hist = reinterpret_cast<unsigned*>(p); p += align256(kBins1 * sizeof(unsigned));
+  w.state = reinterpret_cast<SelectState*>(p);
+  return w;
+}
+
+// ------------------------------------------------------------- tile helpers
+// Element order inside a tile: vector v = r * kBlock + t (round r, thread t),
+// elements 4v .. 4v+3.  Loads are fully coalesced; ranks below follow this
+// order, which is ascending element index.
+__device__ __forceinline__ float load_sum(const float* __restrict__ g,
+                                          const float* __restrict__ acc, size_t i) {
+  return acc ? g[i] + acc[i] : g[i];
+}
+
+// Exclusive offsets, in element order, of per-thread per-round counts c[r].
+// Returns the tile total.  smem: 32 unsigned.
+__device__ __forceinline__ unsigned tile_exclusive(const unsigned (&c)[kVecPerThread],
+                                                   unsigned (&excl)[kVecPerThread],
+                                                   unsigned* smem) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;  // 8 warps
+  unsigned incl[kVecPerThread];
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    unsigned v = c[r];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    incl[r] = v;
+    if (lane == 31) smem[r * 8 + w] = v;  // warp total for (round r, warp w)
+  }
+  __syncthreads();
+  if (w == 0) {  // scan the 32 (round, warp) totals in element order
+    unsigned v = smem[lane];
+    unsigned s = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned u = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += u;
+    }
+    smem[lane] = s - v;          // exclusive
+    if (lane == 31) smem[32] = s;  // tile total
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) excl[r] = smem[r * 8 + w] + incl[r] - c[r];
+  const unsigned total = smem[32];
+  __syncthreads();
+  return total;
+}
+
+// ------------------------------------------------------------ threshold mode
+// kept value of element i: s = g (+ acc); |s| >= thr ? s : 0; sent iff != 0.
+__global__ void __launch_bounds__(kBlock)
+thr_count_kernel(const float* __restrict__ g, const float* __restrict__ acc, size_t n,
+                 float thr, unsigned* __restrict__ tile_counts) {
+  __shared__ unsigned sm[32];
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  unsigned cnt = 0;
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i + j < n) {
+        const float s = load_sum(g, acc, i + j);
+        cnt += (fabsf(s) >= thr && s != 0.0f) ? 1u : 0u;
+      }
+  }
+  // block total (integer, order irrelevant)
+  cnt = __reduce_add_sync(0xffffffffu, cnt);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned t = 0;
+    for (int k = 0; k < kBlock / 32; ++k) t += sm[k];
+    tile_counts[blockIdx.x] = t;
+  }
+}
+
+// One CTA: exclusive scan of up to 2^31/4096 tile counts (two arrays at once),
+// totals to the state.  In-place: counts become offsets.
+__global__ void __launch_bounds__(1024)
+scan_tiles_kernel(unsigned* __restrict__ a, unsigned* __restrict__ b, size_t tiles,
+                  SelectState* __restrict__ st, int write_nnz) {
+  __shared__ unsigned sa[32], sb[32];
+  __shared__ unsigned carry_a, carry_b;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (threadIdx.x == 0) { carry_a = 0; carry_b = 0; }
+  __syncthreads();
+  for (size_t base = 0; base < tiles; base += 1024) {
+    const size_t i = base + threadIdx.x;
+    const unsigned va = i < tiles ? a[i] : 0u;
+    const unsigned vb = (b && i < tiles) ? b[i] : 0u;
+    unsigned xa = va, xb = vb;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned ua = __shfl_up_sync(0xffffffffu, xa, o);
+      unsigned ub = __shfl_up_sync(0xffffffffu, xb, o);
+      if (lane >= o) { xa += ua; xb += ub; }
+    }
+    if (lane == 31) { sa[w] = xa; sb[w] = xb; }
+    __syncthreads();
+    if (w == 0) {
+      unsigned ta = sa[lane], tb = sb[lane];
+      unsigned ya = ta, yb = tb;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        unsigned ua = __shfl_up_sync(0xffffffffu, ya, o);
+        unsigned ub = __shfl_up_sync(0xffffffffu, yb, o);
+        if (lane >= o) { ya += ua; yb += ub; }
+      }
+      sa[lane] = ya - ta;
+      sb[lane] = yb - tb;
+    }
+    __syncthreads();
+    const unsigned ea = carry_a + sa[w] + xa - va;
+    const unsigned eb = carry_b + sb[w] + xb - vb;
+    if (i < tiles) {
+      a[i] = ea;
+      if (b) b[i] = eb;
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) {
+      carry_a = ea + va;
+      carry_b = eb + vb;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0 && write_nnz) st->nnz = static_cast<int>(carry_a);
+}
+
+__global__ void __launch_bounds__(kBlock)
+thr_write_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n, float thr,
+                 const unsigned* __restrict__ tile_offsets, int* __restrict__ idx_out,
+                 float* __restrict__ val_out, const SelectState* __restrict__ st) {
+  __shared__ unsigned sm[33];
+  // packed payload [idx(nnz) | val(nnz)]: values start right after the indices
+  if (!val_out) val_out = reinterpret_cast<float*>(idx_out) + st->nnz;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  float kept[kVecPerThread][4];
+  unsigned c[kVecPerThread], excl[kVecPerThread];
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    c[r] = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      kept[r][j] = 0.0f;
+      if (i + j < n) {
+        const float s = load_sum(g, acc, i + j);
+        const float k = fabsf(s) >= thr ? s : 0.0f;
+        if (acc) acc[i + j] = s - k;   // residual kept locally
+        kept[r][j] = k;
+        c[r] += k != 0.0f ? 1u : 0u;
+      }
+    }
+  }
+  tile_exclusive(c, excl, sm);
+  const unsigned tile_off = tile_offsets[blockIdx.x];
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    unsigned pos = tile_off + excl[r];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (kept[r][j] != 0.0f) {
+        idx_out[pos] = static_cast<int>(i + j + 1);
+        val_out[pos] = kept[r][j];
+        ++pos;
+      }
+  }
+}
+
+// ---------------------------------------------------------------- top-K mode
+// mode 0 "magnitude": key = bits of |s| (monotonic in |s| for non-NaN);
+// mode 1 "compat":    key = |(int)s|, the value the reference's comparator
+//                     actually compares (both operands truncated to int).
+__device__ __forceinline__ unsigned make_key(float s, int mode) {
+  if (mode == 0) return __float_as_uint(s) & 0x7fffffffu;
+  const int t = static_cast<int>(s);  // saturating truncation toward zero
+  return t < 0 ? 0u - static_cast<unsigned>(t) : static_cast<unsigned>(t);
+}
+
+// Pass p (0,1,2) histograms bits [20..31], [10..19], [0..9] of the keys whose
+// higher bits equal the prefix decided so far.  Pass 0 also materialises
+// s = g + acc into `sum` so later passes read 4 bytes per element.
+template <int PASS>
+__global__ void __launch_bounds__(kBlock)
+topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
+                 float* __restrict__ sum, size_t n, int mode,
+                 const SelectState* __restrict__ st, unsigned* __restrict__ hist) {
+  constexpr int kBins = PASS == 0 ? kBins1 : kBins23;
+  constexpr int kShift = PASS == 0 ? 20 : (PASS == 1 ? 10 : 0);
+  __shared__ unsigned sh[kBins];
+  for (int b = threadIdx.x; b < kBins; b += kBlock) sh[b] = 0;
+  __syncthreads();
+  const unsigned prefix = PASS == 0 ? 0u : st->prefix;
+  const unsigned hi_mask = PASS == 0 ? 0u : (PASS == 1 ? 0xfff00000u : 0xfffffc00u);
+  for (size_t tile = blockIdx.x; tile * kTile < n; tile += gridDim.x) {
+    const size_t base = tile * kTile;
+#pragma unroll
+    for (int r = 0; r < kVecPerThread; ++r) {
+      const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool in = i + j < n;
+        float s = 0.f;
+        if (in) {
+          if (PASS == 0) {
+            s = load_sum(g, acc, i + j);
+            sum[i + j] = s;
+          } else {
+            s = sum[i + j];
+          }
+        }
+        const unsigned key = make_key(s, mode);
+        const bool take = in && (key & hi_mask) == prefix;
+        const unsigned bin = (key >> kShift) & (kBins - 1);
+        // warp-aggregated increment: lanes with the same bin elect a leader
+        const unsigned active = __ballot_sync(0xffffffffu, take);
+        if (take) {
+          const unsigned peers = __match_any_sync(active, bin);
+          if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&sh[bin], __popc(peers));
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < kBins; b += kBlock)
+    if (sh[b]) atomicAdd(&hist[b], sh[b]);
+}
+
+// One CTA: walk the histogram from the highest bin down until `remaining`
+// elements are covered; fix that bin's bits into the prefix.  Clears the
+// histogram for the next pass.
+template <int PASS>
+__global__ void __launch_bounds__(1024)
+topk_pick_kernel(unsigned* __restrict__ hist, SelectState* __restrict__ st, unsigned k_total) {
+  constexpr int kBins = PASS == 0 ? kBins1 : kBins23;
+  constexpr int kShift = PASS == 0 ? 20 : (PASS == 1 ? 10 : 0);
+  __shared__ unsigned sh[kBins];
+  for (int b = threadIdx.x; b < kBins; b += 1024) {
+    sh[b] = hist[b];
+    hist[b] = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned remaining = PASS == 0 ? k_total : st->remaining;
+    unsigned prefix = PASS == 0 ? 0u : st->prefix;
+    int b = kBins - 1;
+    for (; b > 0; --b) {
+      if (sh[b] >= remaining) break;
+      remaining -= sh[b];
+    }
+    // b == 0 falls through: whatever is left comes from the lowest bin
+    prefix |= static_cast<unsigned>(b) << kShift;
+    st->prefix = prefix;
+    st->remaining = remaining;
+    if (PASS == 2) {
+      st->threshold = prefix;
+      st->quota = remaining;
+      st->nnz = static_cast<int>(k_total);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+topk_count_kernel(const float* __restrict__ sum, size_t n, int mode,
+                  const SelectState* __restrict__ st, unsigned* __restrict__ tile_gt,
+                  unsigned* __restrict__ tile_eq) {
+  __shared__ unsigned sg[8], se[8];
+  const unsigned T = st->threshold;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  unsigned gt = 0, eq = 0;
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i + j < n) {
+        const unsigned key = make_key(sum[i + j], mode);
+        gt += key > T;
+        eq += key == T;
+      }
+  }
+  gt = __reduce_add_sync(0xffffffffu, gt);
+  eq = __reduce_add_sync(0xffffffffu, eq);
+  if ((threadIdx.x & 31) == 0) { sg[threadIdx.x >> 5] = gt; se[threadIdx.x >> 5] = eq; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned a = 0, b = 0;
+    for (int k = 0; k < 8; ++k) { a += sg[k]; b += se[k]; }
+    tile_gt[blockIdx.x] = a;
+    tile_eq[blockIdx.x] = b;
+  }
+}
+
+// Selected: key > T, or key == T and fewer than `quota` equal keys precede it.
+// Payload position = (#greater before) + min(#equal before, quota).
+__global__ void __launch_bounds__(kBlock)
+topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t n, int mode,
+                  const SelectState* __restrict__ st, const unsigned* __restrict__ gt_off,
+                  const unsigned* __restrict__ eq_off, int* __restrict__ idx_out,
+                  float* __restrict__ val_out) {
+  __shared__ unsigned sm[33];
+  const unsigned T = st->threshold, quota = st->quota;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  float s[kVecPerThread][4];
+  unsigned cg[kVecPerThread], ce[kVecPerThread], eg[kVecPerThread], ee[kVecPerThread];
+  unsigned char flag[kVecPerThread][4];  // 0 none, 1 greater, 2 equal
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    cg[r] = 0; ce[r] = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      flag[r][j] = 0;
+      s[r][j] = 0.f;
+      if (i + j < n) {
+        s[r][j] = sum[i + j];
+        const unsigned key = make_key(s[r][j], mode);
+        if (key > T) { flag[r][j] = 1; ++cg[r]; }
+        else if (key == T) { flag[r][j] = 2; ++ce[r]; }
+      }
+    }
+  }
+  tile_exclusive(cg, eg, sm);
+  tile_exclusive(ce, ee, sm);
+  const unsigned g0 = gt_off[blockIdx.x], e0 = eq_off[blockIdx.x];
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    unsigned ng = g0 + eg[r], ne = e0 + ee[r];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      bool sel = false;
+      if (flag[r][j] == 1) {
+        sel = true;
+      } else if (flag[r][j] == 2) {
+        sel = ne < quota;
+      }
+      if (sel) {
+        const unsigned pos = ng + (ne < quota ? ne : quota);
+        idx_out[pos] = static_cast<int>(i + j + 1);
+        val_out[pos] = s[r][j];
+      }
+      if (acc && i + j < n) acc[i + j] = sel ? 0.0f : s[r][j];  // s - s == 0 when sent
+      if (flag[r][j] == 1) ++ng;
+      if (flag[r][j] == 2) ++ne;
+    }
+  }
+}
+
+// ------------------------------------------------------------- scatter-add
+// dst[idx-1] += val for one rank's payload; the count lives on the device when
+// count_dev != NULL (entry `rank_slot`), else `count` is used.  Index 0 marks
+// padding and is skipped; indices are unique within a payload, so there are
+// no conflicting updates inside one launch.
+__global__ void __launch_bounds__(kBlock)
+scatter_add_kernel(const int* __restrict__ idx, const float* __restrict__ val, size_t count,
+                   const int* __restrict__ count_dev, float* __restrict__ dst, size_t n) {
+  const size_t m = count_dev ? static_cast<size_t>(*count_dev) : count;
+  for (size_t j = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; j < m;
+       j += static_cast<size_t>(gridDim.x) * kBlock) {
+    const int i = idx[j];
+    if (i > 0 && static_cast<size_t>(i) <= n) dst[i - 1] += val[j];
+  }
+}
+
+int check_common(const float* g, size_t n, const void* idx_out, const void* val_out, void* ws,
+                 size_t ws_bytes) {
+  if (!g || !idx_out || !val_out) return SGB_ERR_NULL;
+  if (n > 0x7fffffffu) return SGB_ERR_SIZE;  // 1-based int32 indices on the wire
+  if (!ws || ws_bytes < workspace_bytes(n) || (reinterpret_cast<uintptr_t>(ws) & 255u))
+    return SGB_ERR_WORKSPACE;
+  return SGB_OK;
+}
+
+}  // namespace
+
+// ---- two-phase form used by the communicator (declared in sparse.cuh) ------
+int sparse_threshold_count(const float* g, const float* acc, size_t n, float thr, int* nnz_dev,
+                           void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (n == 0) {
+    cudaError_t e = cudaMemsetAsync(nnz_dev, 0, sizeof(int), s);
+    return e == cudaSuccess ? SGB_OK : note_cuda_error(e);
+  }
+  if (n > 0x7fffffffu) return SGB_ERR_SIZE;
+  if (!ws || ws_bytes < workspace_bytes(n) || (reinterpret_cast<uintptr_t>(ws) & 255u))
+    return SGB_ERR_WORKSPACE;
+  Workspace w = carve(ws, n);
+  const unsigned tiles = static_cast<unsigned>(tiles_of(n));
+  thr_count_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts);
+  scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_counts, nullptr, tiles, w.state, 1);
+  cudaError_t e = cudaMemcpyAsync(nnz_dev, &w.state->nnz, sizeof(int), cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  return launch_status();
+}
+
+int sparse_threshold_write_packed(const float* g, float* acc, size_t n, float thr, int* payload,
+                                  void* ws, cudaStream_t s) {
+  if (n == 0) return SGB_OK;
+  Workspace w = carve(ws, n);
+  const unsigned tiles = static_cast<unsigned>(tiles_of(n));
+  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, payload, nullptr, w.state);
+  return launch_status();
+}
+
+}  // namespace sgb
+
+using namespace sgb;
+
+extern "C" {
+
+size_t sgb_sparse_workspace_bytes(size_t n) { return n ? workspace_bytes(n) : 256; }
+
+int sgb_topk_count(float ratio, size_t n) {
+  // (int)ceil(threshold * num) evaluated in fp32, as the reference does
+  // (float * size_t -> float).
+  const float prod = ratio * static_cast<float>(n);
+  float c = ceilf(prod);
+  if (c < 0.f) c = 0.f;
+  if (c > static_cast<float>(n)) return static_cast<int>(n);
+  return static_cast<int>(c);
+}
+
+int sgb_sparse_threshold_f32(const float* g, float* acc, size_t n, float thr, int32_t* idx_out,
+                             float* val_out, int32_t* nnz_dev, void* ws, size_t ws_bytes,
+                             void* stream) {
+  if (!nnz_dev) return SGB_ERR_NULL;
+  cudaStream_t s = as_stream(stream);
+  if (n == 0) {
+    cudaError_t e = cudaMemsetAsync(nnz_dev, 0, sizeof(int), s);
+    return e == cudaSuccess ? SGB_OK : note_cuda_error(e);
+  }
+  int st = check_common(g, n, idx_out, val_out, ws, ws_bytes);
+  if (st != SGB_OK) return st;
+  Workspace w = carve(ws, n);
+  const unsigned tiles = static_cast<unsigned>(tiles_of(n));
+  thr_count_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts);
+  scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_counts, nullptr, tiles, w.state, 1);
+  cudaError_t e = cudaMemcpyAsync(nnz_dev, &w.state->nnz, sizeof(int), cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, idx_out, val_out, w.state);
+  return launch_status();
+}
+
+int sgb_sparse_topk_f32(const float* g, float* acc, float* sum_scratch, size_t n, size_t k,
+                        int mode, int32_t* idx_out, float* val_out, void* ws, size_t ws_bytes,
+                        void* stream) {
+  if (n == 0 || k == 0) return SGB_OK;
+  if (mode != 0 && mode != 1) return SGB_ERR_UNSUPPORTED;
+  if (!sum_scratch) return SGB_ERR_NULL;
+  int st = check_common(g, n, idx_out, val_out, ws, ws_bytes);
+  if (st != SGB_OK) return st;
+  if (k > n) k = n;
+  cudaStream_t s = as_stream(stream);
+  Workspace w = carve(ws, n);
+  const unsigned tiles = static_cast<unsigned>(tiles_of(n));
+  const unsigned hgrid = capped_grid(tiles, 1, 8);
+  cudaError_t e = cudaMemsetAsync(w.hist, 0, kBins1 * sizeof(unsigned), s);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  topk_hist_kernel<0><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist);
+  topk_pick_kernel<0><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
+  topk_hist_kernel<1><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist);
+  topk_pick_kernel<1><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
+  topk_hist_kernel<2><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist);
+  topk_pick_kernel<2><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
+  topk_count_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, n, mode, w.state, w.tile_gt, w.tile_eq);
+  scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_gt, w.tile_eq, tiles, w.state, 0);
+  topk_write_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, acc, n, mode, w.state, w.tile_gt,
+                                             w.tile_eq, idx_out, val_out);
+  return launch_status();
+}
+
+int sgb_scatter_add_f32(const int32_t* idx, const float* val, size_t count,
+                        const int32_t* count_dev, float* dst, size_t n, void* stream) {
+  if (!count_dev && count == 0) return SGB_OK;
+  if (!idx || !val || !dst) return SGB_ERR_NULL;
+  const size_t guess = count_dev ? (count ? count : n) : count;
+  unsigned grid = capped_grid(guess, kBlock, 8);
+  scatter_add_kernel<<<grid, kBlock, 0, as_stream(stream)>>>(idx, val, count, count_dev, dst, n);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,260 @@
+"""The ResNet-50 backward + gradient-sync + update hot path as a list of ops.
+
+This is the workload of the headline benchmark: the sequence of backward
+calls that the reference's Python autograd issues for its ResNet-50
+(examples/cnn/model/resnet.py: Bottleneck blocks [3, 4, 6, 3], 7x7 stem,
+3x3/2 max pool, 7x7 average pool, 1000-way linear) at batch 32/GPU, 224x224
+input, followed by DistOpt's bucketed gradient synchronisation and the SGD
+update of the 161 parameter tensors.
+
+The Conv/Linear contractions are NOT part of this path (they stay on
+cuDNN/cuBLAS in the reference), so the gradients they would produce are
+stand-in tensors with fixed seeded content: the activation gradient a
+conv-backward-data call would write, and the weight gradient a
+conv-backward-filter call would write.  Everything else - ReLU backward,
+batch-norm backward, the residual joins, max/avg-pool backward,
+softmax-cross-entropy forward/backward, the bias-gradient reduction, the
+gradient synchronisation and the optimizer - is computed.
+
+``build_plan`` is pure python (no device): it returns tensor specs and an op
+list that an executor (GPU: ``HotPathGPU`` below; CPU checker: the oracle
+executor in bench.py/tests) walks in order.
+"""
+from collections import namedtuple
+
+Tensor = namedtuple("Tensor", "name shape kind")
+# kind: "act"   stored forward activation (seeded content)
+#       "stat"  per-channel BN statistic / scale
+#       "syn"   stand-in for a contraction's output gradient (seeded content)
+#       "grad"  activation gradient produced on the path (scratch)
+#       "param" parameter, "pgrad" parameter gradient, "label", "misc"
+
+Op = namedtuple("Op", "kind args")
+
+
+def conv_out(h, k, stride, pad):
+    return (h + 2 * pad - k) // stride + 1
+
+
+def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4, 6, 3)):
+    """Returns dict(tensors, ops, params, grad_order, stats).
+
+    fused=False: one op per reference call (ReLUBackward, GpuBatchNormBackward,
+    ``+=`` join, ...).  fused=True: the join is folded into the following
+    ReLUBackward and ReLUBackward into the following GpuBatchNormBackward
+    (same results, fewer passes over memory)."""
+    T, ops, params = {}, [], []
+    B = batch
+
+    def tensor(name, shape, kind):
+        assert name not in T, name
+        T[name] = Tensor(name, tuple(shape), kind)
+        return name
+
+    def param(name, shape):
+        tensor(name, shape, "param")
+        tensor("d:" + name, shape, "pgrad")
+        params.append(name)
+        return name
+
+    def bn(name, c, h):
+        param(name + ".scale", (c,))
+        param(name + ".bias", (c,))
+        tensor(name + ".x", (B, c, h, h), "act")          # conv output = BN input
+        tensor(name + ".mean", (c,), "stat")
+        tensor(name + ".invstd", (c,), "stat")
+
+    # ---------------------------------------------------------------- forward walk
+    fwd = []          # structural records used to emit the backward ops
+    h = conv_out(image, 7, 2, 3)
+    param("conv1.W", (64, 3, 7, 7))
+    bn("bn1", 64, h)
+    tensor("relu.x", (B, 64, h, h), "act")                 # BN output = ReLU input
+    hp = conv_out(h, 3, 2, 1)
+    tensor("maxpool.x", (B, 64, h, h), "act")              # ReLU output
+    tensor("maxpool.y", (B, 64, hp, hp), "act")
+    stem = dict(h=h, hp=hp)
+    inpl, h = 64, hp
+    for li, (planes, nblk, stride) in enumerate(zip((64, 128, 256, 512), blocks, (1, 2, 2, 2)), 1):
+        for b in range(nblk):
+            s = stride if b == 0 else 1
+            n = "layer%d.%d" % (li, b)
+            hin = h
+            h1 = conv_out(hin, 1, 1, 0)
+            param(n + ".conv1.W", (planes, inpl, 1, 1)); bn(n + ".bn1", planes, h1)
+            tensor(n + ".relu1.x", (B, planes, h1, h1), "act")
+            h2 = conv_out(h1, 3, s, 1)
+            param(n + ".conv2.W", (planes, planes, 3, 3)); bn(n + ".bn2", planes, h2)
+            tensor(n + ".relu2.x", (B, planes, h2, h2), "act")
+            h3 = conv_out(h2, 1, 1, 0)
+            param(n + ".conv3.W", (planes * 4, planes, 1, 1)); bn(n + ".bn3", planes * 4, h3)
+            down = b == 0
+            if down:
+                param(n + ".down.conv.W", (planes * 4, inpl, 1, 1)); bn(n + ".down.bn", planes * 4, h3)
+            tensor(n + ".relu3.x", (B, planes * 4, h3, h3), "act")   # add output
+            fwd.append(dict(name=n, cin=inpl, planes=planes, hin=hin, h1=h1, h2=h2, h3=h3, down=down))
+            inpl, h = planes * 4, h3
+    param("fc.W", (inpl, num_classes))
+    param("fc.b", (num_classes,))
+    tensor("labels", (B,), "label")
+    tensor("logits", (B, num_classes), "act")
+    tensor("prob", (B, num_classes), "grad")
+    tensor("loss_vec", (B,), "grad")
+    tensor("loss", (1,), "grad")
+    tensor("dlogits", (B, num_classes), "grad")
+    tensor("avgpool.dy", (B, inpl, 1, 1), "syn")           # from the fc Matmul backward (cuBLAS)
+    tensor("d:fc.W.syn", (1,), "misc")
+
+    # ---------------------------------------------------------------- backward ops
+    grad_order = []
+
+    def ready(pname):
+        grad_order.append(pname)
+        ops.append(Op("grad_ready", dict(param=pname)))
+
+    def syn(name, shape):
+        return tensor(name, shape, "syn")
+
+    def scratch(name, shape):
+        return tensor(name, shape, "grad")
+
+    # head: loss forward, softmax-CE backward (+1/N), bias gradient, avg-pool backward
+    ops.append(Op("softmax", dict(x="logits", y="prob")))
+    ops.append(Op("ce_fwd", dict(p="prob", t="labels", loss="loss_vec")))
+    ops.append(Op("sum_all", dict(x="loss_vec", out="loss")))
+    if fused:
+        ops.append(Op("ce_grad", dict(p="prob", t="labels", scale=1.0 / B, grad="dlogits")))
+    else:
+        ops.append(Op("ce_bwd", dict(p="prob", t="labels", grad="dlogits")))
+        ops.append(Op("scale", dict(x="dlogits", c=1.0 / B)))
+    ops.append(Op("sum_rows", dict(M="dlogits", v="d:fc.b")))
+    ready("fc.b")
+    ready("fc.W")                                          # cuBLAS weight gradient: stand-in content
+    hlast = fwd[-1]["h3"]
+    dcur = scratch("avgpool.dx", (B, inpl, hlast, hlast))
+    ops.append(Op("avgpool_bwd", dict(dy="avgpool.dy", dx=dcur, kernel=(hlast, hlast), stride=(1, 1), pad=(0, 0))))
+
+    # dcur = gradient w.r.t. the output of the current block (after relu3)
+    pending_join = None    # (a, b): gradient is a + b, not yet materialised (fused mode)
+    for blk in reversed(fwd):
+        n, p4, pl = blk["name"], blk["planes"] * 4, blk["planes"]
+        shape3 = (B, p4, blk["h3"], blk["h3"])
+        d_add = scratch(n + ".d_add", shape3)
+        if pending_join is not None:
+            ops.append(Op("add_relu_bwd", dict(dy_a=pending_join[0], dy_b=pending_join[1], x=n + ".relu3.x", dx=d_add)))
+            pending_join = None
+        else:
+            ops.append(Op("relu_bwd", dict(dy=dcur, x=n + ".relu3.x", dx=d_add)))
+
+        def bn_bwd(bnname, dy, relu_x=None):
+            c, hh = T[bnname + ".x"].shape[1], T[bnname + ".x"].shape[2]
+            dx = scratch(bnname + ".dx", (B, c, hh, hh))
+            args = dict(dy=dy, x=bnname + ".x", scale=bnname + ".scale", mean=bnname + ".mean",
+                        invstd=bnname + ".invstd", dx=dx, dscale="d:" + bnname + ".scale",
+                        dbias="d:" + bnname + ".bias")
+            if relu_x is not None and fused:
+                ops.append(Op("bn_relu_bwd", dict(args, relu_x=relu_x)))
+            else:
+                if relu_x is not None:
+                    masked = scratch(bnname + ".dy_masked", (B, c, hh, hh))
+                    ops.append(Op("relu_bwd", dict(dy=dy, x=relu_x, dx=masked)))
+                    args["dy"] = masked
+                ops.append(Op("bn_bwd", args))
+            ready(bnname + ".bias")
+            ready(bnname + ".scale")
+            return dx
+
+        # main branch: bn3 <- conv3 <- relu2 <- bn2 <- conv2 <- relu1 <- bn1 <- conv1
+        bn_bwd(n + ".bn3", d_add)
+        ready(n + ".conv3.W")
+        g2 = syn(n + ".conv3.dgrad", (B, pl, blk["h2"], blk["h2"]))      # cudnn bwd-data output
+        bn_bwd(n + ".bn2", g2, relu_x=n + ".relu2.x")
+        ready(n + ".conv2.W")
+        g1 = syn(n + ".conv2.dgrad", (B, pl, blk["h1"], blk["h1"]))
+        bn_bwd(n + ".bn1", g1, relu_x=n + ".relu1.x")
+        ready(n + ".conv1.W")
+        dx_main = syn(n + ".conv1.dgrad", (B, blk["cin"], blk["hin"], blk["hin"]))
+        if blk["down"]:
+            bn_bwd(n + ".down.bn", d_add)
+            ready(n + ".down.conv.W")
+            dx_res = syn(n + ".down.dgrad", (B, blk["cin"], blk["hin"], blk["hin"]))
+        else:
+            dx_res = d_add                                 # identity shortcut
+        # join of the two gradients reaching the block input: dxs_[y_idx] += dx
+        if fused and blk is not fwd[0]:
+            pending_join = (dx_main, dx_res)
+            dcur = None
+        else:
+            joined = scratch(n + ".d_in", (B, blk["cin"], blk["hin"], blk["hin"]))
+            ops.append(Op("add_out", dict(a=dx_main, b=dx_res, out=joined)))
+            dcur = joined
+
+    # stem: maxpool <- relu <- bn1 <- conv1
+    d_pool = scratch("maxpool.dx", T["maxpool.x"].shape)
+    ops.append(Op("maxpool_bwd", dict(x="maxpool.x", y="maxpool.y", dy=dcur, dx=d_pool,
+                                      kernel=(3, 3), stride=(2, 2), pad=(1, 1))))
+    c, hh = 64, stem["h"]
+    dx = scratch("bn1.dx", (B, c, hh, hh))
+    bnargs = dict(dy=d_pool, x="bn1.x", scale="bn1.scale", mean="bn1.mean", invstd="bn1.invstd",
+                  dx=dx, dscale="d:bn1.scale", dbias="d:bn1.bias")
+    if fused:
+        ops.append(Op("bn_relu_bwd", dict(bnargs, relu_x="relu.x")))
+    else:
+        masked = scratch("bn1.dy_masked", (B, c, hh, hh))
+        ops.append(Op("relu_bwd", dict(dy=d_pool, x="relu.x", dx=masked)))
+        ops.append(Op("bn_bwd", dict(bnargs, dy=masked)))
+    ready("bn1.bias")
+    ready("bn1.scale")
+    ready("conv1.W")
+    ops.append(Op("sync_and_update", dict()))
+    del T["d:fc.W.syn"]
+    return dict(tensors=T, ops=ops, params=params, grad_order=grad_order, batch=B)
+
+
+def numel(shape):
+    n = 1
+    for s in shape:
+        n *= s
+    return n
+
+
+def algorithmic_bytes(plan, world=1):
+    """Bytes each op must move at minimum (fp32), by op family - the figures the
+    roofline fraction is computed on.  BN backward counts 12 B/element (read x,
+    read dy, write dx) + 20 B/channel whatever the implementation moves; the
+    fused forms add 4 B/element for the ReLU mask / second addend."""
+    T = plan["tensors"]
+    out = {}
+
+    def add(k, v):
+        out[k] = out.get(k, 0) + v
+
+    for op in plan["ops"]:
+        a = op.args
+        if op.kind == "relu_bwd":
+            add("relu_bwd", 12 * numel(T[a["x"]].shape))
+        elif op.kind == "add_relu_bwd":
+            add("add_relu_bwd", 16 * numel(T[a["x"]].shape))
+        elif op.kind == "add_out":
+            add("join", 12 * numel(T[a["out"]].shape))
+        elif op.kind == "bn_bwd":
+            s = T[a["x"]].shape
+            add("bn_bwd", 12 * numel(s) + 20 * s[1])
+        elif op.kind == "bn_relu_bwd":
+            s = T[a["x"]].shape
+            add("bn_relu_bwd", 16 * numel(s) + 20 * s[1])
+        elif op.kind == "maxpool_bwd":
+            add("maxpool_bwd", 4 * (2 * numel(T[a["x"]].shape) + 2 * numel(T[a["y"]].shape)))
+        elif op.kind == "avgpool_bwd":
+            add("avgpool_bwd", 4 * (numel(T[a["dy"]].shape) + numel(T[a["dx"]].shape)))
+        elif op.kind in ("ce_bwd", "ce_grad"):
+            add("softmax_ce", 8 * numel(T[a["p"]].shape))
+        elif op.kind == "softmax":
+            add("softmax_ce", 8 * numel(T[a["x"]].shape))
+        elif op.kind == "scale":
+            add("softmax_ce", 8 * numel(T[a["x"]].shape))
+        elif op.kind == "sum_rows":
+            add("bias_grad", 4 * numel(T[a["M"]].shape))
+    nparam = sum(numel(T[p].shape) for p in plan["params"])
+    add("sgd", 20 * nparam)
+    return out, nparam

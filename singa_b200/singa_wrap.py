@@ -179,3 +179,304 @@ def Transform(t_storage, shape, stride):
     _lib.call("sgb_strided_copy_f32", _p(t_storage), _p(out), n, len(shape),
               C.cast(sh, C.c_void_p), C.cast(st, C.c_void_p), _stream())
     return out
+
+
+# ------------------------------------------------------------------ workspace
+_WS = {}
+
+
+def _workspace(device, nbytes):
+    """A per-device scratch buffer owned by the host layer (the C ABI never
+    allocates).  Grows monotonically; 256-byte aligned by the torch allocator."""
+    buf = _WS.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _WS[device] = buf
+    return buf
+
+
+def _ws_args(device, nbytes):
+    if nbytes == 0:
+        return None, 0
+    buf = _workspace(device, nbytes)
+    return buf.data_ptr(), buf.numel()
+
+
+# ------------------------------------------------------------------ reductions
+def SumRows(M, v=None):
+    """core_tensor.i:380 ``SumRows(M, v)``: v[c] = sum_r M[r, c]."""
+    _chk(M)
+    nrow, ncol = M.shape
+    v = torch.empty(ncol, dtype=_F32, device=M.device) if v is None else v
+    need = _lib.lib().sgb_sum_rows_workspace_bytes(nrow, ncol)
+    ws, wsn = _ws_args(M.device, need)
+    _lib.call("sgb_sum_rows_f32", _p(M), _p(v), nrow, ncol, ws, wsn, _stream())
+    return v
+
+
+def SumColumns(M, v=None):
+    """core_tensor.i:379 ``SumColumns(M, v)``: v[r] = sum_c M[r, c]."""
+    _chk(M)
+    nrow, ncol = M.shape
+    v = torch.empty(nrow, dtype=_F32, device=M.device) if v is None else v
+    _lib.call("sgb_sum_columns_f32", _p(M), _p(v), nrow, ncol, _stream())
+    return v
+
+
+def Sum(t, axis):
+    """core_tensor.i:223 ``Tensor Sum(t, axis)`` (tensor.cc:1229-1240)."""
+    if axis == 0:
+        return SumRows(t)
+    assert axis == 1, "Not support Sum over axis = %d" % axis
+    return SumColumns(t)
+
+
+def SumAll(t):
+    """core_tensor.i:226 ``Tensor SumAll(t)`` -> one-element device tensor."""
+    _chk(t)
+    out = torch.empty(1, dtype=_F32, device=t.device)
+    need = _lib.lib().sgb_sum_all_workspace_bytes(t.numel())
+    ws, wsn = _ws_args(t.device, need)
+    _lib.call("sgb_sum_all_f32", _p(t), _p(out), t.numel(), ws, wsn, _stream())
+    return out
+
+
+def RowMax(t):
+    _chk(t)
+    v = torch.empty(t.shape[0], dtype=_F32, device=t.device)
+    _lib.call("sgb_row_max_f32", _p(t), _p(v), t.shape[0], t.shape[1], _stream())
+    return v
+
+
+def GpuConvBackwardb(dy, b=None, cch=None):
+    """model_operation.i:148: db[c] = sum_{n,h,w} dy (NCHW)."""
+    _chk(dy)
+    n, c = dy.shape[0], dy.shape[1]
+    hw = dy.numel() // (n * c)
+    db = torch.empty(c, dtype=_F32, device=dy.device)
+    need = _lib.lib().sgb_conv_bias_backward_workspace_bytes(n, c, hw)
+    ws, wsn = _ws_args(dy.device, need)
+    _lib.call("sgb_conv_bias_backward_f32", _p(dy), _p(db), n, c, hw, ws, wsn, _stream())
+    return db
+
+
+# ------------------------------------------------------ softmax / cross entropy
+def SoftMax(t, axis=None):
+    """core_tensor.i:229-230.  ``axis`` reshapes to 2-D as tensor.cc:942-972
+    does: rows = prod(shape[:axis]), columns = the rest."""
+    _chk(t)
+    if axis is None:
+        nrow = t.shape[0] if t.dim() == 2 else 1
+    else:
+        axis = axis % t.dim()
+        nrow = 1
+        for s in t.shape[:axis]:
+            nrow *= s
+    y = torch.empty_like(t)
+    _lib.call("sgb_softmax_rows_f32", _p(t), _p(y), nrow, t.numel() // max(nrow, 1), _stream())
+    return y
+
+
+def _ce_dims(p, t):
+    batch = p.shape[0] if p.dim() == 2 else 1
+    dim = p.numel() // batch
+    assert t.dtype == _I32, "targets are int32 (kInt) tensors"
+    return batch, dim, int(t.numel() == batch)
+
+
+def CrossEntropyFwd(p, t):
+    """core_tensor.i:387."""
+    _chk(p, t)
+    batch, dim, it = _ce_dims(p, t)
+    loss = torch.empty(batch, dtype=_F32, device=p.device)
+    _lib.call("sgb_cross_entropy_f32", it, batch, dim, _p(p), _p(t), _p(loss), _stream())
+    return loss
+
+
+def SoftmaxCrossEntropyBwd(p, t):
+    """core_tensor.i:388: returns p - target in a new tensor."""
+    _chk(p, t)
+    batch, dim, it = _ce_dims(p, t)
+    g = torch.empty_like(p)
+    _lib.call("sgb_softmax_cross_entropy_bwd_f32", it, batch, dim, _p(p), _p(t), _p(g), _stream())
+    return g
+
+
+def SoftmaxCrossEntropyGrad(p, t, scale):
+    """Fused SoftmaxCrossEntropyBwd + ``dx *= scale`` (autograd.py:1319-1322
+    with scale = float32(1/N))."""
+    _chk(p, t)
+    batch, dim, it = _ce_dims(p, t)
+    g = torch.empty_like(p)
+    _lib.call("sgb_softmax_cross_entropy_grad_f32", it, batch, dim, _p(p), _p(t),
+              float(scale), _p(g), _stream())
+    return g
+
+
+# ------------------------------------------------------------ operation handles
+class CudnnBatchNormHandle(object):
+    """Shape record with the fields of singa's BatchNormHandle
+    (src/model/operation/batchnorm.h:38-60); no cuDNN descriptors are needed."""
+
+    def __init__(self, momentum, x):
+        self.factor = momentum
+        self.batchsize = x.shape[0]
+        self.channels = x.shape[1]
+        self.is_2d = x.dim() == 2
+        self.height = 1 if self.is_2d else x.shape[2]
+        self.width = 1 if self.is_2d else x.shape[3]
+
+
+def GpuBatchNormBackward(cbnh, dy, x, bnScale, mean, var):
+    """model_operation.i:165: returns [dx, dscale, dbias].  ``var`` is the
+    saved INVERSE standard deviation produced by the forward pass, as in the
+    reference (batchnorm.cc:314-321, 390-396)."""
+    _chk(dy, x, bnScale, mean, var)
+    n, c, hw = cbnh.batchsize, cbnh.channels, cbnh.height * cbnh.width
+    dx = torch.empty_like(dy)
+    ds = torch.empty_like(bnScale)
+    db = torch.empty_like(bnScale)
+    need = _lib.lib().sgb_bn_backward_workspace_bytes(n, c, hw)
+    ws, wsn = _ws_args(dy.device, need)
+    _lib.call("sgb_bn_backward_f32", _p(x), _p(dy), _p(bnScale), _p(mean), _p(var),
+              _p(dx), _p(ds), _p(db), n, c, hw, ws, wsn, _stream())
+    return [dx, ds, db]
+
+
+def GpuBatchNormReLUBackward(cbnh, dy, relu_in, x, bnScale, mean, var):
+    """ReLUBackward(dy, relu_in) followed by GpuBatchNormBackward, one pass."""
+    _chk(dy, relu_in, x, bnScale, mean, var)
+    n, c, hw = cbnh.batchsize, cbnh.channels, cbnh.height * cbnh.width
+    dx = torch.empty_like(dy)
+    ds = torch.empty_like(bnScale)
+    db = torch.empty_like(bnScale)
+    need = _lib.lib().sgb_bn_backward_workspace_bytes(n, c, hw)
+    ws, wsn = _ws_args(dy.device, need)
+    _lib.call("sgb_bn_relu_backward_f32", _p(x), _p(dy), _p(relu_in), _p(bnScale), _p(mean),
+              _p(var), _p(dx), _p(ds), _p(db), n, c, hw, ws, wsn, _stream())
+    return [dx, ds, db]
+
+
+class CudnnPoolingHandle(object):
+    """Fields of singa's PoolingHandle (src/model/operation/pooling.h:41-78,
+    pooling.cc:27-52)."""
+
+    def __init__(self, x, kernel_size, stride, padding, is_max=True):
+        self.kernel_h, self.kernel_w = kernel_size
+        self.stride_h, self.stride_w = stride
+        self.pad_h, self.pad_w = padding
+        self.batchsize, self.channels, self.height, self.width = x.shape
+        self.pooled_height = 1
+        if self.stride_h > 0:
+            self.pooled_height = (self.height + 2 * self.pad_h - self.kernel_h) // self.stride_h + 1
+        self.pooled_width = (self.width + 2 * self.pad_w - self.kernel_w) // self.stride_w + 1
+        self.is_max_pooling = is_max
+
+    def _geom(self):
+        return (self.batchsize, self.channels, self.height, self.width, self.kernel_h,
+                self.kernel_w, self.pad_h, self.pad_w, self.stride_h, self.stride_w)
+
+
+def GpuPoolingForward(cph, x):
+    """model_operation.i:189."""
+    _chk(x)
+    y = torch.empty((cph.batchsize, cph.channels, cph.pooled_height, cph.pooled_width),
+                    dtype=_F32, device=x.device)
+    name = "sgb_maxpool_forward_f32" if cph.is_max_pooling else "sgb_avgpool_forward_f32"
+    _lib.call(name, _p(x), _p(y), *cph._geom(), _stream())
+    return y
+
+
+def GpuPoolingBackward(cph, dy, x, y):
+    """model_operation.i:191."""
+    _chk(dy, x, y)
+    dx = torch.empty_like(x)
+    if cph.is_max_pooling:
+        _lib.call("sgb_maxpool_backward_f32", _p(x), _p(y), _p(dy), _p(dx), *cph._geom(), _stream())
+    else:
+        _lib.call("sgb_avgpool_backward_f32", _p(dy), _p(dx), *cph._geom(), _stream())
+    return dx
+
+
+# ------------------------------------------------------------- multi-tensor ops
+def _ptr_table(tensors):
+    import ctypes as C
+    n = len(tensors)
+    ptrs = (C.c_void_p * n)(*[t.data_ptr() for t in tensors])
+    sizes = (C.c_size_t * n)(*[t.numel() for t in tensors])
+    return ptrs, sizes, n
+
+
+def sgd_update_multi(params, grads, moments, lr, momentum=0.0, dampening=0.0, weight_decay=0.0,
+                     nesterov=False, grad_scale=1.0):
+    """One launch group for SGD.apply over a list of parameter tensors."""
+    _chk(*params)
+    _chk(*grads)
+    pp, sizes, n = _ptr_table(params)
+    gp, _, _ = _ptr_table(grads)
+    mp = None
+    if momentum != 0:
+        _chk(*moments)
+        mp, _, _ = _ptr_table(moments)
+    _lib.call("sgb_sgd_update_multi_f32", pp, gp, mp, sizes, n, float(lr), float(momentum),
+              float(dampening), float(weight_decay), int(nesterov), float(grad_scale), _stream())
+
+
+def pack(tensors, flat, offset=0):
+    _chk(flat, *tensors)
+    ptrs, sizes, n = _ptr_table(tensors)
+    name = "sgb_pack_f32" if flat.dtype == _F32 else "sgb_pack_f32_to_f16"
+    _lib.call(name, ptrs, sizes, n, _p(flat), offset, _stream())
+
+
+def unpack(flat, tensors, offset=0, scale=1.0):
+    _chk(flat, *tensors)
+    ptrs, sizes, n = _ptr_table(tensors)
+    name = "sgb_unpack_f32" if flat.dtype == _F32 else "sgb_unpack_f16_to_f32"
+    _lib.call(name, _p(flat), offset, ptrs, sizes, n, float(scale), _stream())
+
+
+# -------------------------------------------------------- sparsification kernels
+def sparse_threshold(g, acc, thr):
+    """s = g + acc, kept = |s| >= thr; returns (idx 1-based int32, val) of the
+    kept non-zero entries in ascending order; ``acc`` (or None) is updated in
+    place with the residual.  Synchronises to read the count."""
+    _chk(g)
+    n = g.numel()
+    idx = torch.empty(max(n, 1), dtype=_I32, device=g.device)
+    val = torch.empty(max(n, 1), dtype=_F32, device=g.device)
+    nnz = torch.zeros(1, dtype=_I32, device=g.device)
+    need = _lib.lib().sgb_sparse_workspace_bytes(n)
+    ws, wsn = _ws_args(g.device, need)
+    _lib.call("sgb_sparse_threshold_f32", _p(g), None if acc is None else _p(acc), n, float(thr),
+              _p(idx), _p(val), _p(nnz), ws, wsn, _stream())
+    k = int(nnz.item())
+    return idx[:k], val[:k]
+
+
+def sparse_topk(g, acc, k, mode="magnitude"):
+    """The k entries of s = g + acc with the largest key (ties -> lower index),
+    as (idx 1-based int32, val) in ascending index order; ``acc`` (or None)
+    becomes s with the selected entries zeroed."""
+    _chk(g)
+    n = g.numel()
+    k = min(int(k), n)
+    idx = torch.empty(max(k, 1), dtype=_I32, device=g.device)
+    val = torch.empty(max(k, 1), dtype=_F32, device=g.device)
+    scratch = torch.empty(max(n, 1), dtype=_F32, device=g.device)
+    need = _lib.lib().sgb_sparse_workspace_bytes(n)
+    ws, wsn = _ws_args(g.device, need)
+    _lib.call("sgb_sparse_topk_f32", _p(g), None if acc is None else _p(acc), _p(scratch), n, k,
+              {"magnitude": 0, "compat": 1}[mode], _p(idx), _p(val), ws, wsn, _stream())
+    return idx[:k], val[:k]
+
+
+def topk_count(ratio, n):
+    return int(_lib.lib().sgb_topk_count(float(ratio), int(n)))
+
+
+def scatter_add(dst, idx, val):
+    _chk(dst, idx, val)
+    _lib.call("sgb_scatter_add_f32", _p(idx), _p(val), idx.numel(), None, _p(dst), dst.numel(),
+              _stream())
+    return dst

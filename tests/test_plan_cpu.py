@@ -1,0 +1,57 @@
+"""Host-side logic without a GPU: the ResNet-50 hot-path plan, the bucket
+policy against the oracle's restatement, top-K count arithmetic."""
+import numpy as np
+
+from oracle import comm as ocomm
+from singa_b200.opt import plan_buckets
+from singa_b200.resnet50_path import algorithmic_bytes, build_plan, numel
+
+
+def test_resnet50_plan_sizes():
+    plan = build_plan()
+    T = plan["tensors"]
+    assert len(plan["params"]) == 161
+    assert sum(numel(T[p].shape) for p in plan["params"]) == 25557032
+    kinds = [o.kind for o in plan["ops"]]
+    assert kinds.count("bn_bwd") == 53 and kinds.count("relu_bwd") == 49 and kinds.count("add_out") == 16
+    by, nparam = algorithmic_bytes(plan)
+    assert by["relu_bwd"] == 12 * 307456000 + 0 * nparam      # 307.5 M ReLU elements per step
+    assert abs(by["bn_bwd"] - 12 * 355.6e6) < 0.01e9
+    assert by["maxpool_bwd"] == 4 * (2 * 25690112 + 2 * 6422528)
+    assert sorted(plan["grad_order"]) == sorted(plan["params"])
+
+
+def test_bucket_policy_matches_oracle_and_reference_counts():
+    plan = build_plan()
+    sizes = [numel(plan["tensors"]["d:" + n].shape) for n in plan["grad_order"]]
+    ev = plan_buckets(sizes)
+    assert ev == ocomm.plan_buckets(sizes)
+    assert sum(1 for k, _ in ev if k == "direct") == 3          # the three 2,359,296-element 3x3 convs
+    assert sum(1 for k, _ in ev if k == "fused") == 8
+    first = ev[0]
+    assert first[0] == "fused" and len(first[1]) == 5 and sum(sizes[i] for i in first[1]) == 3101672
+    for k, idx in ev:
+        tot = sum(sizes[i] for i in idx)
+        assert tot <= 4194304                                    # fits buffSize
+        if k == "direct":
+            assert tot > 2097152
+    rng = np.random.default_rng(0)
+    for _ in range(20):
+        s = rng.integers(1, 3000000, rng.integers(1, 40)).tolist()
+        assert plan_buckets(s) == ocomm.plan_buckets(s)
+
+
+def test_fused_plan_has_same_parameters_and_fewer_passes():
+    a, b = build_plan(fused=False), build_plan(fused=True)
+    assert a["params"] == b["params"] and a["grad_order"] == b["grad_order"]
+    assert sum(algorithmic_bytes(b)[0].values()) < sum(algorithmic_bytes(a)[0].values())
+
+
+def test_oracle_topk_modes():
+    s = np.array([0.5, -2.5, 0.1, 2.4, -0.7, 3.0, 0.0, -2.0], np.float32)
+    assert ocomm.topk_select(s, 3, "magnitude").tolist() == [1, 3, 5]
+    # the reference comparator truncates to int first: keys 0,2,0,2,0,3,0,2
+    assert ocomm.topk_select(s, 3, "compat").tolist() == [1, 3, 5]
+    assert ocomm.topk_select(s, 2, "compat").tolist() == [1, 5]          # tie 2.5/2.4 -> lower index
+    assert ocomm.topk_select(s * 0.1, 3, "compat").tolist() == [0, 1, 2]  # everything ties at 0
+    assert ocomm.topk_count(0.01, 100000000) == 1000000
