@@ -74,3 +74,41 @@ class OraclePath(object):
             g = np.ascontiguousarray(g, np.float32).copy()
             cpu.sgd_update(t[p], g, t["m:" + p], self.lr, momentum=self.momentum,
                            weight_decay=self.weight_decay)
+
+
+def make_tensors(plan, seed=0):
+    """Seeded numpy tensors for a plan (same roles and value distributions as
+    the GPU executor's, generated on the host)."""
+    rng = np.random.default_rng(seed)
+    T = plan["tensors"]
+    t = {}
+    for name, spec in T.items():
+        k = spec.kind
+        if k == "label":
+            t[name] = rng.integers(0, T["logits"].shape[1], spec.shape).astype(np.int32)
+        elif k == "act":
+            bn_in = name.endswith(".x") and (".bn" in name or name == "bn1.x")
+            t[name] = rng.standard_normal(spec.shape, dtype=np.float32)
+            if bn_in:
+                t[name] = t[name] * np.float32(1.5) + np.float32(0.2)
+        elif k == "syn":
+            t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(1e-2)
+        elif k == "param":
+            if name.endswith(".scale"):
+                t[name] = np.ones(spec.shape, np.float32)
+            elif name.endswith(".bias") or name == "fc.b":
+                t[name] = np.zeros(spec.shape, np.float32)
+            else:
+                t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(0.05)
+        elif k == "pgrad":
+            t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(1e-3)
+        else:
+            t[name] = np.zeros(spec.shape, np.float32)
+    for name in list(T):
+        if name.endswith(".mean"):
+            base = name[:-5]
+            mean, invstd = cpu.bn_stats(t[base + ".x"])
+            t[base + ".mean"], t[base + ".invstd"] = mean, invstd
+    for p in plan["params"]:
+        t["m:" + p] = np.zeros(T[p].shape, np.float32)
+    return t

@@ -70,7 +70,10 @@ struct sgb_comm {
   cudaEvent_t ev_compute = nullptr, ev_c1 = nullptr, ev_s = nullptr, ev_c2 = nullptr,
               ev_host = nullptr;
   size_t send_off = 0;         // elements staged since the last flush
-  bool used = false;
+  // side streams that received work since the last wait(): only those are
+  // joined, so a wait() issued while the compute stream is being captured
+  // never touches a stream outside the capture
+  bool dirty_s = false, dirty_c1 = false, dirty_c2 = false;
 };
 
 namespace {
@@ -197,11 +200,11 @@ void* sgb_comm_stream(const sgb_comm* c, int which) {
 
 int sgb_comm_wait(sgb_comm* c, void* compute_stream) {
   if (!c) return SGB_ERR_NULL;
-  if (!c->used) return SGB_OK;  // nothing was synchronised yet
   cudaStream_t cs = sgb::as_stream(compute_stream);
-  OK(edge(c->ev_s, c->s, cs));
-  OK(edge(c->ev_c1, c->c1, cs));
-  OK(edge(c->ev_c2, c->c2, cs));
+  if (c->dirty_s) OK(edge(c->ev_s, c->s, cs));
+  if (c->dirty_c1) OK(edge(c->ev_c1, c->c1, cs));
+  if (c->dirty_c2) OK(edge(c->ev_c2, c->c2, cs));
+  c->dirty_s = c->dirty_c1 = c->dirty_c2 = false;
   return SGB_OK;
 }
 
@@ -210,7 +213,7 @@ int sgb_comm_synch(sgb_comm* c, void* data, size_t n, int is_half, void* compute
   if (n == 0) return SGB_OK;
   if (!data) return SGB_ERR_NULL;
   if (n > 0x7fffffffu) return SGB_ERR_SIZE;
-  c->used = true;
+  c->dirty_s = true;
   OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->s));
   NC(ncclAllReduce(data, data, n, is_half ? ncclHalf : ncclFloat, ncclSum, c->nccl, c->s));
   return SGB_OK;
@@ -220,11 +223,11 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
                          int is_half, int send, void* compute_stream) {
   if (!c) return SGB_ERR_NULL;
   OK(check_list(tensors, sizes, count));
-  c->used = true;
   const size_t esz = is_half ? sizeof(__half) : sizeof(float);
   if (!send) {
     const size_t total = total_of(sizes, count);
     if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
+    c->dirty_c1 = true;
     OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
     if (!is_half) {
       OK(sgb_pack_f32(tensors, sizes, count, c->send, c->send_off, c->c1));
@@ -242,6 +245,9 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
   // flush: everything staged so far is reduced; `tensors` receive the result
   const size_t total = total_of(sizes, count);
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  if (!c->dirty_c1)  // nothing staged on c1 since the last wait: order after the compute stream
+    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+  c->dirty_c1 = c->dirty_s = true;
   OK(edge(c->ev_c1, c->c1, c->s));
   if (c->send_off)
     NC(ncclAllReduce(c->send, c->recv, c->send_off, is_half ? ncclHalf : ncclFloat, ncclSum,
@@ -267,7 +273,7 @@ int sgb_comm_synch_half(sgb_comm* c, float* data, size_t n, void* compute_stream
   if (!data) return SGB_ERR_NULL;
   if (n > c->max_elems) return SGB_ERR_CAPACITY;
   OK(half_init(c));
-  c->used = true;
+  c->dirty_c1 = c->dirty_s = c->dirty_c2 = true;
   OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
   OK(sgb_cast_f32_f16(data, c->send_h, n, c->c1));
   OK(edge(c->ev_c1, c->c1, c->s));
@@ -282,10 +288,10 @@ int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* s
   if (!c) return SGB_ERR_NULL;
   OK(check_list(tensors, sizes, count));
   OK(half_init(c));
-  c->used = true;
   const size_t total = total_of(sizes, count);
   if (!send) {
     if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
+    c->dirty_c1 = true;
     OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
     // copy + float2half of the reference collapse into one pack-and-cast pass
     OK(sgb_pack_f32_to_f16(tensors, sizes, count, c->send_h, c->send_off, c->c1));
@@ -293,6 +299,9 @@ int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* s
     return SGB_OK;
   }
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  if (!c->dirty_c1)
+    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+  c->dirty_c1 = c->dirty_s = c->dirty_c2 = true;
   OK(edge(c->ev_c1, c->c1, c->s));
   if (c->send_off)
     NC(ncclAllReduce(c->send_h, c->recv_h, c->send_off, ncclHalf, ncclSum, c->nccl, c->s));
@@ -310,7 +319,7 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   if (n > c->max_elems) return SGB_ERR_CAPACITY;
   if (n == 0) return SGB_OK;
   OK(sparse_init(c));
-  c->used = true;
+  c->dirty_c1 = c->dirty_s = c->dirty_c2 = true;
   const int W = c->world;
   OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
   OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));

@@ -145,6 +145,96 @@ maxpool_bwd_band_kernel(const float* __restrict__ x, const float* __restrict__ d
   }
 }
 
+// Same scheme with the geometry (square kernel K, stride S, padding P) known
+// at compile time: window loops unroll, the divisions by the stride become
+// shifts, dy rows are staged in shared memory as well, and every thread
+// produces four consecutive dx values of one row (one 128-bit store).  This is
+// the form the ResNet stem (3x3 / 2 / 1) and the small CNN (2x2 / 2 / 0) hit;
+// it needs W % 4 == 0.  About 60 instructions per dx element instead of ~200.
+template <int K, int S, int P>
+__global__ void __launch_bounds__(kBlock)
+maxpool_bwd_band_fast_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                             float* __restrict__ dx, PoolShape p, BandPlan bp) {
+  extern __shared__ float smem[];
+  float* xs = smem;
+  int* winner = reinterpret_cast<int*>(xs + bp.max_xrows * p.W);
+  float* gs = reinterpret_cast<float*>(winner + bp.max_orows * p.OW);
+  const size_t plane = blockIdx.x;
+  const int H = p.H, W = p.W, OH = p.OH, OW = p.OW;
+  const int h_lo = blockIdx.y * bp.rows, h_hi = min(h_lo + bp.rows, H);
+  const int t_lo = h_lo + P - K + 1;
+  const int o_lo = t_lo > 0 ? (t_lo + S - 1) / S : 0;
+  const int o_hi = min((h_hi - 1 + P) / S, OH - 1);
+  const float* xp = x + plane * H * W;
+  const float* gp = dy + plane * OH * OW;
+  float* dp = dx + plane * H * W;
+  const int xr_lo = max(o_lo * S - P, 0);
+  if (o_hi >= o_lo) {
+    const int xr_hi = min(o_hi * S - P + K, H);
+    const int nv = ((xr_hi - xr_lo) * W) >> 2;                 // W % 4 == 0
+    const float4* src = reinterpret_cast<const float4*>(xp + xr_lo * W);
+    for (int v = threadIdx.x; v < nv; v += kBlock) reinterpret_cast<float4*>(xs)[v] = src[v];
+    const int nwin = (o_hi - o_lo + 1) * OW;
+    const float* gsrc = gp + o_lo * OW;
+    for (int o = threadIdx.x; o < nwin; o += kBlock) gs[o] = gsrc[o];
+    __syncthreads();
+    for (int o = threadIdx.x; o < nwin; o += kBlock) {
+      const int r = o / OW, ow = o - r * OW, oh = o_lo + r;
+      float best = -FLT_MAX;
+      int bi = -1;
+#pragma unroll
+      for (int i = 0; i < K; ++i) {
+        const int h = oh * S - P + i;
+        if (h < 0 || h >= H) continue;
+        const float* row = xs + (h - xr_lo) * W;
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+          const int w = ow * S - P + j;
+          if (w < 0 || w >= W) continue;
+          const float v = row[w];
+          if (v > best) {
+            best = v;
+            bi = h * W + w;
+          }
+        }
+      }
+      winner[o] = bi;
+    }
+  }
+  __syncthreads();
+  constexpr int kCover = (K + S - 1) / S;                       // windows covering one row/column
+  const int w4 = W >> 2, nq = (h_hi - h_lo) * w4;
+  for (int q = threadIdx.x; q < nq; q += kBlock) {
+    const int r = q / w4, c4 = q - r * w4, h = h_lo + r;
+    const int th = h + P - K + 1;
+    const int oh_lo = th > 0 ? (th + S - 1) / S : 0;
+    const int oh_hi = min((h + P) / S, OH - 1);
+    float out[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int w = 4 * c4 + e, i = h * W + w;
+      const int tw = w + P - K + 1;
+      const int ow_lo = tw > 0 ? (tw + S - 1) / S : 0;
+      const int ow_hi = min((w + P) / S, OW - 1);
+      float acc = 0.f;
+#pragma unroll
+      for (int a = 0; a < kCover; ++a) {
+        const int oh = oh_lo + a;
+        if (oh > oh_hi) break;
+#pragma unroll
+        for (int b = 0; b < kCover; ++b) {
+          const int ow = ow_lo + b;
+          if (ow > ow_hi) break;
+          const int widx = (oh - o_lo) * OW + ow;
+          if (winner[widx] == i) acc += gs[widx];
+        }
+      }
+      out[e] = acc;
+    }
+    *reinterpret_cast<float4*>(dp + h * W + 4 * c4) = make_float4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 // Band height: the largest power-of-two-ish row count whose staging fits
 // `budget` bytes of shared memory; 0 rows means even one row does not fit.
 BandPlan plan_bands(const PoolShape& p, size_t budget) {
@@ -153,7 +243,7 @@ BandPlan plan_bands(const PoolShape& p, size_t budget) {
     // windows covering `rows` consecutive dx rows, and the x rows they touch
     const int orows = min((rows + p.kh - 2) / p.sh + 2, p.OH);
     const int xrows = min((orows - 1) * p.sh + p.kh, p.H);
-    const size_t bytes = (static_cast<size_t>(xrows) * p.W + static_cast<size_t>(orows) * p.OW) * 4;
+    const size_t bytes = (static_cast<size_t>(xrows) * p.W + 2 * static_cast<size_t>(orows) * p.OW) * 4;
     if (bytes <= budget) {
       bp.rows = rows;
       bp.bands = (p.H + rows - 1) / rows;
@@ -289,9 +379,22 @@ int sgb_maxpool_backward_f32(const float* x, const float* y, const float* dy, fl
   const BandPlan bp = plan_bands(p, 24 * 1024);
   if (bp.rows > 0 && bp.bands <= 65535) {
     const size_t smem = (static_cast<size_t>(bp.max_xrows) * W +
-                         static_cast<size_t>(bp.max_orows) * p.OW) * sizeof(float);
-    maxpool_bwd_band_kernel<<<dim3(static_cast<unsigned>(planes), bp.bands), kBlock, smem,
-                              as_stream(stream)>>>(x, dy, dx, p, bp);
+                         2 * static_cast<size_t>(bp.max_orows) * p.OW) * sizeof(float);
+    const dim3 grid(static_cast<unsigned>(planes), bp.bands);
+    cudaStream_t s = as_stream(stream);
+    const bool square = kh == kw && sh == sw && ph == pw && W % 4 == 0 && aligned16(x) && aligned16(dx);
+#define SGB_POOL_FAST(KK, SS, PP)                                                       \
+  if (square && kh == KK && sh == SS && ph == PP) {                                     \
+    maxpool_bwd_band_fast_kernel<KK, SS, PP><<<grid, kBlock, smem, s>>>(x, dy, dx, p, bp); \
+    return launch_status();                                                             \
+  }
+    SGB_POOL_FAST(3, 2, 1)
+    SGB_POOL_FAST(2, 2, 0)
+    SGB_POOL_FAST(3, 2, 0)
+    SGB_POOL_FAST(3, 1, 1)
+    SGB_POOL_FAST(2, 1, 0)
+#undef SGB_POOL_FAST
+    maxpool_bwd_band_kernel<<<grid, kBlock, smem, s>>>(x, dy, dx, p, bp);
   } else {
     const unsigned by = blocks_for(static_cast<size_t>(H) * W);
     if (by > 65535) return SGB_ERR_SIZE;
