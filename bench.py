@@ -49,7 +49,7 @@ class ClockSampler(object):
         try:
             self.f = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=self.f,
+                                          "-lms", "100", "-i", str(self.index)], stdout=self.f,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -131,7 +131,7 @@ def reference_main(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--dist-option", default="plain", choices=["plain", "half"])
@@ -237,7 +237,7 @@ def main():
            "ms_per_step": e2e_s * 1e3}
 
     # ---- per-family device times (instrumented eager pass, rank 0 reports)
-    fam_ms = profile_families(path, torch, reps=3)
+    fam_ms = profile_families(path, torch)
     peak, peak_kind = measured_peak()
     fam = {}
     alias = {"relu_bwd": "relu_bwd", "add_relu_bwd": "add_relu_bwd", "add_out": "join", "bn_bwd": "bn_bwd",
@@ -311,39 +311,51 @@ def kernel_launches(path):
     return n
 
 
-def profile_families(path, torch, reps=3):
-    """Device time per op family: CUDA events around every call of one eager
-    step (events on the launching stream), averaged over `reps` steps."""
-    totals = {}
-    stream = torch.cuda.current_stream().cuda_stream
+def profile_families(path, torch, reps=5):
+    """Device time per op family.  All calls of one family are captured, in
+    step order, into one CUDA graph (no host gaps, no other kernels between
+    them) and the replay is timed with CUDA events on the replaying stream;
+    the best of `reps` replays is kept.  Inputs are the buffers the preceding
+    full steps left behind, i.e. far larger than L2 in total."""
+    import numpy as np
     L = path.lib
     kinds = [o.kind for o in path.plan["ops"]]
-    order_index = {n: i for i, n in enumerate(path.plan["grad_order"])}
-    for _ in range(reps):
-        marks = []
-        for (name, args), kind in zip(path.calls, kinds):
-            if name == "grad_ready":
-                path._on_grad_ready(order_index[args], stream)
-                continue
+    fams = {}
+    for (name, args), kind in zip(path.calls, kinds):
+        if name == "grad_ready":
+            continue
+        fams.setdefault("sgd" if name == "sync_and_update" else kind, []).append((name, args))
+    out = {}
+    side = torch.cuda.Stream()
+    for fam, calls in fams.items():
+        def issue(stream):
+            for name, args in calls:
+                if name == "sync_and_update":
+                    pp, gp, mp, sizes, n = path.sgd_tables
+                    L.sgb_sgd_update_multi_f32(pp, gp, mp, sizes, n, path.lr, path.momentum, 0.0,
+                                               path.weight_decay, 0,
+                                               float(np.float32(1.0) / np.float32(path.world)), stream)
+                else:
+                    getattr(L, name)(*[stream if v == "STREAM" else v for v in args])
+        g = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                issue(side.cuda_stream)
+        torch.cuda.current_stream().wait_stream(side)
+        g.replay()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(reps):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            if name == "sync_and_update":
-                if path.comm is not None:
-                    L.sgb_comm_wait(path.comm._h, stream)
-                    a.record()
-                pp, gp, mp, sizes, n = path.sgd_tables
-                import numpy as np
-                L.sgb_sgd_update_multi_f32(pp, gp, mp, sizes, n, path.lr, path.momentum, 0.0, path.weight_decay, 0,
-                                           float(np.float32(1.0) / np.float32(path.world)), stream)
-                kind = "sgd"
-            else:
-                getattr(L, name)(*[stream if v == "STREAM" else v for v in args])
+            g.replay()
             b.record()
-            marks.append((kind, a, b))
-        torch.cuda.synchronize()
-        for kind, a, b in marks:
-            totals[kind] = totals.get(kind, 0.0) + a.elapsed_time(b)
-    return {k: v / reps for k, v in totals.items()}
+            torch.cuda.synchronize()
+            t = a.elapsed_time(b)
+            best = t if best is None or t < best else best
+        out[fam] = best
+    return out
 
 
 if __name__ == "__main__":

@@ -6,8 +6,17 @@
 //               (dy - dbias[c]/M - (x - mean[c]) * invstd[c] * dscale[c] / M)
 // M = N*H*W (spatial mode, NCHW) or N (per-activation mode, N x D).
 //
+// Single-pass scheme (12 bytes of HBM traffic per element), used whenever one
+// channel's x and dy (N*H*W*8 bytes) fit the shared memory of a thread-block
+// cluster of at most 8 CTAs: the cluster stages its channel in shared memory
+// with 16-byte asynchronous copies (cp.async, no register staging), every CTA
+// reduces its share with warp shuffles, the CTAs exchange their two partial
+// sums through distributed shared memory, and dx is computed from the staged
+// copy.  Shares are sized so that two to four CTAs are resident per SM and
+// the load phase of one overlaps the store phase of another.
+//
 // Two-pass scheme, 20 bytes of HBM traffic per element when the tensor does
-// not fit L2:
+// not fit L2 (channels too large for a cluster, e.g. 32 x 112 x 112):
 //   pass 1  grid (slices, C): a CTA walks its slice of the channel's flattened
 //           (n, hw) space with 128-bit loads and leaves two partial sums in the
 //           workspace (no atomics, fixed order -> run-to-run identical);
@@ -18,7 +27,12 @@
 // The optional ReLU mask fuses "dy = relu_in > 0 ? dy : 0" (the backward of
 // the ReLU that follows the BN layer) into both passes, which removes one
 // full write + read of the intermediate gradient.
+#include <cooperative_groups.h>
+#include <stdlib.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace sgb {
 namespace {
@@ -28,6 +42,26 @@ constexpr int kMaxSlices = 64;
 
 struct BnShape {
   int N, C, HW;
+};
+
+// Walks the units u0 + tid, u0 + tid + T, ... of a share and keeps the
+// (plane n, position q) decomposition up to date without a division per step.
+struct UnitWalk {
+  int n, q, dn, dq, hwu;
+  __device__ __forceinline__ UnitWalk(int u, int step, int hwu_) : hwu(hwu_) {
+    n = u / hwu_;
+    q = u - n * hwu_;
+    dn = step / hwu_;
+    dq = step - dn * hwu_;
+  }
+  __device__ __forceinline__ void next() {
+    n += dn;
+    q += dq;
+    if (q >= hwu) {
+      q -= hwu;
+      ++n;
+    }
+  }
 };
 
 __host__ __device__ inline int bn_slices_for(long long per_channel, int C, int sms) {
@@ -50,9 +84,9 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   if (VEC) {
     const int hw4 = sh.HW >> 2, total = sh.N * hw4;
     const int i0 = slice * per_slice, i1 = min(i0 + per_slice, total);
-    for (int i = i0 + threadIdx.x; i < i1; i += kBlock) {
-      const int n = i / hw4, q = i - n * hw4;
-      const size_t off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + 4 * q;
+    UnitWalk w(i0 + threadIdx.x, kBlock, hw4);
+    for (int i = i0 + threadIdx.x; i < i1; i += kBlock, w.next()) {
+      const size_t off = (static_cast<size_t>(w.n) * sh.C + c) * sh.HW + 4 * w.q;
       Vec4f vx, vg, vm;
       vx.u = ld128(x + off);
       vg.u = ld128(dy + off);
@@ -92,6 +126,28 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                     float* __restrict__ dscale, float* __restrict__ dbias, BnShape sh) {
   __shared__ float coef[4];
   const int c = blockIdx.y;
+  // issue this thread's loads first, so that their latency overlaps the
+  // partial-sum lookup below
+  const int unit = blockIdx.x * kBlock + threadIdx.x;
+  constexpr int kW = VEC ? 4 : 1;
+  const int hwu = sh.HW / kW, total = sh.N * hwu;
+  const bool live = unit < total;
+  size_t off = 0;
+  Vec4f vx, vg, vm;
+  vx.f[0] = vg.f[0] = vm.f[0] = 0.f;
+  if (live) {
+    const int n = unit / hwu, q = unit - n * hwu;
+    off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + static_cast<size_t>(q) * kW;
+    if (VEC) {
+      vx.u = ld128(x + off);
+      vg.u = ld128(dy + off);
+      if (MASK) vm.u = ld128(relu_in + off);
+    } else {
+      vx.f[0] = x[off];
+      vg.f[0] = dy[off];
+      if (MASK) vm.f[0] = relu_in[off];
+    }
+  }
   if (threadIdx.x < 32) {
     // add the channel's partials: lanes take slices lane, lane+32; fixed order
     float a = 0.f, b = 0.f;
@@ -117,36 +173,275 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     }
   }
   __syncthreads();
+  if (!live) return;
   const float k = coef[0], a = coef[1], b = coef[2], mu = coef[3];
   if (VEC) {
-    const int hw4 = sh.HW >> 2, total = sh.N * hw4;
-    const int i = blockIdx.x * kBlock + threadIdx.x;
-    if (i < total) {
-      const int n = i / hw4, q = i - n * hw4;
-      const size_t off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + 4 * q;
-      Vec4f vx, vg, vm, o;
-      vx.u = ld128(x + off);
-      vg.u = ld128(dy + off);
-      if (MASK) vm.u = ld128(relu_in + off);
+    Vec4f o;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float g = vg.f[j];
-        if (MASK) g = vm.f[j] > 0 ? g : 0.0f;
-        o.f[j] = k * (g - a - (vx.f[j] - mu) * b);
-      }
-      st128(dx + off, o.u);
+    for (int j = 0; j < 4; ++j) {
+      float g = vg.f[j];
+      if (MASK) g = vm.f[j] > 0 ? g : 0.0f;
+      o.f[j] = k * (g - a - (vx.f[j] - mu) * b);
     }
+    st128(dx + off, o.u);
   } else {
-    const int total = sh.N * sh.HW;
-    const int i = blockIdx.x * kBlock + threadIdx.x;
-    if (i < total) {
-      const int n = i / sh.HW, q = i - n * sh.HW;
-      const size_t off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + q;
-      float g = dy[off];
-      if (MASK) g = relu_in[off] > 0 ? g : 0.0f;
-      dx[off] = k * (g - a - (x[off] - mu) * b);
+    float g = vg.f[0];
+    if (MASK) g = vm.f[0] > 0 ? g : 0.0f;
+    dx[off] = k * (g - a - (vx.f[0] - mu) * b);
+  }
+}
+
+// ----------------------------------------------------------- single pass
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// CTA size of the single-pass kernel: 512 threads for large shares (fewer
+// serial iterations per thread), 256 for small ones.
+
+// grid.x = C * CS with cluster dimension CS: the CS CTAs of a cluster share
+// channel blockIdx.x / CS.  A "unit" is one float4 (VEC) or one float.
+// Dynamic shared memory: 2 * per_cta units (x share, then dy share).
+template <bool VEC, bool MASK, int T>
+__global__ void __launch_bounds__(T)
+bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                      const float* __restrict__ relu_in, const float* __restrict__ scale,
+                      const float* __restrict__ mean, const float* __restrict__ invstd,
+                      float* __restrict__ dx, float* __restrict__ dscale,
+                      float* __restrict__ dbias, BnShape sh, int per_cta) {
+  extern __shared__ __align__(16) float stage[];
+  __shared__ float red[2 * T / 32];
+  __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cs = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int c = blockIdx.x / cs;
+  cluster.barrier_arrive();                           // matched by barrier_wait before the exchange
+  constexpr int kW = VEC ? 4 : 1;                     // floats per unit
+  const int hwu = sh.HW / kW;                         // units per plane
+  const int total = sh.N * hwu;
+  const int u0 = min(rank * per_cta, total), u1 = min(u0 + per_cta, total);
+  const int first = u0 + threadIdx.x;
+  float* sx = stage;
+  float* sg = stage + static_cast<size_t>(per_cta) * kW;
+  const float mu = mean[c];
+  const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
+  const size_t chan_off = static_cast<size_t>(c) * sh.HW;
+
+  // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
+  {
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1; u += T, w.next()) {
+      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * kW;
+      const int l = (u - u0) * kW;
+      if (VEC) {
+        cp_async16(sx + l, x + off);
+        cp_async16(sg + l, dy + off);
+      } else {
+        float g = dy[off];
+        if (MASK) g = relu_in[off] > 0 ? g : 0.0f;
+        sx[l] = x[off];
+        sg[l] = g;
+      }
     }
   }
+  // fused ReLU: while the copies fly, read the ReLU input and keep only the
+  // sign decisions, 4 bits per unit (a share is at most 16 units per thread)
+  unsigned long long keep = 0;
+  if (VEC && MASK) {
+    UnitWalk w(first, T, hwu);
+    int slot = 0;
+    for (int u = first; u < u1;) {
+      // up to 8 independent 16-byte loads in flight per thread, then the sign tests
+      Vec4f vm[8];
+      int cnt = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (u < u1) {
+          const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4;
+          vm[j].u = ld128(relu_in + off);
+          u += T;
+          w.next();
+          cnt = j + 1;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < cnt) {
+          unsigned bits = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) bits |= (vm[j].f[k] > 0 ? 1u : 0u) << k;
+          keep |= static_cast<unsigned long long>(bits) << slot;
+          slot += 4;
+        }
+      }
+    }
+  }
+  if (VEC) cp_async_wait_all();
+
+  // phase 2: partial sums over the share (each thread re-reads what it staged)
+  float s_dy = 0.f, s_dyx = 0.f;
+  {
+    int slot = 0;
+    for (int u = first; u < u1; u += T, slot += 4) {
+      const int l = (u - u0) * kW;
+      if (VEC) {
+        Vec4f vx, vg;
+        vx.u = *reinterpret_cast<const uint4*>(sx + l);
+        vg.u = *reinterpret_cast<const uint4*>(sg + l);
+        if (MASK) {
+          const unsigned bits = static_cast<unsigned>(keep >> slot);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) vg.f[k] = (bits >> k) & 1u ? vg.f[k] : 0.0f;
+          *reinterpret_cast<uint4*>(sg + l) = vg.u;    // keep the masked gradient for phase 3
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          s_dy += vg.f[k];
+          s_dyx += vg.f[k] * (vx.f[k] - mu);
+        }
+      } else {
+        s_dy += sg[l];
+        s_dyx += sg[l] * (sx[l] - mu);
+      }
+    }
+  }
+  // one block reduction for both sums (fixed order), then every CTA pushes its
+  // pair into the slot `parts[rank]` of all peers through distributed shared
+  // memory; after one cluster barrier each CTA owns a full copy, so nobody
+  // reads a peer's memory afterwards and CTAs can retire independently.
+  {
+    constexpr int kWarps = T / 32;
+    static_assert(kWarps <= 32, "one warp finishes the reduction");
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    s_dy = warp_sum(s_dy);
+    s_dyx = warp_sum(s_dyx);
+    if (lane == 0) {
+      red[wid] = s_dy;
+      red[kWarps + wid] = s_dyx;
+    }
+    __syncthreads();
+    if (wid == 0) {
+      float p0 = lane < kWarps ? red[lane] : 0.0f;
+      float p1 = lane < kWarps ? red[kWarps + lane] : 0.0f;
+      p0 = warp_sum(p0);
+      p1 = warp_sum(p1);
+      cluster.barrier_wait();                       // peers have started: their memory is addressable
+      if (lane < cs) *cluster.map_shared_rank(&parts[rank], lane) = make_float2(p0, p1);
+    } else {
+      cluster.barrier_wait();
+    }
+  }
+  cluster.sync();
+
+  float a = 0.f, b = 0.f;
+  for (int r = 0; r < cs; ++r) {                    // rank order: same totals in every CTA
+    a += parts[r].x;
+    b += parts[r].y;
+  }
+  const float r_ = invstd[c];
+  const float inv_m = 1.0f / (static_cast<float>(sh.N) * static_cast<float>(sh.HW));
+  const float ds = b * r_;
+  const float k_ = scale[c] * r_, am = a * inv_m, bm = ds * r_ * inv_m;
+  if (rank == 0 && threadIdx.x == 0) {
+    dscale[c] = ds;
+    dbias[c] = a;
+  }
+
+  // phase 3: dx from the staged copy
+  {
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1; u += T, w.next()) {
+      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * kW;
+      const int l = (u - u0) * kW;
+      if (VEC) {
+        Vec4f vx, vg, o;
+        vx.u = *reinterpret_cast<const uint4*>(sx + l);
+        vg.u = *reinterpret_cast<const uint4*>(sg + l);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o.f[j] = k_ * (vg.f[j] - am - (vx.f[j] - mu) * bm);
+        st128(dx + off, o.u);
+      } else {
+        dx[off] = k_ * (sg[l] - am - (sx[l] - mu) * bm);
+      }
+    }
+  }
+}
+
+// Cluster size (1, 2, 4 or 8) and per-CTA share for the single-pass kernel;
+// returns 0 when a channel does not fit 8 CTAs' shared memory.
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
+int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta) {
+  static const int share_kb = env_int("SGB_BN_SHARE_KB", 50);     // preferred staging per CTA
+  static const int max_cs = env_int("SGB_BN_MAX_CLUSTER", 8) > 8 ? 8 : env_int("SGB_BN_MAX_CLUSTER", 8);
+  const long long kPreferred = share_kb * 1024LL, kLimit = 100 * 1024;
+  for (int pass = 0; pass < 2; ++pass) {
+    const long long cap = pass == 0 ? kPreferred : kLimit;
+    for (int cs = 1; cs <= max_cs; cs *= 2) {
+      const long long share = (units_per_channel + cs - 1) / cs;
+      if (share * unit_bytes * 2 <= cap && share <= 8192) {   // <= 16 units per thread of a 512-thread CTA
+        *per_cta = static_cast<int>(share);
+        return cs;
+      }
+    }
+  }
+  return 0;
+}
+
+template <bool VEC, bool MASK, int T>
+int launch_cluster_t(const float* x, const float* dy, const float* relu_in, const float* scale,
+                     const float* mean, const float* invstd, float* dx, float* dscale,
+                     float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s) {
+  auto kernel = bn_bwd_cluster_kernel<VEC, MASK, T>;
+  const size_t smem = static_cast<size_t>(per_cta) * (VEC ? 16 : 4) * 2;
+  // Opt in to > 48 KB of dynamic shared memory once per device and kernel
+  // instantiation (the attribute sticks to the function in that context), so
+  // that later launches - including launches under stream capture - issue no
+  // attribute call.
+  static bool attr_set[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sh.C) * cs);
+  cfg.blockDim = dim3(T);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, dy, relu_in, scale, mean, invstd, dx, dscale,
+                                     dbias, sh, per_cta);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  return launch_status();
+}
+
+template <bool VEC, bool MASK>
+int launch_cluster(const float* x, const float* dy, const float* relu_in, const float* scale,
+                   const float* mean, const float* invstd, float* dx, float* dscale,
+                   float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s) {
+  // at most 16 units per thread (the fused mask keeps 4 bits per unit in 64 bits)
+  if (per_cta > 2048)
+    return launch_cluster_t<VEC, MASK, 512>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias,
+                                            sh, cs, per_cta, s);
+  return launch_cluster_t<VEC, MASK, 256>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh,
+                                          cs, per_cta, s);
 }
 
 // Per-activation mode (N x D, one statistic per feature): a thread owns one
@@ -192,13 +487,23 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
         x, dy, scale, mean, invstd, dx, dscale, dbias, N, C);
     return launch_status();
   }
+  const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(dy) && aligned16(dx) &&
+                   (!MASK || aligned16(relu_in));
+  const BnShape sh{N, C, HW};
+  {
+    int per_cta = 0;
+    const int cs = cluster_plan(vec ? per_channel / 4 : per_channel, vec ? 16 : 4, &per_cta);
+    if (cs > 0 && static_cast<long long>(C) * cs <= 0x7fffffffLL) {
+      return vec ? launch_cluster<true, MASK>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias,
+                                              sh, cs, per_cta, s)
+                 : launch_cluster<false, MASK>(x, dy, relu_in, scale, mean, invstd, dx, dscale,
+                                               dbias, sh, cs, per_cta, s);
+    }
+  }
   const int slices = bn_slices_for(per_channel, C, sm_count());
   if (!ws || ws_bytes < static_cast<size_t>(slices) * C * sizeof(float2) || !aligned16(ws))
     return SGB_ERR_WORKSPACE;
   float2* partial = static_cast<float2*>(ws);
-  const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(dy) && aligned16(dx) &&
-                   (!MASK || aligned16(relu_in));
-  const BnShape sh{N, C, HW};
   const int total = static_cast<int>(vec ? per_channel / 4 : per_channel);
   const int per_slice = static_cast<int>(ceil_div(total, slices));
   const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock)), C);

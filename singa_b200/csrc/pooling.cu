@@ -316,6 +316,29 @@ avgpool_bwd_kernel(const float* __restrict__ dy, float* __restrict__ dx, PoolSha
   dx[i] = acc;
 }
 
+// Global average pooling (one window = the whole plane, no padding): every dx
+// element of a plane is dy[plane] / (H*W).  Four consecutive elements per
+// thread, one 128-bit store; the plane index advances without extra divisions.
+__global__ void __launch_bounds__(kBlock)
+avgpool_bwd_global_kernel(const float* __restrict__ dy, float* __restrict__ dx, unsigned hw,
+                          unsigned total4) {
+  const unsigned v = blockIdx.x * static_cast<unsigned>(kBlock) + threadIdx.x;
+  if (v >= total4) return;
+  const unsigned i = 4u * v;
+  unsigned plane = i / hw, r = i - plane * hw;
+  const float inv = static_cast<float>(hw);
+  float out[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    out[e] = dy[plane] / inv;
+    if (++r == hw) {
+      r = 0;
+      ++plane;
+    }
+  }
+  *reinterpret_cast<float4*>(dx + i) = make_float4(out[0], out[1], out[2], out[3]);
+}
+
 int make_shape(PoolShape& p, int N, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
                int sw) {
   if (N < 0 || C < 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0 || sh <= 0 ||
@@ -410,6 +433,13 @@ int sgb_avgpool_backward_f32(const float* dy, float* dx, int N, int C, int H, in
   if (!dy || !dx) return SGB_ERR_NULL;
   const size_t planes = static_cast<size_t>(N) * C;
   if (static_cast<long long>(H) * W > 0x7fffffffLL) return SGB_ERR_SIZE;
+  if (p.OH == 1 && p.OW == 1 && ph == 0 && pw == 0 && kh == H && kw == W && aligned16(dx) &&
+      in_total % 4 == 0 && in_total < 0x7fffffffu) {
+    const unsigned total4 = static_cast<unsigned>(in_total / 4);
+    avgpool_bwd_global_kernel<<<blocks_for(total4), kBlock, 0, as_stream(stream)>>>(
+        dy, dx, static_cast<unsigned>(H * W), total4);
+    return launch_status();
+  }
   // whole planes per launch, each launch below 2^31 elements
   const size_t hw = static_cast<size_t>(H) * W;
   const size_t planes_per_launch = (0x7fffffffu - kBlock) / hw;
