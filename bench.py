@@ -146,6 +146,10 @@ def main():
     if args.impl == "reference":
         return reference_main(args, rank, world)
 
+    import faulthandler
+    # A rank that stops making progress ends itself with a traceback instead of
+    # holding the GPUs until an outer time limit.
+    faulthandler.dump_traceback_later(int(os.environ.get("SGB_BENCH_WATCHDOG_S", "900")), exit=True)
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -282,11 +286,16 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": kernel_launches(path) * K,
             "roofline": roofline, "roofline_by_family": fam, "cpu_baseline": cpu_baseline,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    path.release_graph()          # graphs that captured NCCL work must go before the communicator
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
     comm.close()
     if multi:
         dist.barrier()
         dist.destroy_process_group()
+    faulthandler.cancel_dump_traceback_later()
 
 
 def kernel_launches(path):

@@ -55,8 +55,10 @@ struct sgb_comm {
   size_t max_elems = 0;
   float* send = nullptr;   // fusedSendBuff
   float* recv = nullptr;   // fusedRecvBuff
-  __half* send_h = nullptr;
+  __half* send_h = nullptr;    // staging bucket in fp16
   __half* recv_h = nullptr;
+  __half* dsend_h = nullptr;   // direct (unbucketed) fp16 synch: never aliases a half-filled bucket
+  __half* drecv_h = nullptr;
   // sparse path (allocated at first use)
   float* sum = nullptr;        // g + acc (backupBuff)
   int* pay_send = nullptr;     // [idx | val], 2 * max_elems words
@@ -84,10 +86,38 @@ int edge(cudaEvent_t ev, cudaStream_t from, cudaStream_t to) {
   return SGB_OK;
 }
 
+// Ordering rules around every collective (stream s):
+//   before: s waits for the staging stream c1 and, if it carries work, for the
+//           post-processing stream c2 - so the send buffer is complete and the
+//           previous consumer of the receive buffer is done;
+//   after:  c1 (and c2 when it will post-process) wait for the collective - so
+//           nothing refills a send buffer that NCCL is still reading.
+int before_collective(sgb_comm* c, cudaStream_t compute) {
+  if (!c->dirty_c1)  // c1 idle since the last wait(): order it after the compute stream first
+    OK(edge(c->ev_compute, compute, c->c1));
+  c->dirty_c1 = true;
+  OK(edge(c->ev_c1, c->c1, c->s));
+  if (c->dirty_c2) OK(edge(c->ev_c2, c->c2, c->s));
+  c->dirty_s = true;
+  return SGB_OK;
+}
+
+int after_collective(sgb_comm* c, bool c2_too) {
+  CU(cudaEventRecord(c->ev_s, c->s));
+  CU(cudaStreamWaitEvent(c->c1, c->ev_s, 0));
+  if (c2_too) {
+    CU(cudaStreamWaitEvent(c->c2, c->ev_s, 0));
+    c->dirty_c2 = true;
+  }
+  return SGB_OK;
+}
+
 int half_init(sgb_comm* c) {
   if (c->send_h) return SGB_OK;
   CU(cudaMalloc(&c->send_h, c->max_elems * sizeof(__half)));
   CU(cudaMalloc(&c->recv_h, c->max_elems * sizeof(__half)));
+  CU(cudaMalloc(&c->dsend_h, c->max_elems * sizeof(__half)));
+  CU(cudaMalloc(&c->drecv_h, c->max_elems * sizeof(__half)));
   return SGB_OK;
 }
 
@@ -165,7 +195,7 @@ int sgb_comm_destroy(sgb_comm* c) {
   if (c->c1) cudaStreamSynchronize(c->c1);
   if (c->c2) cudaStreamSynchronize(c->c2);
   if (c->nccl) ncclCommDestroy(c->nccl);
-  void* bufs[] = {c->send, c->recv, c->send_h, c->recv_h, c->sum, c->pay_send,
+  void* bufs[] = {c->send, c->recv, c->send_h, c->recv_h, c->dsend_h, c->drecv_h, c->sum, c->pay_send,
                   c->pay_recv, c->ws, c->nnz_dev};
   for (void* b : bufs)
     if (b) cudaFree(b);
@@ -245,15 +275,12 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
   // flush: everything staged so far is reduced; `tensors` receive the result
   const size_t total = total_of(sizes, count);
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
-  if (!c->dirty_c1)  // nothing staged on c1 since the last wait: order after the compute stream
-    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
-  c->dirty_c1 = c->dirty_s = true;
-  OK(edge(c->ev_c1, c->c1, c->s));
+  OK(before_collective(c, sgb::as_stream(compute_stream)));
   if (c->send_off)
     NC(ncclAllReduce(c->send, c->recv, c->send_off, is_half ? ncclHalf : ncclFloat, ncclSum,
                      c->nccl, c->s));
   c->send_off = 0;
-  OK(edge(c->ev_s, c->s, c->c1));
+  OK(after_collective(c, false));
   if (!is_half) {
     OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c1));
   } else {
@@ -273,13 +300,13 @@ int sgb_comm_synch_half(sgb_comm* c, float* data, size_t n, void* compute_stream
   if (!data) return SGB_ERR_NULL;
   if (n > c->max_elems) return SGB_ERR_CAPACITY;
   OK(half_init(c));
-  c->dirty_c1 = c->dirty_s = c->dirty_c2 = true;
   OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
-  OK(sgb_cast_f32_f16(data, c->send_h, n, c->c1));
-  OK(edge(c->ev_c1, c->c1, c->s));
-  NC(ncclAllReduce(c->send_h, c->recv_h, n, ncclHalf, ncclSum, c->nccl, c->s));
-  OK(edge(c->ev_s, c->s, c->c2));
-  OK(sgb_cast_f16_f32(c->recv_h, data, n, c->c2));
+  c->dirty_c1 = true;
+  OK(sgb_cast_f32_f16(data, c->dsend_h, n, c->c1));
+  OK(before_collective(c, sgb::as_stream(compute_stream)));
+  NC(ncclAllReduce(c->dsend_h, c->drecv_h, n, ncclHalf, ncclSum, c->nccl, c->s));
+  OK(after_collective(c, true));
+  OK(sgb_cast_f16_f32(c->drecv_h, data, n, c->c2));
   return SGB_OK;
 }
 
@@ -299,14 +326,11 @@ int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* s
     return SGB_OK;
   }
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
-  if (!c->dirty_c1)
-    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
-  c->dirty_c1 = c->dirty_s = c->dirty_c2 = true;
-  OK(edge(c->ev_c1, c->c1, c->s));
+  OK(before_collective(c, sgb::as_stream(compute_stream)));
   if (c->send_off)
     NC(ncclAllReduce(c->send_h, c->recv_h, c->send_off, ncclHalf, ncclSum, c->nccl, c->s));
   c->send_off = 0;
-  OK(edge(c->ev_s, c->s, c->c2));
+  OK(after_collective(c, true));
   OK(sgb_unpack_f16_to_f32(c->recv_h, 0, tensors, sizes, count, 1.0f, c->c2));
   return SGB_OK;
 }
@@ -319,9 +343,9 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   if (n > c->max_elems) return SGB_ERR_CAPACITY;
   if (n == 0) return SGB_OK;
   OK(sparse_init(c));
-  c->dirty_c1 = c->dirty_s = c->dirty_c2 = true;
   const int W = c->world;
   OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+  c->dirty_c1 = true;
   OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
 
   size_t nnz_max = 0;
@@ -347,10 +371,10 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
                              c->c1));
   }
 
-  OK(edge(c->ev_c1, c->c1, c->s));
+  OK(before_collective(c, sgb::as_stream(compute_stream)));
   if (nnz_max)
     NC(ncclAllGather(c->pay_send, c->pay_recv, 2 * nnz_max, ncclFloat, c->nccl, c->s));
-  OK(edge(c->ev_s, c->s, c->c2));
+  OK(after_collective(c, true));
   CU(cudaMemsetAsync(c->recv, 0, n * sizeof(float), c->c2));
   for (int r = 0; r < W && nnz_max; ++r) {  // ranks in ascending order, as the reference
     const int* seg = c->pay_recv + static_cast<size_t>(r) * 2 * nnz_max;

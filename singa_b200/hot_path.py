@@ -263,5 +263,11 @@ class HotPathGPU(object):
         self.graph = g
         return g
 
+    def release_graph(self):
+        """Drops the captured step.  Must be called before the communicator is
+        closed: NCCL keeps a communicator alive (its destroy call waits) for as
+        long as a CUDA graph that captured its collectives exists."""
+        self.graph = None
+
     def loss(self):
         return self.t["loss"]

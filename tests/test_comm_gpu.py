@@ -18,7 +18,10 @@ def run_world(n, port):
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "dist_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
-    assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-6000:]
+    if r.returncode != 0:
+        # keep the ranks' own tracebacks, not only the launcher's summary
+        lines = [ln for ln in r.stderr.splitlines() if ln.startswith("[rank") or "Error" in ln]
+        raise AssertionError("\n".join(lines[-40:]) or r.stderr[-4000:])
     assert r.stdout.count("communicator checks passed") == n, r.stdout[-2000:]
 
 
