@@ -212,11 +212,13 @@ def main():
     barrier()
     if rank == 0:
         sampler.start()
+    torch.cuda.profiler.start()     # lets `ncu --profile-from-start off` see exactly the timed steps
     e0.record()
     for _ in range(K):
         one_step()
     e1.record()
     barrier()
+    torch.cuda.profiler.stop()
     ms = max_over_ranks(e0.elapsed_time(e1)) / K
     value = BATCH * world / (ms / 1e3)
 

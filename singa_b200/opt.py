@@ -77,10 +77,14 @@ class DistOpt(object):
     step run as ONE multi-tensor launch group at the end of each
     ``backward_and_*`` call (``grad_scale`` of the fused SGD kernel)."""
 
-    def __init__(self, opt, nccl_id, local_rank, world_size, buffSize=4194304):
-        from .communicator import Communicator
+    def __init__(self, opt, nccl_id=None, local_rank=0, world_size=1, buffSize=4194304,
+                 communicator=None):
         self.opt = opt
-        self.communicator = Communicator(local_rank, world_size, nccl_id, buffSize)
+        if communicator is None:
+            from .communicator import Communicator
+            communicator = Communicator(local_rank, world_size, nccl_id, buffSize)
+        # any object with the reference Communicator's methods and rank fields
+        self.communicator = communicator
         self.world_size = self.communicator.world_size
         self.local_rank = self.communicator.local_rank
         self.global_rank = self.communicator.global_rank
