@@ -38,6 +38,7 @@ extern "C" {
 #define SGB_ERR_UNSUPPORTED (-6) /* enum value / dtype / mode not supported */
 #define SGB_ERR_STATE (-7)       /* call not valid in the handle's state */
 #define SGB_ERR_CAPACITY (-8)    /* does not fit the communicator's buffers */
+#define SGB_ERR_LIMIT (-9)       /* size exceeds an entry point's built-in scratch */
 
 const char *sgb_status_string(int status);
 int sgb_last_cuda_error(void); /* last cudaError_t recorded by this library */
@@ -223,6 +224,29 @@ int sgb_bn_backward_f32(const float *x, const float *dy, const float *scale,
                         const float *mean, const float *invstd, float *dx,
                         float *dscale, float *dbias, int N, int C, int HW,
                         void *ws, size_t ws_bytes, void *stream);
+/* Batch-norm backward for callers that can neither allocate device memory nor
+ * hand in a workspace.  (No counterpart in the reference: this entry point
+ * exists only in this library.)  Typical callers: an operator running inside
+ * a framework whose own pool already holds the device's memory, so that a
+ * second allocator may fail; or a thread that must not trigger the
+ * device-wide synchronisation a cudaMalloc/cudaFree can imply.  Same
+ * arithmetic and results contract as sgb_bn_backward_f32 (it always takes the
+ * two-pass form, so sums may differ from the other entry point in the last
+ * bits).  The partial sums live in a 2 MiB array inside the library's device
+ * image (held by every GPU that loads the library until exit), which limits
+ * C to 4096 channels: a larger C returns SGB_ERR_LIMIT and launches
+ * nothing.  No cudaMalloc/cudaFree or allocating routine is called.  The
+ * first call on each device looks up the array's device address (one
+ * cudaGetSymbolAddress): make that first call before any stream capture
+ * begins.  All calls share the one array and it keeps the previous call's
+ * contents; nothing in it needs clearing (each call overwrites every entry it
+ * later reads), but two calls whose kernels can overlap on the GPU (different
+ * streams, no ordering between them) race on it - keep them ordered. */
+int sgb_bn_backward_noalloc_f32(const float *x, const float *dy,
+                                const float *scale, const float *mean,
+                                const float *invstd, float *dx, float *dscale,
+                                float *dbias, int N, int C, int HW,
+                                void *stream);
 /* Same with the backward of the ReLU that follows the BN layer folded in:
  * dy is first masked by relu_in > 0 (relu_in = the tensor ReLU stored, i.e.
  * the BN output).  Equals ReLUBackward + GpuBatchNormBackward bit for bit. */

@@ -519,6 +519,74 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
   return launch_status();
 }
 
+// ------------------------------------------------ variant with built-in scratch
+// Partial sums of the two-pass scheme for callers that cannot provide a
+// workspace: a fixed array that lives in the library's device image.  Every
+// GPU that loads the library holds these 2 MiB until the process exits.
+constexpr int kNoAllocMaxChannels = 4096;
+static __device__ __align__(256) float2 g_bn_static_scratch[kMaxSlices * kNoAllocMaxChannels];
+
+// In host code `g_bn_static_scratch` is only a handle for the symbol, not an
+// address a kernel could use; the device address is looked up once per device
+// (with that device current) and cached here.
+float2* static_scratch_address(int* status) {
+  static float2* cached[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    *status = note_cuda_error(e);
+    return nullptr;
+  }
+  if (dev < 0 || dev >= 64) {
+    *status = SGB_ERR_UNSUPPORTED;
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_bn_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      *status = note_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+      return nullptr;
+    }
+    cached[dev] = static_cast<float2*>(ptr);
+  }
+  *status = SGB_OK;
+  return cached[dev];
+}
+
+int bn_backward_static(const float* x, const float* dy, const float* scale, const float* mean,
+                       const float* invstd, float* dx, float* dscale, float* dbias, int N, int C,
+                       int HW, void* stream) {
+  if (N < 0 || C < 0 || HW < 0) return SGB_ERR_SIZE;
+  if (N == 0 || C == 0 || HW == 0) return SGB_OK;
+  if (!x || !dy || !scale || !mean || !invstd || !dx || !dscale || !dbias) return SGB_ERR_NULL;
+  if (C > kNoAllocMaxChannels) return SGB_ERR_LIMIT;   // the built-in scratch holds 4096 channels
+  const long long per_channel = static_cast<long long>(N) * HW;
+  if (per_channel > 0x7fffffffLL) return SGB_ERR_SIZE;
+  int st = SGB_OK;
+  float2* partial = static_scratch_address(&st);
+  if (!partial) return st;
+  cudaStream_t s = as_stream(stream);
+  const int slices = bn_slices_for(per_channel, C, sm_count());   // <= kMaxSlices
+  const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(dy) && aligned16(dx);
+  const BnShape sh{N, C, HW};
+  const int total = static_cast<int>(vec ? per_channel / 4 : per_channel);
+  const int per_slice = static_cast<int>(ceil_div(total, slices));
+  const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock)), C);
+  // pass 1 writes partial[c * slices + k] for every k < slices before pass 2
+  // (same stream) reads exactly those entries, so nothing has to be cleared
+  if (vec) {
+    bn_bwd_reduce_kernel<true, false><<<g1, kBlock, 0, s>>>(x, dy, nullptr, mean, partial, sh, per_slice);
+    bn_bwd_apply_kernel<true, false><<<g2, kBlock, 0, s>>>(x, dy, nullptr, scale, mean, invstd, partial,
+                                                           slices, dx, dscale, dbias, sh);
+  } else {
+    bn_bwd_reduce_kernel<false, false><<<g1, kBlock, 0, s>>>(x, dy, nullptr, mean, partial, sh, per_slice);
+    bn_bwd_apply_kernel<false, false><<<g2, kBlock, 0, s>>>(x, dy, nullptr, scale, mean, invstd, partial,
+                                                            slices, dx, dscale, dbias, sh);
+  }
+  return launch_status();
+}
+
 }  // namespace
 }  // namespace sgb
 
@@ -536,6 +604,12 @@ int sgb_bn_backward_f32(const float* x, const float* dy, const float* scale, con
                         int C, int HW, void* ws, size_t ws_bytes, void* stream) {
   return bn_backward<false>(x, dy, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
                             ws, ws_bytes, stream);
+}
+
+int sgb_bn_backward_noalloc_f32(const float* x, const float* dy, const float* scale,
+                                const float* mean, const float* invstd, float* dx, float* dscale,
+                                float* dbias, int N, int C, int HW, void* stream) {
+  return bn_backward_static(x, dy, scale, mean, invstd, dx, dscale, dbias, N, C, HW, stream);
 }
 
 int sgb_bn_relu_backward_f32(const float* x, const float* dy, const float* relu_in,

@@ -40,6 +40,7 @@ const char* sgb_status_string(int status) {
     case SGB_ERR_UNSUPPORTED: return "unsupported op, dtype or mode";
     case SGB_ERR_STATE: return "call not valid in this state";
     case SGB_ERR_CAPACITY: return "does not fit the communicator's buffers";
+    case SGB_ERR_LIMIT: return "size exceeds the built-in scratch of this entry point (limit stated in sgb.h)";
     default: return "unknown status";
   }
 }
