@@ -387,10 +387,14 @@ int sgb_comm_wait(sgb_comm *c, void *compute_stream);
 int sgb_comm_synch(sgb_comm *c, void *data, size_t n, int is_half,
                    void *compute_stream);
 /* Communicator::fusedSynch(t, send) (communicator.cc:212-302).  send == 0:
- * append the tensors to the staging buffer (one pack launch).  send != 0:
- * all-reduce everything staged, then scatter the result back into `tensors`
- * (the full list staged since the last flush, in staging order).  tensors /
- * sizes are HOST arrays.  SGB_ERR_CAPACITY if the bucket would overflow. */
+ * append the tensors to the bucket.  send != 0: all-reduce everything staged,
+ * then scatter the result back into `tensors` (the full list staged since the
+ * last flush, in staging order).  Staging is deferred: a stage call records
+ * pointers and reserves space, and the bytes are gathered by one multi-tensor
+ * pack launch at flush time, so a staged tensor must stay allocated and
+ * unchanged until the flush (it has to: the flush writes the result into it).
+ * tensors / sizes are HOST arrays.  SGB_ERR_CAPACITY if the bucket would
+ * overflow. */
 int sgb_comm_fused_synch(sgb_comm *c, void *const *tensors, const size_t *sizes,
                          size_t count, int is_half, int send,
                          void *compute_stream);

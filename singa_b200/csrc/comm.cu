@@ -76,6 +76,13 @@ struct sgb_comm {
   // joined, so a wait() issued while the compute stream is being captured
   // never touches a stream outside the capture
   bool dirty_s = false, dirty_c1 = false, dirty_c2 = false;
+  // Staging is deferred: a stage call only records the tensors; the bytes are
+  // gathered by ONE multi-tensor pack launch when the bucket is flushed (the
+  // tensors must stay alive until then anyway - the flush writes into them).
+  std::vector<void*> pend_ptrs;
+  std::vector<size_t> pend_sizes;
+  size_t pend_off = 0;         // staging-buffer offset of the first pending tensor
+  int pend_half = 0;           // pending tensors go to the fp16 staging buffer
 };
 
 namespace {
@@ -110,6 +117,32 @@ int after_collective(sgb_comm* c, bool c2_too) {
     c->dirty_c2 = true;
   }
   return SGB_OK;
+}
+
+int pack_pending(sgb_comm* c, cudaStream_t compute) {
+  if (c->pend_ptrs.empty()) return SGB_OK;
+  OK(edge(c->ev_compute, compute, c->c1));   // every staged gradient was produced before this point
+  c->dirty_c1 = true;
+  if (c->pend_half)
+    OK(sgb_pack_f32_to_f16(c->pend_ptrs.data(), c->pend_sizes.data(), c->pend_ptrs.size(), c->send_h,
+                           c->pend_off, c->c1));
+  else
+    OK(sgb_pack_f32(c->pend_ptrs.data(), c->pend_sizes.data(), c->pend_ptrs.size(), c->send,
+                    c->pend_off, c->c1));
+  c->pend_ptrs.clear();
+  c->pend_sizes.clear();
+  return SGB_OK;
+}
+
+void defer(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count, int half) {
+  if (c->pend_ptrs.empty()) {
+    c->pend_off = c->send_off;
+    c->pend_half = half;
+  }
+  for (size_t i = 0; i < count; ++i) {
+    c->pend_ptrs.push_back(tensors[i]);
+    c->pend_sizes.push_back(sizes[i]);
+  }
 }
 
 int half_init(sgb_comm* c) {
@@ -257,11 +290,12 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
   if (!send) {
     const size_t total = total_of(sizes, count);
     if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
-    c->dirty_c1 = true;
-    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
     if (!is_half) {
-      OK(sgb_pack_f32(tensors, sizes, count, c->send, c->send_off, c->c1));
+      if (!c->pend_ptrs.empty() && c->pend_half) OK(pack_pending(c, sgb::as_stream(compute_stream)));
+      defer(c, tensors, sizes, count, 0);
     } else {
+      c->dirty_c1 = true;
+      OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
       size_t off = c->send_off;
       for (size_t i = 0; i < count; ++i) {
         CU(cudaMemcpyAsync(reinterpret_cast<char*>(c->send) + off * esz, tensors[i],
@@ -275,6 +309,7 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
   // flush: everything staged so far is reduced; `tensors` receive the result
   const size_t total = total_of(sizes, count);
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  OK(pack_pending(c, sgb::as_stream(compute_stream)));
   OK(before_collective(c, sgb::as_stream(compute_stream)));
   if (c->send_off)
     NC(ncclAllReduce(c->send, c->recv, c->send_off, is_half ? ncclHalf : ncclFloat, ncclSum,
@@ -318,14 +353,14 @@ int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* s
   const size_t total = total_of(sizes, count);
   if (!send) {
     if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
-    c->dirty_c1 = true;
-    OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
-    // copy + float2half of the reference collapse into one pack-and-cast pass
-    OK(sgb_pack_f32_to_f16(tensors, sizes, count, c->send_h, c->send_off, c->c1));
+    // copy + float2half of the reference collapse into one pack-and-cast pass at flush time
+    if (!c->pend_ptrs.empty() && !c->pend_half) OK(pack_pending(c, sgb::as_stream(compute_stream)));
+    defer(c, tensors, sizes, count, 1);
     c->send_off += total;
     return SGB_OK;
   }
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  OK(pack_pending(c, sgb::as_stream(compute_stream)));
   OK(before_collective(c, sgb::as_stream(compute_stream)));
   if (c->send_off)
     NC(ncclAllReduce(c->send_h, c->recv_h, c->send_off, ncclHalf, ncclSum, c->nccl, c->s));

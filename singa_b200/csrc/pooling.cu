@@ -235,6 +235,102 @@ maxpool_bwd_band_fast_kernel(const float* __restrict__ x, const float* __restric
   }
 }
 
+// 3x3 window, stride 2, padding 1 on even H and W % 4 == 0 (the ResNet stem):
+// the general scheme above with everything that can be decided at compile time
+// decided.  The staged x band carries a -FLT_MAX column on the left and, at the
+// top of the plane, a -FLT_MAX row, so the nine reads of a window need no
+// bounds tests; every thread then produces a 2 x 4 patch of dx from six parked
+// winners (two window rows x three window columns), whose raster-order sums
+// are written out explicitly.  ~30 instructions per dx element.
+struct StemPlan {
+  int rows;     // dx rows per band (even)
+  int bands;
+};
+
+__global__ void __launch_bounds__(kBlock)
+maxpool_bwd_k3s2p1_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                          float* __restrict__ dx, int H, int W, int OH, int OW, int rows) {
+  extern __shared__ float smem[];
+  const int pitch = W + 4;                       // xs[r][4 + c] = x[xr0 + r][c], xs[r][3] = -FLT_MAX
+  const int wp = OW + 1;                         // winner / dy pitch (one never-matching pad column)
+  const int h_lo = blockIdx.y * rows, h_hi = min(h_lo + rows, H);
+  const int o_lo = h_lo >> 1, o_hi = min(h_hi >> 1, OH - 1);     // window rows [o_lo, o_hi]
+  const int norow = o_hi - o_lo + 1;
+  const int xr0 = 2 * o_lo - 1;                                 // may be -1
+  const int xr1 = min(2 * o_hi + 2, H);                         // x rows [xr0, xr1)
+  const int nxr = xr1 - xr0;
+  float* xs = smem;
+  int* winner = reinterpret_cast<int*>(xs + (rows + 3) * pitch);
+  float* gs = reinterpret_cast<float*>(winner + ((rows >> 1) + 2) * wp);
+  const size_t plane = blockIdx.x;
+  const float* xp = x + plane * H * W;
+  const float* gp = dy + plane * OH * OW;
+  float* dp = dx + plane * H * W;
+
+  const int w4 = W >> 2;
+  for (int v = threadIdx.x; v < nxr * w4; v += kBlock) {
+    const int r = v / w4, c4 = v - r * w4, xr = xr0 + r;
+    float4 val = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+    if (xr >= 0) val = *reinterpret_cast<const float4*>(xp + xr * W + 4 * c4);
+    *reinterpret_cast<float4*>(xs + r * pitch + 4 + 4 * c4) = val;
+  }
+  for (int r = threadIdx.x; r < nxr; r += kBlock) xs[r * pitch + 3] = -FLT_MAX;
+  // dy rows of the band's windows, plus a pad row / column of winners that match nothing
+  for (int o = threadIdx.x; o < (norow + 1) * wp; o += kBlock) {
+    const int r = o / wp, c = o - r * wp;
+    const bool real = r < norow && c < OW;
+    gs[o] = real ? gp[(o_lo + r) * OW + c] : 0.0f;
+    if (!real) winner[o] = -2;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < norow * OW; o += kBlock) {
+    const int r = o / OW, ow = o - r * OW;
+    const float* win = xs + (2 * r) * pitch + 2 * ow + 3;        // top-left cell of the window
+    const int g0 = (2 * (o_lo + r) - 1) * W + 2 * ow - 1;        // its flat plane index
+    float best = -FLT_MAX;
+    int bi = -1;
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const float v = win[i * pitch + j];
+        if (v > best) {
+          best = v;
+          bi = g0 + i * W + j;
+        }
+      }
+    winner[r * wp + ow] = bi;
+  }
+  __syncthreads();
+  const int npatch = ((h_hi - h_lo) >> 1) * w4;
+  for (int t = threadIdx.x; t < npatch; t += kBlock) {
+    const int m = t / w4, q = t - m * w4;
+    const int* w0 = winner + m * wp + 2 * q;       // windows (m, 2q .. 2q+2)
+    const int* w1 = w0 + wp;                        // windows (m+1, ...)
+    const float* g0 = gs + m * wp + 2 * q;
+    const float* g1 = g0 + wp;
+    const int a0 = w0[0], a1 = w0[1], a2 = w0[2], b0 = w1[0], b1 = w1[1], b2 = w1[2];
+    const float ga0 = g0[0], ga1 = g0[1], ga2 = g0[2], gb0 = g1[0], gb1 = g1[1], gb2 = g1[2];
+    const int h = h_lo + 2 * m;
+    const int i0 = h * W + 4 * q, i1 = i0 + W;      // flat indices of the patch's two rows
+#define PICK(wv, gv, idx) ((wv) == (idx) ? (gv) : 0.0f)
+    float4 top, bot;
+    top.x = 0.0f + PICK(a0, ga0, i0);
+    top.y = (0.0f + PICK(a0, ga0, i0 + 1)) + PICK(a1, ga1, i0 + 1);
+    top.z = 0.0f + PICK(a1, ga1, i0 + 2);
+    top.w = (0.0f + PICK(a1, ga1, i0 + 3)) + PICK(a2, ga2, i0 + 3);
+    bot.x = (0.0f + PICK(a0, ga0, i1)) + PICK(b0, gb0, i1);
+    bot.y = (((0.0f + PICK(a0, ga0, i1 + 1)) + PICK(a1, ga1, i1 + 1)) + PICK(b0, gb0, i1 + 1)) +
+            PICK(b1, gb1, i1 + 1);
+    bot.z = (0.0f + PICK(a1, ga1, i1 + 2)) + PICK(b1, gb1, i1 + 2);
+    bot.w = (((0.0f + PICK(a1, ga1, i1 + 3)) + PICK(a2, ga2, i1 + 3)) + PICK(b1, gb1, i1 + 3)) +
+            PICK(b2, gb2, i1 + 3);
+#undef PICK
+    *reinterpret_cast<float4*>(dp + i0) = top;
+    *reinterpret_cast<float4*>(dp + i1) = bot;
+  }
+}
+
 // Band height: the largest power-of-two-ish row count whose staging fits
 // `budget` bytes of shared memory; 0 rows means even one row does not fit.
 BandPlan plan_bands(const PoolShape& p, size_t budget) {
@@ -406,6 +502,19 @@ int sgb_maxpool_backward_f32(const float* x, const float* y, const float* dy, fl
     const dim3 grid(static_cast<unsigned>(planes), bp.bands);
     cudaStream_t s = as_stream(stream);
     const bool square = kh == kw && sh == sw && ph == pw && W % 4 == 0 && aligned16(x) && aligned16(dx);
+    if (square && kh == 3 && sh == 2 && ph == 1 && H % 2 == 0 && H >= 2) {
+      const int nb = (H + 31) / 32;
+      int rows = (H + nb - 1) / nb;
+      rows += rows & 1;
+      const int nbands = (H + rows - 1) / rows;
+      const size_t bytes = (static_cast<size_t>(rows + 3) * (W + 4) +
+                            2 * static_cast<size_t>((rows >> 1) + 2) * (p.OW + 1)) * sizeof(float);
+      if (bytes <= 48 * 1024 && nbands <= 65535) {
+        maxpool_bwd_k3s2p1_kernel<<<dim3(static_cast<unsigned>(planes), nbands), kBlock, bytes, s>>>(
+            x, dy, dx, H, W, p.OH, p.OW, rows);
+        return launch_status();
+      }
+    }
 #define SGB_POOL_FAST(KK, SS, PP)                                                       \
   if (square && kh == KK && sh == SS && ph == PP) {                                     \
     maxpool_bwd_band_fast_kernel<KK, SS, PP><<<grid, kBlock, smem, s>>>(x, dy, dx, p, bp); \

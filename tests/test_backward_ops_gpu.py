@@ -199,6 +199,9 @@ POOL_CASES = [
     ((3, 2, 6, 6), (2, 2), (3, 3), (0, 0)),          # stride > kernel: gaps get zero
     ((1, 2, 4, 8192), (2, 2), (2, 2), (0, 0)),       # rows too wide to stage: fallback kernel
     ((2, 3, 300, 40), (3, 3), (2, 2), (1, 1)),       # several bands per plane
+    ((2, 3, 38, 20), (3, 3), (2, 2), (1, 1)),        # uneven bands
+    ((1, 2, 2, 4), (3, 3), (2, 2), (1, 1)),          # smallest stem-geometry plane
+    ((2, 2, 9, 12), (3, 3), (2, 2), (1, 1)),         # odd height: general kernel
 ]
 
 
