@@ -64,6 +64,36 @@ __device__ __forceinline__ float load_sum(const float* __restrict__ g,
   return acc ? g[i] + acc[i] : g[i];
 }
 
+// The four values s = g (+ acc) of elements i .. i+3; out-of-range lanes get 0.
+// `vec` (host-checked 16-byte alignment of g and acc) turns the eight scalar
+// loads into two 128-bit loads.
+__device__ __forceinline__ void load_sum4(const float* __restrict__ g,
+                                          const float* __restrict__ acc, size_t i, size_t n,
+                                          bool vec, float (&s)[4]) {
+  if (vec && i + 4 <= n) {
+    const float4 a = *reinterpret_cast<const float4*>(g + i);
+    s[0] = a.x; s[1] = a.y; s[2] = a.z; s[3] = a.w;
+    if (acc) {
+      const float4 b = *reinterpret_cast<const float4*>(acc + i);
+      s[0] += b.x; s[1] += b.y; s[2] += b.z; s[3] += b.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[j] = i + j < n ? load_sum(g, acc, i + j) : 0.0f;
+  }
+}
+
+__device__ __forceinline__ void store4(float* __restrict__ p, size_t i, size_t n, bool vec,
+                                       const float (&v)[4]) {
+  if (vec && i + 4 <= n) {
+    *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i + j < n) p[i + j] = v[j];
+  }
+}
+
 // Exclusive offsets, in element order, of per-thread per-round counts c[r].
 // Returns the tile total.  smem: 32 unsigned.
 __device__ __forceinline__ unsigned tile_exclusive(const unsigned (&c)[kVecPerThread],
@@ -106,19 +136,17 @@ __device__ __forceinline__ unsigned tile_exclusive(const unsigned (&c)[kVecPerTh
 // kept value of element i: s = g (+ acc); |s| >= thr ? s : 0; sent iff != 0.
 __global__ void __launch_bounds__(kBlock)
 thr_count_kernel(const float* __restrict__ g, const float* __restrict__ acc, size_t n,
-                 float thr, unsigned* __restrict__ tile_counts) {
+                 float thr, unsigned* __restrict__ tile_counts, bool vec) {
   __shared__ unsigned sm[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
   unsigned cnt = 0;
 #pragma unroll
   for (int r = 0; r < kVecPerThread; ++r) {
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    float s[4];
+    load_sum4(g, acc, i, n, vec, s);      // out-of-range lanes are 0 and never counted
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (i + j < n) {
-        const float s = load_sum(g, acc, i + j);
-        cnt += (fabsf(s) >= thr && s != 0.0f) ? 1u : 0u;
-      }
+    for (int j = 0; j < 4; ++j) cnt += (fabsf(s[j]) >= thr && s[j] != 0.0f) ? 1u : 0u;
   }
   // block total (integer, order irrelevant)
   cnt = __reduce_add_sync(0xffffffffu, cnt);
@@ -131,62 +159,62 @@ thr_count_kernel(const float* __restrict__ g, const float* __restrict__ acc, siz
   }
 }
 
-// One CTA: exclusive scan of up to 2^31/4096 tile counts (two arrays at once),
-// totals to the state.  In-place: counts become offsets.
+// One CTA: exclusive scan of the tile counts (two arrays at once), totals to
+// the state.  In place: counts become offsets.  Every thread owns a contiguous
+// chunk: it adds the chunk up, a block-wide scan of the 1024 chunk totals gives
+// its base, and a second walk over the chunk writes the offsets.
 __global__ void __launch_bounds__(1024)
 scan_tiles_kernel(unsigned* __restrict__ a, unsigned* __restrict__ b, size_t tiles,
                   SelectState* __restrict__ st, int write_nnz) {
   __shared__ unsigned sa[32], sb[32];
-  __shared__ unsigned carry_a, carry_b;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  if (threadIdx.x == 0) { carry_a = 0; carry_b = 0; }
+  const size_t chunk = (tiles + 1023) / 1024;
+  const size_t lo = threadIdx.x * chunk, hi = lo + chunk < tiles ? lo + chunk : tiles;
+  unsigned ta = 0, tb = 0;
+  for (size_t i = lo; i < hi; ++i) {
+    ta += a[i];
+    if (b) tb += b[i];
+  }
+  unsigned xa = ta, xb = tb;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned ua = __shfl_up_sync(0xffffffffu, xa, o);
+    const unsigned ub = __shfl_up_sync(0xffffffffu, xb, o);
+    if (lane >= o) { xa += ua; xb += ub; }
+  }
+  if (lane == 31) { sa[w] = xa; sb[w] = xb; }
   __syncthreads();
-  for (size_t base = 0; base < tiles; base += 1024) {
-    const size_t i = base + threadIdx.x;
-    const unsigned va = i < tiles ? a[i] : 0u;
-    const unsigned vb = (b && i < tiles) ? b[i] : 0u;
-    unsigned xa = va, xb = vb;
+  if (w == 0) {
+    const unsigned va = sa[lane], vb = sb[lane];
+    unsigned ya = va, yb = vb;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      unsigned ua = __shfl_up_sync(0xffffffffu, xa, o);
-      unsigned ub = __shfl_up_sync(0xffffffffu, xb, o);
-      if (lane >= o) { xa += ua; xb += ub; }
+      const unsigned ua = __shfl_up_sync(0xffffffffu, ya, o);
+      const unsigned ub = __shfl_up_sync(0xffffffffu, yb, o);
+      if (lane >= o) { ya += ua; yb += ub; }
     }
-    if (lane == 31) { sa[w] = xa; sb[w] = xb; }
-    __syncthreads();
-    if (w == 0) {
-      unsigned ta = sa[lane], tb = sb[lane];
-      unsigned ya = ta, yb = tb;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        unsigned ua = __shfl_up_sync(0xffffffffu, ya, o);
-        unsigned ub = __shfl_up_sync(0xffffffffu, yb, o);
-        if (lane >= o) { ya += ua; yb += ub; }
-      }
-      sa[lane] = ya - ta;
-      sb[lane] = yb - tb;
-    }
-    __syncthreads();
-    const unsigned ea = carry_a + sa[w] + xa - va;
-    const unsigned eb = carry_b + sb[w] + xb - vb;
-    if (i < tiles) {
-      a[i] = ea;
-      if (b) b[i] = eb;
-    }
-    __syncthreads();
-    if (threadIdx.x == 1023) {
-      carry_a = ea + va;
-      carry_b = eb + vb;
-    }
-    __syncthreads();
+    sa[lane] = ya - va;
+    sb[lane] = yb - vb;
+    if (lane == 31 && write_nnz) st->nnz = static_cast<int>(ya);
   }
-  if (threadIdx.x == 0 && write_nnz) st->nnz = static_cast<int>(carry_a);
+  __syncthreads();
+  unsigned ra = sa[w] + xa - ta, rb = sb[w] + xb - tb;   // exclusive base of this chunk
+  for (size_t i = lo; i < hi; ++i) {
+    const unsigned va = a[i];
+    a[i] = ra;
+    ra += va;
+    if (b) {
+      const unsigned vb = b[i];
+      b[i] = rb;
+      rb += vb;
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kBlock)
 thr_write_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n, float thr,
                  const unsigned* __restrict__ tile_offsets, int* __restrict__ idx_out,
-                 float* __restrict__ val_out, const SelectState* __restrict__ st) {
+                 float* __restrict__ val_out, const SelectState* __restrict__ st, bool vec) {
   __shared__ unsigned sm[33];
   // packed payload [idx(nnz) | val(nnz)]: values start right after the indices
   if (!val_out) val_out = reinterpret_cast<float*>(idx_out) + st->nnz;
@@ -197,17 +225,16 @@ thr_write_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n,
   for (int r = 0; r < kVecPerThread; ++r) {
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
     c[r] = 0;
+    float s[4], res[4];
+    load_sum4(g, acc, i, n, vec, s);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      kept[r][j] = 0.0f;
-      if (i + j < n) {
-        const float s = load_sum(g, acc, i + j);
-        const float k = fabsf(s) >= thr ? s : 0.0f;
-        if (acc) acc[i + j] = s - k;   // residual kept locally
-        kept[r][j] = k;
-        c[r] += k != 0.0f ? 1u : 0u;
-      }
+      const float k = fabsf(s[j]) >= thr ? s[j] : 0.0f;   // out-of-range lanes: s == 0 -> k == 0
+      res[j] = s[j] - k;                                  // residual kept locally
+      kept[r][j] = k;
+      c[r] += k != 0.0f ? 1u : 0u;
     }
+    if (acc) store4(acc, i, n, vec, res);
   }
   tile_exclusive(c, excl, sm);
   const unsigned tile_off = tile_offsets[blockIdx.x];
@@ -242,7 +269,7 @@ template <int PASS>
 __global__ void __launch_bounds__(kBlock)
 topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
                  float* __restrict__ sum, size_t n, int mode,
-                 const SelectState* __restrict__ st, unsigned* __restrict__ hist) {
+                 const SelectState* __restrict__ st, unsigned* __restrict__ hist, bool vec) {
   constexpr int kBins = PASS == 0 ? kBins1 : kBins23;
   constexpr int kShift = PASS == 0 ? 20 : (PASS == 1 ? 10 : 0);
   __shared__ unsigned sh[kBins];
@@ -255,27 +282,33 @@ topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
 #pragma unroll
     for (int r = 0; r < kVecPerThread; ++r) {
       const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+      float s[4];
+      if (PASS == 0) {
+        load_sum4(g, acc, i, n, vec, s);
+        store4(sum, i, n, vec, s);
+      } else {
+        load_sum4(sum, nullptr, i, n, vec, s);
+      }
+      unsigned bin[4];
+      bool take[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const bool in = i + j < n;
-        float s = 0.f;
-        if (in) {
-          if (PASS == 0) {
-            s = load_sum(g, acc, i + j);
-            sum[i + j] = s;
-          } else {
-            s = sum[i + j];
-          }
-        }
-        const unsigned key = make_key(s, mode);
-        const bool take = in && (key & hi_mask) == prefix;
-        const unsigned bin = (key >> kShift) & (kBins - 1);
-        // warp-aggregated increment: lanes with the same bin elect a leader
-        const unsigned active = __ballot_sync(0xffffffffu, take);
-        if (take) {
-          const unsigned peers = __match_any_sync(active, bin);
-          if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&sh[bin], __popc(peers));
-        }
+        const unsigned key = make_key(s[j], mode);
+        take[j] = i + j < n && (key & hi_mask) == prefix;
+        bin[j] = (key >> kShift) & (kBins - 1);
+      }
+      // Fast path: every lane of the warp takes all four of its elements and
+      // they all fall into one bin (always true when every key ties): one
+      // shared-memory atomic per warp for 128 elements.
+      const bool mine_same = take[0] && take[1] && take[2] && take[3] && bin[0] == bin[1] &&
+                             bin[1] == bin[2] && bin[2] == bin[3];
+      const unsigned b0 = __shfl_sync(0xffffffffu, bin[0], 0);
+      if (__all_sync(0xffffffffu, mine_same && bin[0] == b0)) {
+        if ((threadIdx.x & 31) == 0) atomicAdd(&sh[b0], 128u);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (take[j]) atomicAdd(&sh[bin[j]], 1u);
       }
     }
   }
@@ -284,30 +317,65 @@ topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
     if (sh[b]) atomicAdd(&hist[b], sh[b]);
 }
 
-// One CTA: walk the histogram from the highest bin down until `remaining`
-// elements are covered; fix that bin's bits into the prefix.  Clears the
-// histogram for the next pass.
+// One CTA: find the bin, counted from the top, in which the cumulative count
+// reaches `remaining`, and fix that bin's bits into the prefix.  Each of the
+// 1024 threads owns kBins/1024 consecutive bins (descending), a block-wide
+// inclusive scan gives every thread the count of all higher bins, and exactly
+// one thread finds the crossing inside its own bins.  Clears the histogram for
+// the next pass.
 template <int PASS>
 __global__ void __launch_bounds__(1024)
 topk_pick_kernel(unsigned* __restrict__ hist, SelectState* __restrict__ st, unsigned k_total) {
   constexpr int kBins = PASS == 0 ? kBins1 : kBins23;
   constexpr int kShift = PASS == 0 ? 20 : (PASS == 1 ? 10 : 0);
-  __shared__ unsigned sh[kBins];
-  for (int b = threadIdx.x; b < kBins; b += 1024) {
-    sh[b] = hist[b];
+  constexpr int kPer = kBins / 1024;                 // 4 or 1 bins per thread
+  __shared__ unsigned warp_tot[32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  // thread t owns descending bins  kBins-1 - t*kPer - j,  j = 0 .. kPer-1
+  unsigned mine[kPer], local = 0;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int b = kBins - 1 - (threadIdx.x * kPer + j);
+    mine[j] = hist[b];
     hist[b] = 0;
+    local += mine[j];
+  }
+  unsigned incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned u = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += u;
+  }
+  if (lane == 31) warp_tot[w] = incl;
+  __syncthreads();
+  if (w == 0) {
+    const unsigned t = warp_tot[lane];
+    unsigned x = t;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned u = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += u;
+    }
+    warp_tot[lane] = x - t;                          // exclusive over warps
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned remaining = PASS == 0 ? k_total : st->remaining;
-    unsigned prefix = PASS == 0 ? 0u : st->prefix;
-    int b = kBins - 1;
-    for (; b > 0; --b) {
-      if (sh[b] >= remaining) break;
-      remaining -= sh[b];
+  const unsigned remaining0 = PASS == 0 ? k_total : st->remaining;
+  const unsigned prefix0 = PASS == 0 ? 0u : st->prefix;
+  unsigned above = warp_tot[w] + incl - local;       // elements in bins above this thread's
+  __syncthreads();
+  // crossing thread: above < remaining0 <= above + local.  If the total is
+  // short (cannot happen for k <= n) the lowest bin takes whatever is left.
+  const bool last = threadIdx.x == 1023;
+  if (above < remaining0 && (remaining0 <= above + local || last)) {
+    unsigned remaining = remaining0 - above;
+    int b = kBins - 1 - threadIdx.x * kPer;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      if (mine[j] >= remaining || (last && j == kPer - 1)) break;
+      remaining -= mine[j];
+      --b;
     }
-    // b == 0 falls through: whatever is left comes from the lowest bin
-    prefix |= static_cast<unsigned>(b) << kShift;
+    const unsigned prefix = prefix0 | (static_cast<unsigned>(b) << kShift);
     st->prefix = prefix;
     st->remaining = remaining;
     if (PASS == 2) {
@@ -321,7 +389,7 @@ topk_pick_kernel(unsigned* __restrict__ hist, SelectState* __restrict__ st, unsi
 __global__ void __launch_bounds__(kBlock)
 topk_count_kernel(const float* __restrict__ sum, size_t n, int mode,
                   const SelectState* __restrict__ st, unsigned* __restrict__ tile_gt,
-                  unsigned* __restrict__ tile_eq) {
+                  unsigned* __restrict__ tile_eq, bool vec) {
   __shared__ unsigned sg[8], se[8];
   const unsigned T = st->threshold;
   const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
@@ -329,10 +397,12 @@ topk_count_kernel(const float* __restrict__ sum, size_t n, int mode,
 #pragma unroll
   for (int r = 0; r < kVecPerThread; ++r) {
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    float s[4];
+    load_sum4(sum, nullptr, i, n, vec, s);
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       if (i + j < n) {
-        const unsigned key = make_key(sum[i + j], mode);
+        const unsigned key = make_key(s[j], mode);
         gt += key > T;
         eq += key == T;
       }
@@ -355,7 +425,7 @@ __global__ void __launch_bounds__(kBlock)
 topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t n, int mode,
                   const SelectState* __restrict__ st, const unsigned* __restrict__ gt_off,
                   const unsigned* __restrict__ eq_off, int* __restrict__ idx_out,
-                  float* __restrict__ val_out) {
+                  float* __restrict__ val_out, bool vec) {
   __shared__ unsigned sm[33];
   const unsigned T = st->threshold, quota = st->quota;
   const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
@@ -366,12 +436,11 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
   for (int r = 0; r < kVecPerThread; ++r) {
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
     cg[r] = 0; ce[r] = 0;
+    load_sum4(sum, nullptr, i, n, vec, s[r]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       flag[r][j] = 0;
-      s[r][j] = 0.f;
       if (i + j < n) {
-        s[r][j] = sum[i + j];
         const unsigned key = make_key(s[r][j], mode);
         if (key > T) { flag[r][j] = 1; ++cg[r]; }
         else if (key == T) { flag[r][j] = 2; ++ce[r]; }
@@ -385,6 +454,7 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
   for (int r = 0; r < kVecPerThread; ++r) {
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
     unsigned ng = g0 + eg[r], ne = e0 + ee[r];
+    float res[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       bool sel = false;
@@ -398,10 +468,11 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
         idx_out[pos] = static_cast<int>(i + j + 1);
         val_out[pos] = s[r][j];
       }
-      if (acc && i + j < n) acc[i + j] = sel ? 0.0f : s[r][j];  // s - s == 0 when sent
+      res[j] = sel ? 0.0f : s[r][j];  // s - s == 0 when sent
       if (flag[r][j] == 1) ++ng;
       if (flag[r][j] == 2) ++ne;
     }
+    if (acc) store4(acc, i, n, vec, res);
   }
 }
 
@@ -444,7 +515,7 @@ int sparse_threshold_count(const float* g, const float* acc, size_t n, float thr
     return SGB_ERR_WORKSPACE;
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
-  thr_count_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts);
+  thr_count_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, aligned16(g) && (!acc || aligned16(acc)));
   scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_counts, nullptr, tiles, w.state, 1);
   cudaError_t e = cudaMemcpyAsync(nnz_dev, &w.state->nnz, sizeof(int), cudaMemcpyDeviceToDevice, s);
   if (e != cudaSuccess) return note_cuda_error(e);
@@ -456,7 +527,7 @@ int sparse_threshold_write_packed(const float* g, float* acc, size_t n, float th
   if (n == 0) return SGB_OK;
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
-  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, payload, nullptr, w.state);
+  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, payload, nullptr, w.state, aligned16(g) && (!acc || aligned16(acc)));
   return launch_status();
 }
 
@@ -491,11 +562,11 @@ int sgb_sparse_threshold_f32(const float* g, float* acc, size_t n, float thr, in
   if (st != SGB_OK) return st;
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
-  thr_count_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts);
+  thr_count_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, aligned16(g) && (!acc || aligned16(acc)));
   scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_counts, nullptr, tiles, w.state, 1);
   cudaError_t e = cudaMemcpyAsync(nnz_dev, &w.state->nnz, sizeof(int), cudaMemcpyDeviceToDevice, s);
   if (e != cudaSuccess) return note_cuda_error(e);
-  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, idx_out, val_out, w.state);
+  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, idx_out, val_out, w.state, aligned16(g) && (!acc || aligned16(acc)));
   return launch_status();
 }
 
@@ -512,18 +583,19 @@ int sgb_sparse_topk_f32(const float* g, float* acc, float* sum_scratch, size_t n
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
   const unsigned hgrid = capped_grid(tiles, 1, 8);
+  const bool vec = aligned16(g) && (!acc || aligned16(acc)) && aligned16(sum_scratch);
   cudaError_t e = cudaMemsetAsync(w.hist, 0, kBins1 * sizeof(unsigned), s);
   if (e != cudaSuccess) return note_cuda_error(e);
-  topk_hist_kernel<0><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist);
+  topk_hist_kernel<0><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<0><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
-  topk_hist_kernel<1><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist);
+  topk_hist_kernel<1><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<1><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
-  topk_hist_kernel<2><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist);
+  topk_hist_kernel<2><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<2><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
-  topk_count_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, n, mode, w.state, w.tile_gt, w.tile_eq);
+  topk_count_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, n, mode, w.state, w.tile_gt, w.tile_eq, vec);
   scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_gt, w.tile_eq, tiles, w.state, 0);
   topk_write_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, acc, n, mode, w.state, w.tile_gt,
-                                             w.tile_eq, idx_out, val_out);
+                                             w.tile_eq, idx_out, val_out, vec);
   return launch_status();
 }
 
