@@ -24,6 +24,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "resnet50_backward_sync_update_images_per_sec"
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the batch-norm
+# backward kernels, averaged per call over one step, from the ncu capture
+# summarised in profiles/bench_resnet50_launch_list.md (fused / call-pattern plan).
+NCU_BN_TRAFFIC_PER_CALL = {True: 77.7e6, False: 65.7e6}
 BATCH = 32
 CPU_SAMPLE_BATCH = 8
 
@@ -156,7 +160,7 @@ def main():
     from singa_b200 import _lib
     from singa_b200.communicator import Communicator, NcclIdHolder
     from singa_b200.hot_path import HotPathGPU
-    from singa_b200.resnet50_path import algorithmic_bytes, build_plan
+    from singa_b200.resnet50_path import algorithmic_bytes, build_plan, fuse_plan
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback "
@@ -173,7 +177,9 @@ def main():
 
     K, W = max(args.steps, 1), max(args.warmup, 3)
     fused = not args.call_pattern
-    plan = build_plan(batch=BATCH, fused=fused)
+    plan = build_plan(batch=BATCH, fused=False)        # the reference's call sequence ...
+    if fused:
+        plan = fuse_plan(plan)                         # ... rewritten by the peephole pass
     path = HotPathGPU(plan, communicator=comm, world=world, seed=1000 + rank, dist_option=args.dist_option)
     by_family, nparam = algorithmic_bytes(plan, world)
 
@@ -282,7 +288,8 @@ def main():
     bn_launches = sum(1 for o in plan["ops"] if o.kind in bn_keys)
     achieved = bn_bytes / bn_ms / 1e6
     roofline = {"bound": "hbm", "kernel": "batch-norm backward (reduce + apply)", "achieved": round(achieved, 1),
-                "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "traffic": NCU_BN_TRAFFIC_PER_CALL[fused],
                 "peak_kind": peak_kind, "launches_per_step": bn_launches,
                 "algorithmic_bytes_per_launch": bn_bytes / max(bn_launches, 1),
                 "avg_launch_ms": bn_ms / max(bn_launches, 1)}

@@ -170,10 +170,27 @@ scan_tiles_kernel(unsigned* __restrict__ a, unsigned* __restrict__ b, size_t til
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const size_t chunk = (tiles + 1023) / 1024;
   const size_t lo = threadIdx.x * chunk, hi = lo + chunk < tiles ? lo + chunk : tiles;
+  constexpr int kReg = 32;                 // chunks up to 32 entries live in registers
+  const bool in_regs = chunk <= kReg;
+  unsigned ra_[kReg], rb_[kReg];
   unsigned ta = 0, tb = 0;
-  for (size_t i = lo; i < hi; ++i) {
-    ta += a[i];
-    if (b) tb += b[i];
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < kReg; ++j) {       // independent loads, one round trip
+      const size_t i = lo + j;
+      ra_[j] = (j < static_cast<int>(chunk) && i < tiles) ? a[i] : 0u;
+      rb_[j] = (b && j < static_cast<int>(chunk) && i < tiles) ? b[i] : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < kReg; ++j) {
+      ta += ra_[j];
+      tb += rb_[j];
+    }
+  } else {
+    for (size_t i = lo; i < hi; ++i) {
+      ta += a[i];
+      if (b) tb += b[i];
+    }
   }
   unsigned xa = ta, xb = tb;
 #pragma unroll
@@ -199,6 +216,21 @@ scan_tiles_kernel(unsigned* __restrict__ a, unsigned* __restrict__ b, size_t til
   }
   __syncthreads();
   unsigned ra = sa[w] + xa - ta, rb = sb[w] + xb - tb;   // exclusive base of this chunk
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < kReg; ++j) {
+      const size_t i = lo + j;
+      if (j < static_cast<int>(chunk) && i < tiles) {
+        a[i] = ra;
+        ra += ra_[j];
+        if (b) {
+          b[i] = rb;
+          rb += rb_[j];
+        }
+      }
+    }
+    return;
+  }
   for (size_t i = lo; i < hi; ++i) {
     const unsigned va = a[i];
     a[i] = ra;
@@ -447,8 +479,17 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
       }
     }
   }
-  tile_exclusive(cg, eg, sm);
-  tile_exclusive(ce, ee, sm);
+  {  // one scan for both counters: greater in the high half, equal in the low half (each <= 4096)
+    unsigned packed[kVecPerThread], excl[kVecPerThread];
+#pragma unroll
+    for (int r = 0; r < kVecPerThread; ++r) packed[r] = (cg[r] << 16) | ce[r];
+    tile_exclusive(packed, excl, sm);
+#pragma unroll
+    for (int r = 0; r < kVecPerThread; ++r) {
+      eg[r] = excl[r] >> 16;
+      ee[r] = excl[r] & 0xffffu;
+    }
+  }
   const unsigned g0 = gt_off[blockIdx.x], e0 = eq_off[blockIdx.x];
 #pragma unroll
   for (int r = 0; r < kVecPerThread; ++r) {

@@ -211,6 +211,63 @@ def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4,
     return dict(tensors=T, ops=ops, params=params, grad_order=grad_order, batch=B)
 
 
+READS = {
+    "relu_bwd": ("dy", "x"), "add_relu_bwd": ("dy_a", "dy_b", "x"), "add_out": ("a", "b"),
+    "bn_bwd": ("dy", "x", "scale", "mean", "invstd"),
+    "bn_relu_bwd": ("dy", "relu_x", "x", "scale", "mean", "invstd"),
+    "maxpool_bwd": ("x", "y", "dy"), "avgpool_bwd": ("dy",), "softmax": ("x",), "ce_fwd": ("p", "t"),
+    "sum_all": ("x",), "ce_bwd": ("p", "t"), "ce_grad": ("p", "t"), "scale": ("x",), "sum_rows": ("M",),
+}
+
+
+def fuse_plan(plan):
+    """Peephole fusion over a recorded op list (the counterpart of a pass over
+    the reference's buffered Graph nodes, keyed on the op kinds):
+
+      add_out(a, b -> t) ; relu_bwd(dy=t, x -> dx)       =>  add_relu_bwd(a, b, x -> dx)
+      relu_bwd(dy, x=r -> m) ; bn_bwd(dy=m, ...)         =>  bn_relu_bwd(dy, relu_x=r, ...)
+      ce_bwd(p, t -> g) ; scale(g, c)                    =>  ce_grad(p, t, c -> g)
+
+    A pair is fused only when the intermediate tensor has no other reader;
+    the intermediate then disappears from the plan.  Results are unchanged
+    bit for bit (the fused kernels perform the same roundings)."""
+    ops = list(plan["ops"])
+    readers = {}
+    for i, op in enumerate(ops):
+        for key in READS.get(op.kind, ()):
+            readers.setdefault(op.args[key], []).append(i)
+    dead, out, T = set(), [], dict(plan["tensors"])
+    producer = {}
+    for i, op in enumerate(ops):
+        k, a = op.kind, op.args
+        if k == "relu_bwd" and a["dy"] in producer and ops[producer[a["dy"]]].kind == "add_out" \
+                and readers.get(a["dy"]) == [i]:
+            j = producer[a["dy"]]
+            src = ops[j].args
+            dead.add(j)
+            T.pop(a["dy"], None)
+            op = Op("add_relu_bwd", dict(dy_a=src["a"], dy_b=src["b"], x=a["x"], dx=a["dx"]))
+        elif k == "bn_bwd" and a["dy"] in producer and ops[producer[a["dy"]]].kind == "relu_bwd" \
+                and readers.get(a["dy"]) == [i]:
+            j = producer[a["dy"]]
+            src = ops[j].args
+            dead.add(j)
+            T.pop(a["dy"], None)
+            op = Op("bn_relu_bwd", dict(a, dy=src["dy"], relu_x=src["x"]))
+        elif k == "scale" and a["x"] in producer and ops[producer[a["x"]]].kind == "ce_bwd":
+            j = producer[a["x"]]
+            src = ops[j].args
+            dead.add(j)
+            op = Op("ce_grad", dict(p=src["p"], t=src["t"], scale=a["c"], grad=a["x"]))
+        out.append(op)
+        for key in ("dx", "out", "grad", "y", "loss", "v"):
+            if key in op.args and isinstance(op.args[key], str):
+                producer[op.args[key]] = i
+    # a fused relu_bwd may itself have consumed an add_out: drop everything marked dead
+    fused_ops = [op for i, op in enumerate(out) if i not in dead]
+    return dict(plan, ops=fused_ops, tensors=T)
+
+
 def numel(shape):
     n = 1
     for s in shape:

@@ -4,7 +4,7 @@ import numpy as np
 
 from oracle import comm as ocomm
 from singa_b200.opt import plan_buckets
-from singa_b200.resnet50_path import algorithmic_bytes, build_plan, numel
+from singa_b200.resnet50_path import algorithmic_bytes, build_plan, fuse_plan, numel
 
 
 def test_resnet50_plan_sizes():
@@ -55,3 +55,22 @@ def test_oracle_topk_modes():
     assert ocomm.topk_select(s, 2, "compat").tolist() == [1, 5]          # tie 2.5/2.4 -> lower index
     assert ocomm.topk_select(s * 0.1, 3, "compat").tolist() == [0, 1, 2]  # everything ties at 0
     assert ocomm.topk_count(0.01, 100000000) == 1000000
+
+
+def test_peephole_pass_reproduces_the_hand_fused_plan():
+    def key(plan):
+        return [(o.kind, sorted((k, str(v)) for k, v in o.args.items())) for o in plan["ops"]]
+    for kw in (dict(), dict(batch=4, image=64, num_classes=10, blocks=(2, 1, 1, 1))):
+        by_hand = build_plan(fused=True, **kw)
+        by_pass = fuse_plan(build_plan(fused=False, **kw))
+        assert key(by_hand) == key(by_pass)
+        assert set(by_pass["tensors"]) == set(by_hand["tensors"])
+    # an intermediate with a second reader must not be fused away
+    from singa_b200.resnet50_path import Op
+    plan = build_plan(batch=2, image=64, num_classes=10, blocks=(1, 1, 1, 1))
+    ops = list(plan["ops"])
+    i = next(k for k, o in enumerate(ops) if o.kind == "relu_bwd" and ops[k + 1].kind == "bn_bwd"
+             and ops[k + 1].args["dy"] == o.args["dx"])
+    extra = Op("sum_all", dict(x=ops[i].args["dx"], out="loss"))
+    fused = fuse_plan(dict(plan, ops=ops[:i + 2] + [extra] + ops[i + 2:]))
+    assert any(o.kind == "relu_bwd" and o.args["dx"] == ops[i].args["dx"] for o in fused["ops"])
