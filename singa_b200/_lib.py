@@ -65,7 +65,12 @@ def lib():
             raise ImportError(
                 "libsgb.so is not built (%s). Run `python -m singa_b200.build`; "
                 "there is no CPU fallback." % LIB_PATH)
-        handle = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        # libsgb.so needs libnccl.so.2.  torch ships its own (newer) NCCL under the
+        # same soname and must find THAT one already loaded, otherwise
+        # libtorch_cuda fails to resolve its symbols: import torch first, then
+        # our library binds to the copy torch loaded.
+        import torch  # noqa: F401
+        handle = C.CDLL(LIB_PATH)
         for name, restype, argtypes in declarations():
             fn = getattr(handle, name)   # AttributeError if the symbol is missing
             fn.restype = restype

@@ -2,6 +2,8 @@
 include/sgb.h declares (no compute calls here)."""
 import ctypes
 
+import torch  # noqa: F401  (loads torch's NCCL before libsgb.so binds to libnccl.so.2)
+
 from singa_b200 import _lib, build
 
 
