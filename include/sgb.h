@@ -224,6 +224,20 @@ int sgb_bn_backward_f32(const float *x, const float *dy, const float *scale,
                         const float *mean, const float *invstd, float *dx,
                         float *dscale, float *dbias, int N, int C, int HW,
                         void *ws, size_t ws_bytes, void *stream);
+/* Forward partner: training-mode batch norm.  y = scale * (x - mean) * invstd
+ * + bias with batch statistics; save_mean / save_invstd (= 1/sqrt(biased var
+ * + eps)) are what sgb_bn_backward_f32 consumes; running_mean / running_var
+ * are updated in place as r = (1 - factor) * r + factor * batch value, the
+ * variance unbiased.  Replaces GpuBatchNormForwardTraining
+ * (src/model/operation/batchnorm.cc:287-329, cudnnBatchNormalizationForward
+ * Training; the reference passes eps = CUDNN_BN_MIN_EPSILON).  HW = 1 is the
+ * per-activation mode.  Workspace as for the backward. */
+int sgb_bn_forward_training_f32(const float *x, const float *scale,
+                                const float *bias, float *running_mean,
+                                float *running_var, float factor, float eps,
+                                float *y, float *save_mean, float *save_invstd,
+                                int N, int C, int HW, void *ws, size_t ws_bytes,
+                                void *stream);
 /* Batch-norm backward for callers that can neither allocate device memory nor
  * hand in a workspace.  (No counterpart in the reference: this entry point
  * exists only in this library.)  Typical callers: an operator running inside

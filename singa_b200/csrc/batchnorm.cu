@@ -125,7 +125,9 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                     const float2* __restrict__ partial, int slices, float* __restrict__ dx,
                     float* __restrict__ dscale, float* __restrict__ dbias, BnShape sh) {
   __shared__ float coef[4];
-  const int c = blockIdx.y;
+  // channels in DESCENDING order: the reduce pass walked them ascending, so the
+  // last ones it touched are the ones most likely still in L2
+  const int c = sh.C - 1 - blockIdx.y;
   // issue this thread's loads first, so that their latency overlaps the
   // partial-sum lookup below
   const int unit = blockIdx.x * kBlock + threadIdx.x;
@@ -372,6 +374,122 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   }
 }
 
+// ------------------------------------------- single pass, channel groups
+// Planes whose size is not a multiple of four floats (7x7 = 49) cannot be
+// moved with 16-byte accesses one channel at a time, but G = 4 / gcd(HW, 4)
+// ADJACENT channels of one sample form a contiguous, 16-byte aligned run of
+// G*HW floats.  One CTA stages the G channels of all N samples (G*N*HW*8
+// bytes of shared memory) with 16-byte copies, reduces every channel with a
+// sub-group of its threads from shared memory, overwrites the staged dy with
+// dx in place and streams it back with 16-byte stores.
+template <bool MASK, int G>
+__global__ void __launch_bounds__(kBlock)
+bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                    const float* __restrict__ relu_in, const float* __restrict__ scale,
+                    const float* __restrict__ mean, const float* __restrict__ invstd,
+                    float* __restrict__ dx, float* __restrict__ dscale,
+                    float* __restrict__ dbias, BnShape sh) {
+  extern __shared__ __align__(16) float stage[];
+  constexpr int kSub = kBlock / G;                    // threads per channel
+  __shared__ float red[2][kBlock / 32];
+  __shared__ float coef[G][4];
+  const int c0 = blockIdx.x * G;
+  const int run = G * sh.HW;                          // floats per sample, multiple of 4
+  const int run4 = run >> 2;
+  const int units = sh.N * run4;
+  float* sx = stage;
+  float* sg = stage + static_cast<size_t>(sh.N) * run;
+  const size_t sample_stride = static_cast<size_t>(sh.C) * sh.HW;
+  const size_t base = static_cast<size_t>(c0) * sh.HW;
+  for (int u = threadIdx.x; u < units; u += kBlock) {
+    const int n = u / run4, q = u - n * run4;
+    const size_t off = n * sample_stride + base + 4 * static_cast<size_t>(q);
+    cp_async16(sx + 4 * u, x + off);
+    if (MASK) {
+      Vec4f g, m;
+      g.u = ld128(dy + off);
+      m.u = ld128(relu_in + off);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) g.f[k] = m.f[k] > 0 ? g.f[k] : 0.0f;
+      *reinterpret_cast<uint4*>(sg + 4 * u) = g.u;
+    } else {
+      cp_async16(sg + 4 * u, dy + off);
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  // channel g is handled by threads [g*kSub, (g+1)*kSub): element (n, i) of the
+  // channel sits at staged offset n*run + g*HW + i
+  const int g = threadIdx.x / kSub, t = threadIdx.x - g * kSub;
+  const int c = c0 + g;
+  const float mu = mean[c];
+  const int per = sh.N * sh.HW;
+  float s_dy = 0.f, s_dyx = 0.f;
+  for (int e = t; e < per; e += kSub) {
+    const int n = e / sh.HW, i = e - n * sh.HW;
+    const int l = n * run + g * sh.HW + i;
+    s_dy += sg[l];
+    s_dyx += sg[l] * (sx[l] - mu);
+  }
+  // reduce inside the sub-group (kSub is a multiple of 32: whole warps per channel)
+  s_dy = warp_sum(s_dy);
+  s_dyx = warp_sum(s_dyx);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) {
+    red[0][wid] = s_dy;
+    red[1][wid] = s_dyx;
+  }
+  __syncthreads();
+  if (t == 0) {
+    constexpr int kWarpsPer = kSub / 32;
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < kWarpsPer; ++w) {
+      a += red[0][g * kWarpsPer + w];
+      b += red[1][g * kWarpsPer + w];
+    }
+    const float r = invstd[c];
+    const float inv_m = 1.0f / (static_cast<float>(sh.N) * static_cast<float>(sh.HW));
+    const float ds = b * r;
+    coef[g][0] = scale[c] * r;
+    coef[g][1] = a * inv_m;
+    coef[g][2] = ds * r * inv_m;
+    coef[g][3] = mu;
+    dscale[c] = ds;
+    dbias[c] = a;
+  }
+  __syncthreads();
+  const float k_ = coef[g][0], am = coef[g][1], bm = coef[g][2];
+  for (int e = t; e < per; e += kSub) {
+    const int n = e / sh.HW, i = e - n * sh.HW;
+    const int l = n * run + g * sh.HW + i;
+    sg[l] = k_ * (sg[l] - am - (sx[l] - mu) * bm);          // dx in place
+  }
+  __syncthreads();
+  for (int u = threadIdx.x; u < units; u += kBlock) {
+    const int n = u / run4, q = u - n * run4;
+    const size_t off = n * sample_stride + base + 4 * static_cast<size_t>(q);
+    st128(dx + off, *reinterpret_cast<const uint4*>(sg + 4 * u));
+  }
+}
+
+template <bool MASK, int G>
+int launch_group(const float* x, const float* dy, const float* relu_in, const float* scale,
+                 const float* mean, const float* invstd, float* dx, float* dscale, float* dbias,
+                 BnShape sh, cudaStream_t s) {
+  auto kernel = bn_bwd_group_kernel<MASK, G>;
+  const size_t smem = static_cast<size_t>(G) * sh.N * sh.HW * 8;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_set[dev] = true;
+  }
+  kernel<<<sh.C / G, kBlock, smem, s>>>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh);
+  return launch_status();
+}
+
 // Cluster size (1, 2, 4 or 8) and per-CTA share for the single-pass kernel;
 // returns 0 when a channel does not fit 8 CTAs' shared memory.
 int env_int(const char* name, int dflt) {
@@ -490,6 +608,17 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
   const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(dy) && aligned16(dx) &&
                    (!MASK || aligned16(relu_in));
   const BnShape sh{N, C, HW};
+  if (!vec && HW > 1 && aligned16(x) && aligned16(dy) && aligned16(dx) && (!MASK || aligned16(relu_in))) {
+    // odd planes: groups of adjacent channels make 16-byte runs (7x7 layers)
+    const int G = (HW % 2) ? 4 : 2;
+    // worth it only when the groups still fill the machine (fewer, larger CTAs otherwise lose)
+    if ((HW * G) % 4 == 0 && C % G == 0 && static_cast<long long>(G) * per_channel * 8 <= 100 * 1024 &&
+        C / G >= 2 * sm_count()) {
+      if (G == 4)
+        return launch_group<MASK, 4>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
+      return launch_group<MASK, 2>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
+    }
+  }
   {
     int per_cta = 0;
     const int cs = cluster_plan(vec ? per_channel / 4 : per_channel, vec ? 16 : 4, &per_cta);
@@ -516,6 +645,236 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
     bn_bwd_apply_kernel<false, MASK><<<g2, kBlock, 0, s>>>(x, dy, relu_in, scale, mean, invstd,
                                                            partial, slices, dx, dscale, dbias, sh);
   }
+  return launch_status();
+}
+
+// ------------------------------------------------------------ forward (training)
+// Forward partner of the backward kernels: batch statistics, normalisation and
+// running-statistics update in one pass over x.  A cluster stages its channel
+// in shared memory once; mean and the centred sum of squares are two reductions
+// over the staged copy (no E[x^2]-E[x]^2 cancellation), each exchanged through
+// distributed shared memory.  Emits what the backward consumes: save_mean and
+// save_invstd = 1/sqrt(biased_var + eps).  Running statistics follow cuDNN:
+// r = (1-f)*r + f*batch_value, with the UNBIASED variance (M/(M-1)).
+template <bool VEC, int T>
+__global__ void __launch_bounds__(T)
+bn_fwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+                      const float* __restrict__ bias, float* __restrict__ running_mean,
+                      float* __restrict__ running_var, float factor, float eps,
+                      float* __restrict__ y, float* __restrict__ save_mean,
+                      float* __restrict__ save_invstd, BnShape sh, int per_cta) {
+  extern __shared__ __align__(16) float stage[];
+  __shared__ float red[T / 32];
+  __shared__ float parts[2][16];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cs = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int c = blockIdx.x / cs;
+  cluster.barrier_arrive();
+  constexpr int kW = VEC ? 4 : 1;
+  const int hwu = sh.HW / kW, total = sh.N * hwu;
+  const int u0 = min(rank * per_cta, total), u1 = min(u0 + per_cta, total);
+  const int first = u0 + threadIdx.x;
+  const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
+  const size_t chan_off = static_cast<size_t>(c) * sh.HW;
+  {
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1; u += T, w.next()) {
+      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * kW;
+      if (VEC) cp_async16(stage + (u - u0) * 4, x + off);
+      else stage[u - u0] = x[off];
+    }
+  }
+  if (VEC) cp_async_wait_all();
+  const float inv_m = 1.0f / (static_cast<float>(sh.N) * static_cast<float>(sh.HW));
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  constexpr int kWarps = T / 32;
+  auto cluster_total = [&](float v, int slot) -> float {
+    v = warp_sum(v);
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+      float p = lane < kWarps ? red[lane] : 0.0f;
+      p = warp_sum(p);
+      if (slot == 0) cluster.barrier_wait();      // first exchange: peers must have started
+      if (lane < cs) *cluster.map_shared_rank(&parts[slot][rank], lane) = p;
+    } else if (slot == 0) {
+      cluster.barrier_wait();
+    }
+    cluster.sync();
+    float t = 0.f;
+    for (int r = 0; r < cs; ++r) t += parts[slot][r];
+    return t;
+  };
+  float s = 0.f;
+  for (int u = first; u < u1; u += T) {
+    const int l = (u - u0) * kW;
+#pragma unroll
+    for (int k = 0; k < kW; ++k) s += stage[l + k];
+  }
+  const float mu = cluster_total(s, 0) * inv_m;
+  float q = 0.f;
+  for (int u = first; u < u1; u += T) {
+    const int l = (u - u0) * kW;
+#pragma unroll
+    for (int k = 0; k < kW; ++k) {
+      const float d = stage[l + k] - mu;
+      q += d * d;
+    }
+  }
+  const float var = cluster_total(q, 1) * inv_m;      // biased
+  const float invstd = 1.0f / sqrtf(var + eps);
+  if (rank == 0 && threadIdx.x == 0) {
+    save_mean[c] = mu;
+    save_invstd[c] = invstd;
+    const float m = static_cast<float>(sh.N) * static_cast<float>(sh.HW);
+    const float unbiased = m > 1.0f ? var * (m / (m - 1.0f)) : var;
+    running_mean[c] = (1.0f - factor) * running_mean[c] + factor * mu;
+    running_var[c] = (1.0f - factor) * running_var[c] + factor * unbiased;
+  }
+  const float g = scale[c] * invstd, b = bias[c];
+  {
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1; u += T, w.next()) {
+      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * kW;
+      const int l = (u - u0) * kW;
+      if (VEC) {
+        Vec4f v, o;
+        v.u = *reinterpret_cast<const uint4*>(stage + l);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o.f[k] = (v.f[k] - mu) * g + b;
+        st128(y + off, o.u);
+      } else {
+        y[off] = (stage[l] - mu) * g + b;
+      }
+    }
+  }
+}
+
+// Fallback for channels that do not fit a cluster: three streaming kernels
+// (mean partials, centred-square partials, normalise), partials in workspace.
+template <int PHASE>
+__global__ void __launch_bounds__(kBlock)
+bn_fwd_partial_kernel(const float* __restrict__ x, const float* __restrict__ mean_in,
+                      float* __restrict__ partial, BnShape sh, int per_slice) {
+  __shared__ float sm[32];
+  const int c = blockIdx.y, slice = blockIdx.x;
+  const int total = sh.N * sh.HW;
+  const int i0 = slice * per_slice, i1 = min(i0 + per_slice, total);
+  const float mu = PHASE == 1 ? mean_in[c] : 0.0f;
+  float acc = 0.f;
+  UnitWalk w(i0 + threadIdx.x, kBlock, sh.HW);
+  for (int i = i0 + threadIdx.x; i < i1; i += kBlock, w.next()) {
+    const float v = x[(static_cast<size_t>(w.n) * sh.C + c) * sh.HW + w.q];
+    acc += PHASE == 0 ? v : (v - mu) * (v - mu);
+  }
+  acc = block_sum(acc, sm);
+  if (threadIdx.x == 0) partial[static_cast<size_t>(c) * gridDim.x + slice] = acc;
+}
+
+__global__ void bn_fwd_finish_kernel(int phase, const float* __restrict__ partial, int slices,
+                                     float* __restrict__ save_mean, float* __restrict__ save_invstd,
+                                     float* __restrict__ running_mean, float* __restrict__ running_var,
+                                     float factor, float eps, BnShape sh) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= sh.C) return;
+  float t = 0.f;
+  for (int k = 0; k < slices; ++k) t += partial[static_cast<size_t>(c) * slices + k];
+  const float m = static_cast<float>(sh.N) * static_cast<float>(sh.HW);
+  if (phase == 0) {
+    save_mean[c] = t / m;
+  } else {
+    const float var = t / m;
+    save_invstd[c] = 1.0f / sqrtf(var + eps);
+    const float unbiased = m > 1.0f ? var * (m / (m - 1.0f)) : var;
+    running_mean[c] = (1.0f - factor) * running_mean[c] + factor * save_mean[c];
+    running_var[c] = (1.0f - factor) * running_var[c] + factor * unbiased;
+  }
+}
+
+__global__ void __launch_bounds__(kBlock)
+bn_fwd_normalize_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+                        const float* __restrict__ bias, const float* __restrict__ mean,
+                        const float* __restrict__ invstd, float* __restrict__ y, BnShape sh) {
+  const int c = blockIdx.y;
+  const int i = blockIdx.x * kBlock + threadIdx.x;
+  if (i >= sh.N * sh.HW) return;
+  const int n = i / sh.HW, q = i - n * sh.HW;
+  const size_t off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + q;
+  y[off] = (x[off] - mean[c]) * (scale[c] * invstd[c]) + bias[c];
+}
+
+template <bool VEC, int T>
+int launch_fwd_cluster(const float* x, const float* scale, const float* bias, float* rm, float* rv,
+                       float factor, float eps, float* y, float* sm_, float* si, BnShape sh, int cs,
+                       int per_cta, cudaStream_t s) {
+  auto kernel = bn_fwd_cluster_kernel<VEC, T>;
+  const size_t smem = static_cast<size_t>(per_cta) * (VEC ? 16 : 4);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sh.C) * cs);
+  cfg.blockDim = dim3(T);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, scale, bias, rm, rv, factor, eps, y, sm_, si, sh, per_cta);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  return launch_status();
+}
+
+int bn_forward_training(const float* x, const float* scale, const float* bias, float* rm, float* rv,
+                        float factor, float eps, float* y, float* save_mean, float* save_invstd,
+                        int N, int C, int HW, void* ws, size_t ws_bytes, void* stream) {
+  if (N < 0 || C < 0 || HW < 0) return SGB_ERR_SIZE;
+  if (N == 0 || C == 0 || HW == 0) return SGB_OK;
+  if (!x || !scale || !bias || !rm || !rv || !y || !save_mean || !save_invstd) return SGB_ERR_NULL;
+  const long long per_channel = static_cast<long long>(N) * HW;
+  if (per_channel > 0x7fffffffLL || C > 65535) return SGB_ERR_SIZE;
+  cudaStream_t s = as_stream(stream);
+  const BnShape sh{N, C, HW};
+  const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(y);
+  // x only is staged: a share of `units` units costs units * unit_bytes
+  const long long units = vec ? per_channel / 4 : per_channel;
+  const int unit_bytes = vec ? 16 : 4;
+  for (int pass = 0; pass < 2; ++pass) {
+    const long long cap = pass == 0 ? 50 * 1024 : 100 * 1024;
+    for (int cs = 1; cs <= 8; cs *= 2) {
+      const long long share = (units + cs - 1) / cs;
+      if (share * unit_bytes <= cap) {
+        const int per_cta = static_cast<int>(share);
+        if (vec)
+          return share > 2048
+                     ? launch_fwd_cluster<true, 512>(x, scale, bias, rm, rv, factor, eps, y, save_mean, save_invstd, sh, cs, per_cta, s)
+                     : launch_fwd_cluster<true, 256>(x, scale, bias, rm, rv, factor, eps, y, save_mean, save_invstd, sh, cs, per_cta, s);
+        return launch_fwd_cluster<false, 256>(x, scale, bias, rm, rv, factor, eps, y, save_mean, save_invstd, sh, cs, per_cta, s);
+      }
+    }
+  }
+  const int slices = bn_slices_for(per_channel, C, sm_count());
+  if (!ws || ws_bytes < static_cast<size_t>(slices) * C * sizeof(float)) return SGB_ERR_WORKSPACE;
+  float* partial = static_cast<float*>(ws);
+  const int per_slice = static_cast<int>(ceil_div(static_cast<size_t>(per_channel), slices));
+  const dim3 g1(slices, C);
+  const unsigned fb = static_cast<unsigned>(ceil_div(C, 128));
+  bn_fwd_partial_kernel<0><<<g1, kBlock, 0, s>>>(x, nullptr, partial, sh, per_slice);
+  bn_fwd_finish_kernel<<<fb, 128, 0, s>>>(0, partial, slices, save_mean, save_invstd, rm, rv, factor, eps, sh);
+  bn_fwd_partial_kernel<1><<<g1, kBlock, 0, s>>>(x, save_mean, partial, sh, per_slice);
+  bn_fwd_finish_kernel<<<fb, 128, 0, s>>>(1, partial, slices, save_mean, save_invstd, rm, rv, factor, eps, sh);
+  bn_fwd_normalize_kernel<<<dim3(static_cast<unsigned>(ceil_div(static_cast<size_t>(per_channel), kBlock)), C),
+                            kBlock, 0, s>>>(x, scale, bias, save_mean, save_invstd, y, sh);
   return launch_status();
 }
 
@@ -604,6 +963,14 @@ int sgb_bn_backward_f32(const float* x, const float* dy, const float* scale, con
                         int C, int HW, void* ws, size_t ws_bytes, void* stream) {
   return bn_backward<false>(x, dy, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
                             ws, ws_bytes, stream);
+}
+
+int sgb_bn_forward_training_f32(const float* x, const float* scale, const float* bias,
+                                float* running_mean, float* running_var, float factor, float eps,
+                                float* y, float* save_mean, float* save_invstd, int N, int C,
+                                int HW, void* ws, size_t ws_bytes, void* stream) {
+  return bn_forward_training(x, scale, bias, running_mean, running_var, factor, eps, y, save_mean,
+                             save_invstd, N, C, HW, ws, ws_bytes, stream);
 }
 
 int sgb_bn_backward_noalloc_f32(const float* x, const float* dy, const float* scale,

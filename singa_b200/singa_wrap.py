@@ -327,6 +327,24 @@ class CudnnBatchNormHandle(object):
         self.width = 1 if self.is_2d else x.shape[3]
 
 
+def GpuBatchNormForwardTraining(cbnh, x, bnScale, bnBias, running_mean, running_var, eps=0.0):
+    """model_operation.i:159: returns [y, mean, var] where ``var`` is the saved
+    INVERSE standard deviation 1/sqrt(batch_var + eps); running statistics are
+    updated in place with ``cbnh.factor``.  ``eps`` defaults to the value the
+    reference passes with cuDNN 9 (CUDNN_BN_MIN_EPSILON == 0)."""
+    _chk(x, bnScale, bnBias, running_mean, running_var)
+    n, c, hw = cbnh.batchsize, cbnh.channels, cbnh.height * cbnh.width
+    y = torch.empty_like(x)
+    mean = torch.empty_like(running_mean)
+    var = torch.empty_like(running_var)
+    need = _lib.lib().sgb_bn_backward_workspace_bytes(n, c, hw)
+    ws, wsn = _ws_args(x.device, need)
+    _lib.call("sgb_bn_forward_training_f32", _p(x), _p(bnScale), _p(bnBias), _p(running_mean),
+              _p(running_var), float(cbnh.factor), float(eps), _p(y), _p(mean), _p(var), n, c, hw,
+              ws, wsn, _stream())
+    return [y, mean, var]
+
+
 def GpuBatchNormBackward(cbnh, dy, x, bnScale, mean, var):
     """model_operation.i:165: returns [dx, dscale, dbias].  ``var`` is the
     saved INVERSE standard deviation produced by the forward pass, as in the

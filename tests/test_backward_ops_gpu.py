@@ -127,7 +127,33 @@ def test_batchnorm_golden(sw, oracle, golden):
 
 
 BN_SHAPES = [(1, 1, 1, 1), (2, 3, 4, 4), (4, 5, 7, 7), (3, 2, 5, 3), (8, 16, 14, 14), (32, 64, 28, 28),
-             (32, 2048, 7, 7), (32, 64, 56, 56), (16, 100), (256, 4096), (7, 3)]
+             (32, 2048, 7, 7), (32, 64, 56, 56), (16, 100), (256, 4096), (7, 3),
+             (3, 8, 5, 5), (2, 6, 3, 2), (32, 512, 7, 7), (5, 12, 3, 3), (32, 256, 56, 56)]
+
+
+@pytest.mark.parametrize("shape", BN_SHAPES)
+def test_batchnorm_forward_training(sw, oracle, shape):
+    rng = np.random.default_rng(sum(shape) + 7)
+    x, _, scale = bn_case(rng, shape)
+    c = shape[1]
+    bias = rng.standard_normal(c).astype(np.float32)
+    rm0, rv0 = rng.standard_normal(c).astype(np.float32), (rng.random(c) + 0.5).astype(np.float32)
+    eps = 1e-5
+    mean, invstd = oracle.bn_stats(x, eps=eps)
+    h = sw.CudnnBatchNormHandle(0.1, dev(x))
+    rm, rv = dev(rm0), dev(rv0)
+    y, m, v = sw.GpuBatchNormForwardTraining(h, dev(x), dev(scale), dev(bias), rm, rv, eps=eps)
+    close(host(m), mean, what="mean %s" % (shape,))
+    close(host(v), invstd, what="invstd %s" % (shape,))
+    bshape = (1, c) + (1,) * (x.ndim - 2)
+    want = (x.astype(np.float64) - mean.reshape(bshape)) * invstd.reshape(bshape) * scale.reshape(bshape) \
+        + bias.reshape(bshape)
+    close(host(y), want, rtol=2e-5, what="y %s" % (shape,))
+    axes = (0,) + tuple(range(2, x.ndim))
+    M = x.size // c
+    var_unbiased = x.astype(np.float64).var(axis=axes) * (M / (M - 1.0) if M > 1 else 1.0)
+    close(host(rm), 0.9 * rm0 + 0.1 * x.astype(np.float64).mean(axis=axes), what="running mean")
+    close(host(rv), 0.9 * rv0 + 0.1 * var_unbiased, what="running var")
 
 
 @pytest.mark.parametrize("shape", BN_SHAPES)
@@ -144,7 +170,8 @@ def test_batchnorm_backward(sw, oracle, shape):
         close(host(a), b, what="%s %s" % (name, shape))
 
 
-@pytest.mark.parametrize("shape", [(2, 3, 4, 4), (4, 5, 7, 7), (8, 16, 14, 14), (32, 64, 28, 28)])
+@pytest.mark.parametrize("shape", [(2, 3, 4, 4), (4, 5, 7, 7), (8, 16, 14, 14), (32, 64, 28, 28), (32, 64, 7, 7),
+                                   (2, 6, 3, 2), (32, 128, 56, 56)])
 def test_batchnorm_relu_fused_equals_unfused(sw, oracle, shape):
     rng = np.random.default_rng(sum(shape) + 1)
     x, dy, scale = bn_case(rng, shape)

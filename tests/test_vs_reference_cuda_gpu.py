@@ -154,7 +154,20 @@ def test_batchnorm_backward_matches_cudnn_call(sw, rd, shape):
     assert rd.refcudnn_bn_backward(is2d, N, Cc, H, W, eps, p(x), p(dy), p(sc), p(sm), p(si), p(dx), p(ds),
                                    p(db), None) == 0
     torch.cuda.synchronize()
-    h = sw.CudnnBatchNormHandle(0.9, x.view(N, Cc) if is2d else x)
+    h = sw.CudnnBatchNormHandle(0.1, x.view(N, Cc) if is2d else x)
+    # forward partner against cudnnBatchNormalizationForwardTraining (same factor, eps)
+    rm2, rv2 = z.clone(), o.clone()
+    my, mm, mv = sw.GpuBatchNormForwardTraining(h, x.view(N, Cc) if is2d else x, sc, z, rm2, rv2,
+                                                eps=rd.refcudnn_bn_min_epsilon())
+    rm_ref, rv_ref = z.clone(), o.clone()
+    y2 = torch.empty_like(x)
+    assert rd.refcudnn_bn_forward_training(is2d, N, Cc, H, W, eps, p(x), p(sc), p(z), p(y2), p(rm_ref),
+                                           p(rv_ref), C.c_double(0.1), p(sm), p(si), None) == 0
+    torch.cuda.synchronize()
+    for name, a, b in (("y", my.view_as(x), y2), ("save_mean", mm, sm), ("save_invstd", mv, si),
+                       ("running_mean", rm2, rm_ref), ("running_var", rv2, rv_ref)):
+        rel = float((a - b).abs().max() / b.abs().max())
+        assert rel <= 1e-5, (name, rel)
     mdx, mds, mdb = sw.GpuBatchNormBackward(h, dy, x, sc, sm, si)
     for name, a, b in (("dx", mdx, dx), ("dscale", mds, ds), ("dbias", mdb, db)):
         rel = float((a - b).abs().max() / b.abs().max())
