@@ -55,6 +55,8 @@ class OraclePath(object):
                 cpu.scale_inplace(t[a["x"]], np.float32(a["c"]))
             elif k == "sum_rows":
                 t[a["v"]][...] = cpu.sum_rows(t[a["M"]])
+            elif k == "conv_bias_bwd":
+                t[a["db"]][...] = cpu.conv_bias_backward(t[a["dy"]])
             elif k == "grad_ready":
                 pass     # one rank: the all-reduce of a single contribution is the identity
             elif k == "sync_and_update":

@@ -84,6 +84,11 @@ class HotPathGPU(object):
         if "maxpool.x" in self.t:
             self.t["maxpool.x"].copy_(torch.relu(self.t["relu.x"]))
             self.t["maxpool.y"].copy_(torch.nn.functional.max_pool2d(self.t["maxpool.x"], 3, 2, 1))
+        for op in self.plan["ops"]:        # other max-pool layers: post-ReLU input, consistent output
+            if op.kind == "maxpool_bwd" and op.args["x"] != "maxpool.x":
+                a = op.args
+                self.t[a["x"]].copy_(torch.relu(self.t[a["x"]]))
+                self.t[a["y"]].copy_(torch.nn.functional.max_pool2d(self.t[a["x"]], a["kernel"], a["stride"], a["pad"]))
         self.moments = {p: torch.zeros_like(self.t[p]) for p in self.plan["params"]}
         self.ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
         torch.cuda.synchronize()
@@ -157,6 +162,12 @@ class HotPathGPU(object):
             elif k == "sum_rows":
                 r, c = t[a["M"]].shape
                 self.calls.append(("sgb_sum_rows_f32", (p(a["M"]), p(a["v"]), r, c, ws.data_ptr(), ws.numel(), S)))
+            elif k == "conv_bias_bwd":
+                n, c = t[a["dy"]].shape[:2]
+                hw = t[a["dy"]].numel() // (n * c)
+                assert L.sgb_conv_bias_backward_workspace_bytes(n, c, hw) <= ws.numel()
+                self.calls.append(("sgb_conv_bias_backward_f32",
+                                   (p(a["dy"]), p(a["db"]), n, c, hw, ws.data_ptr(), ws.numel(), S)))
             elif k == "grad_ready":
                 self.calls.append(("grad_ready", a["param"]))
             elif k == "sync_and_update":

@@ -217,6 +217,7 @@ READS = {
     "bn_relu_bwd": ("dy", "relu_x", "x", "scale", "mean", "invstd"),
     "maxpool_bwd": ("x", "y", "dy"), "avgpool_bwd": ("dy",), "softmax": ("x",), "ce_fwd": ("p", "t"),
     "sum_all": ("x",), "ce_bwd": ("p", "t"), "ce_grad": ("p", "t"), "scale": ("x",), "sum_rows": ("M",),
+    "conv_bias_bwd": ("dy",),
 }
 
 
@@ -315,3 +316,117 @@ def algorithmic_bytes(plan, world=1):
     nparam = sum(numel(T[p].shape) for p in plan["params"])
     add("sgd", 20 * nparam)
     return out, nparam
+
+
+# ---------------------------------------------------------------- small configs
+def build_mlp_plan(batch=256, dims=(784, 4096, 4096, 10)):
+    """Backward + update path of the reference MLP (Linear-ReLU-Linear-ReLU-Linear,
+    softmax cross entropy; examples/mlp/model.py shape family, BASELINE config 1).
+    Matmul gradients are stand-ins (cuBLAS); the bias gradients (SumRows), ReLU
+    backward, softmax-CE and the SGD update are computed."""
+    T, ops, params, order = {}, [], [], []
+    B = batch
+
+    def tensor(name, shape, kind):
+        T[name] = Tensor(name, tuple(shape), kind)
+        return name
+
+    def param(name, shape):
+        tensor(name, shape, "param")
+        tensor("d:" + name, shape, "pgrad")
+        params.append(name)
+
+    nl = len(dims) - 1
+    for i in range(nl):
+        param("fc%d.W" % i, (dims[i], dims[i + 1]))
+        param("fc%d.b" % i, (dims[i + 1],))
+        if i < nl - 1:
+            tensor("relu%d.x" % i, (B, dims[i + 1]), "act")
+    tensor("labels", (B,), "label")
+    tensor("logits", (B, dims[-1]), "act")
+    for n, shp in (("prob", (B, dims[-1])), ("loss_vec", (B,)), ("loss", (1,)), ("dlogits", (B, dims[-1]))):
+        tensor(n, shp, "grad")
+
+    def ready(p):
+        order.append(p)
+        ops.append(Op("grad_ready", dict(param=p)))
+
+    ops.append(Op("softmax", dict(x="logits", y="prob")))
+    ops.append(Op("ce_fwd", dict(p="prob", t="labels", loss="loss_vec")))
+    ops.append(Op("sum_all", dict(x="loss_vec", out="loss")))
+    ops.append(Op("ce_bwd", dict(p="prob", t="labels", grad="dlogits")))
+    ops.append(Op("scale", dict(x="dlogits", c=1.0 / B)))
+    dy = "dlogits"
+    for i in reversed(range(nl)):
+        ops.append(Op("sum_rows", dict(M=dy, v="d:fc%d.b" % i)))     # AddBias.backward
+        ready("fc%d.b" % i)
+        ready("fc%d.W" % i)                                           # Matmul.backward (cuBLAS)
+        if i > 0:
+            g = tensor("fc%d.dgrad" % i, (B, dims[i]), "syn")        # dy @ W^T from cuBLAS
+            dx = tensor("relu%d.dx" % (i - 1), (B, dims[i]), "grad")
+            ops.append(Op("relu_bwd", dict(dy=g, x="relu%d.x" % (i - 1), dx=dx)))
+            dy = dx
+    ops.append(Op("sync_and_update", dict()))
+    return dict(tensors=T, ops=ops, params=params, grad_order=order, batch=B)
+
+
+def build_cnn_plan(batch=64, channels=32, num_classes=10):
+    """Backward + update path of the small CNN of BASELINE config 2:
+    conv5x5(32)+bias -> ReLU -> maxpool2 -> conv5x5(32)+bias -> ReLU -> maxpool2
+    -> linear 500 -> ReLU -> linear 10, on 1x28x28 inputs.  Convolution and
+    matmul gradients are stand-ins; conv-bias and linear-bias gradients, ReLU /
+    max-pool backward, softmax-CE and the update are computed."""
+    T, ops, params, order = {}, [], [], []
+    B, C = batch, channels
+
+    def tensor(name, shape, kind):
+        T[name] = Tensor(name, tuple(shape), kind)
+        return name
+
+    def param(name, shape):
+        tensor(name, shape, "param")
+        tensor("d:" + name, shape, "pgrad")
+        params.append(name)
+
+    def ready(p):
+        order.append(p)
+        ops.append(Op("grad_ready", dict(param=p)))
+
+    param("conv1.W", (C, 1, 5, 5)); param("conv1.b", (C,))
+    param("conv2.W", (C, C, 5, 5)); param("conv2.b", (C,))
+    flat = C * 4 * 4
+    param("fc1.W", (flat, 500)); param("fc1.b", (500,))
+    param("fc2.W", (500, num_classes)); param("fc2.b", (num_classes,))
+    tensor("relu1.x", (B, C, 24, 24), "act"); tensor("pool1.x", (B, C, 24, 24), "act")
+    tensor("pool1.y", (B, C, 12, 12), "act")
+    tensor("relu2.x", (B, C, 8, 8), "act"); tensor("pool2.x", (B, C, 8, 8), "act")
+    tensor("pool2.y", (B, C, 4, 4), "act")
+    tensor("relu3.x", (B, 500), "act")
+    tensor("labels", (B,), "label")
+    tensor("logits", (B, num_classes), "act")
+    for n, shp in (("prob", (B, num_classes)), ("loss_vec", (B,)), ("loss", (1,)), ("dlogits", (B, num_classes))):
+        tensor(n, shp, "grad")
+    ops.append(Op("softmax", dict(x="logits", y="prob")))
+    ops.append(Op("ce_fwd", dict(p="prob", t="labels", loss="loss_vec")))
+    ops.append(Op("sum_all", dict(x="loss_vec", out="loss")))
+    ops.append(Op("ce_bwd", dict(p="prob", t="labels", grad="dlogits")))
+    ops.append(Op("scale", dict(x="dlogits", c=1.0 / B)))
+    ops.append(Op("sum_rows", dict(M="dlogits", v="d:fc2.b"))); ready("fc2.b"); ready("fc2.W")
+    g = tensor("fc2.dgrad", (B, 500), "syn")
+    d3 = tensor("relu3.dx", (B, 500), "grad")
+    ops.append(Op("relu_bwd", dict(dy=g, x="relu3.x", dx=d3)))
+    ops.append(Op("sum_rows", dict(M=d3, v="d:fc1.b"))); ready("fc1.b"); ready("fc1.W")
+    g = tensor("fc1.dgrad", (B, C, 4, 4), "syn")                      # reshaped dy @ W^T
+    dp2 = tensor("pool2.dx", (B, C, 8, 8), "grad")
+    ops.append(Op("maxpool_bwd", dict(x="pool2.x", y="pool2.y", dy=g, dx=dp2, kernel=(2, 2), stride=(2, 2), pad=(0, 0))))
+    d2 = tensor("relu2.dx", (B, C, 8, 8), "grad")
+    ops.append(Op("relu_bwd", dict(dy=dp2, x="relu2.x", dx=d2)))
+    ops.append(Op("conv_bias_bwd", dict(dy=d2, db="d:conv2.b"))); ready("conv2.b"); ready("conv2.W")
+    g = tensor("conv2.dgrad", (B, C, 12, 12), "syn")
+    dp1 = tensor("pool1.dx", (B, C, 24, 24), "grad")
+    ops.append(Op("maxpool_bwd", dict(x="pool1.x", y="pool1.y", dy=g, dx=dp1, kernel=(2, 2), stride=(2, 2), pad=(0, 0))))
+    d1 = tensor("relu1.dx", (B, C, 24, 24), "grad")
+    ops.append(Op("relu_bwd", dict(dy=dp1, x="relu1.x", dx=d1)))
+    ops.append(Op("conv_bias_bwd", dict(dy=d1, db="d:conv1.b"))); ready("conv1.b"); ready("conv1.W")
+    ops.append(Op("sync_and_update", dict()))
+    return dict(tensors=T, ops=ops, params=params, grad_order=order, batch=B)

@@ -58,3 +58,29 @@ def test_fused_and_unfused_plans_agree_bitwise():
         outs.append({p: gpu.t[p].clone() for p in plan["params"]})
     for p in outs[0]:
         assert torch.equal(outs[0][p], outs[1][p]), p
+
+
+@pytest.mark.parametrize("which", ["mlp", "cnn"])
+def test_small_config_steps_match_oracle(which):
+    """BASELINE configs 1 (MLP 784-4096-4096-10, batch 256) and 2 (small CNN,
+    batch 64) at their full sizes: one backward + SGD-momentum step, eager and
+    fused, against the oracle executor."""
+    from oracle.path import OraclePath
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import build_cnn_plan, build_mlp_plan, fuse_plan
+    plan = build_mlp_plan() if which == "mlp" else build_cnn_plan()
+    lr = 0.05 if which == "mlp" else 0.005
+    wd = 0.0 if which == "mlp" else 1e-5
+    for p in (plan, fuse_plan(plan)):
+        gpu = HotPathGPU(p, communicator=None, world=1, seed=0, lr=lr, momentum=0.9, weight_decay=wd)
+        host = gpu.host_copy()
+        OraclePath(p, host, lr=lr, momentum=0.9, weight_decay=wd).run_step()
+        gpu.run_step()
+        torch.cuda.synchronize()
+        got = gpu.host_copy()
+        for name, spec in p["tensors"].items():
+            if spec.kind == "grad":
+                close(got[name], host[name], 2e-5, name)
+        for name in p["params"]:
+            close(got["d:" + name], host["d:" + name], 2e-5, "grad " + name)
+            close(got[name], host[name], 1e-6, "param " + name)
