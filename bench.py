@@ -347,7 +347,10 @@ def kernel_launches(path):
                 n += 2 * ((len(idx) + 71) // 72)  # pack and unpack launches at flush
             elif path.dist_option == "half":
                 n += 2                           # cast down, cast up
-    n += (len(path.plan["params"]) + 71) // 72   # fused SGD
+    if getattr(path, "update_on_arrival", False):
+        n += sum((len(idx) + 71) // 72 for _, idx in path.events)   # one fused SGD group per bucket
+    else:
+        n += (len(path.plan["params"]) + 71) // 72               # one fused SGD group per step
     return n
 
 

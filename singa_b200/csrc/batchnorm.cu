@@ -497,15 +497,25 @@ int env_int(const char* name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta) {
+int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int channels) {
   static const int share_kb = env_int("SGB_BN_SHARE_KB", 50);     // preferred staging per CTA
-  static const int max_cs = env_int("SGB_BN_MAX_CLUSTER", 8) > 8 ? 8 : env_int("SGB_BN_MAX_CLUSTER", 8);
+  static const int max_cs = env_int("SGB_BN_MAX_CLUSTER", 8);     // 16 = non-portable cluster size
+  static const int fill = env_int("SGB_BN_FILL_CTAS_PER_SM", 0);  // >0: split small channels further (measured slower on B200)
   const long long kPreferred = share_kb * 1024LL, kLimit = 100 * 1024;
   for (int pass = 0; pass < 2; ++pass) {
     const long long cap = pass == 0 ? kPreferred : kLimit;
     for (int cs = 1; cs <= max_cs; cs *= 2) {
-      const long long share = (units_per_channel + cs - 1) / cs;
+      long long share = (units_per_channel + cs - 1) / cs;
       if (share * unit_bytes * 2 <= cap && share <= 8192) {   // <= 16 units per thread of a 512-thread CTA
+        // Small tensors: a grid of C*cs CTAs that leaves SMs idle is latency
+        // bound; split the channel over more CTAs (shorter per-thread loops)
+        // while a share still keeps every thread of a 256-thread CTA busy.
+        const long long want = static_cast<long long>(sm_count()) * fill;
+        while (cs * 2 <= max_cs && static_cast<long long>(channels) * cs < want &&
+               (units_per_channel + 2 * cs - 1) / (2 * cs) >= 512) {
+          cs *= 2;
+          share = (units_per_channel + cs - 1) / cs;
+        }
         *per_cta = static_cast<int>(share);
         return cs;
       }
@@ -529,6 +539,8 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
   if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e != cudaSuccess) return note_cuda_error(e);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_set[dev] = true;
   }
@@ -621,7 +633,7 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
   }
   {
     int per_cta = 0;
-    const int cs = cluster_plan(vec ? per_channel / 4 : per_channel, vec ? 16 : 4, &per_cta);
+    const int cs = cluster_plan(vec ? per_channel / 4 : per_channel, vec ? 16 : 4, &per_cta, C);
     if (cs > 0 && static_cast<long long>(C) * cs <= 0x7fffffffLL) {
       return vec ? launch_cluster<true, MASK>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias,
                                               sh, cs, per_cta, s)

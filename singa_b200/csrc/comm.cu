@@ -213,9 +213,14 @@ int sgb_comm_create(sgb_comm** out, int rank, int world, const void* unique_id, 
   NC(ncclCommInitRank(&c->nccl, world, id, rank));
   CU(cudaMalloc(&c->send, max_elems * sizeof(float)));
   CU(cudaMalloc(&c->recv, max_elems * sizeof(float)));
-  CU(cudaStreamCreateWithFlags(&c->s, cudaStreamNonBlocking));
-  CU(cudaStreamCreateWithFlags(&c->c1, cudaStreamNonBlocking));
-  CU(cudaStreamCreateWithFlags(&c->c2, cudaStreamNonBlocking));
+  // Highest priority: the collectives and their small pack / unpack kernels
+  // should start as soon as their inputs exist instead of queueing behind the
+  // large backward kernels of the compute stream.
+  int prio_lo = 0, prio_hi = 0;
+  CU(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
+  CU(cudaStreamCreateWithPriority(&c->s, cudaStreamNonBlocking, prio_hi));
+  CU(cudaStreamCreateWithPriority(&c->c1, cudaStreamNonBlocking, prio_hi));
+  CU(cudaStreamCreateWithPriority(&c->c2, cudaStreamNonBlocking, prio_hi));
   cudaEvent_t* evs[] = {&c->ev_compute, &c->ev_c1, &c->ev_s, &c->ev_c2};
   for (cudaEvent_t* e : evs) CU(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
   CU(cudaEventCreateWithFlags(&c->ev_host, cudaEventDisableTiming | cudaEventBlockingSync));

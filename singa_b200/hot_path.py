@@ -26,10 +26,16 @@ def _table(tensors):
 class HotPathGPU(object):
     def __init__(self, plan, communicator=None, world=1, seed=0, lr=0.1, momentum=0.9,
                  weight_decay=1e-5, threshold=2097152, dist_option="plain", spars=0.05,
-                 device=None):
+                 device=None, update_on_arrival=True):
         self.plan, self.comm, self.world = plan, communicator, world
         self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
         self.threshold, self.dist_option, self.spars = threshold, dist_option, spars
+        # With a communicator, every bucket's parameters are updated on the
+        # communicator's side stream as soon as that bucket's reduced gradients
+        # have landed, overlapped with the rest of the backward pass (same
+        # results as updating everything after the final wait).
+        self.update_on_arrival = bool(update_on_arrival) and communicator is not None \
+            and dist_option in ("plain", "half")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.lib = _lib.lib()
         self.t = {}
@@ -182,6 +188,13 @@ class HotPathGPU(object):
         self.flush_after = {ev[1][-1]: ev for ev in self.events}
         self.fused_tables = {ev[1][-1]: _table([self.grads[i] for i in ev[1]]) for ev in self.events if ev[0] == "fused"}
         self.single_tables = {i: _table([self.grads[i]]) for i in range(len(order))}
+        names = self.plan["grad_order"]
+        self.bucket_sgd = {}
+        for ev in self.events:
+            ps = [names[i] for i in ev[1]]
+            self.bucket_sgd[ev[1][-1]] = (_table([t[n] for n in ps])[0], _table([t["d:" + n] for n in ps])[0],
+                                          _table([self.moments[n] for n in ps])[0],
+                                          _table([t[n] for n in ps])[1], len(ps))
         plist = self.plan["params"]
         self.sgd_tables = (_table([t[n] for n in plist])[0], _table([t["d:" + n] for n in plist])[0],
                            _table([self.moments[n] for n in plist])[0], _table([t[n] for n in plist])[1], len(plist))
@@ -211,8 +224,10 @@ class HotPathGPU(object):
                 g = self.grads[idx]
                 if half:
                     self._check("synch_half", L.sgb_comm_synch_half(c._h, g.data_ptr(), g.numel(), stream))
+                    self._sgd_bucket(idx, 2)          # result lands on c2
                 else:
                     self._check("synch", L.sgb_comm_synch(c._h, g.data_ptr(), g.numel(), 0, stream))
+                    self._sgd_bucket(idx, 0)          # in place on the NCCL stream
                 return 1
             ptrs, sizes, n = self.single_tables[idx]
             if half:
@@ -224,8 +239,10 @@ class HotPathGPU(object):
                 ptrs, sizes, n = self.fused_tables[idx]
                 if half:
                     self._check("flush_half", L.sgb_comm_fused_synch_half(c._h, ptrs, sizes, n, 1, stream))
+                    self._sgd_bucket(idx, 2)
                 else:
                     self._check("flush", L.sgb_comm_fused_synch(c._h, ptrs, sizes, n, 0, 1, stream))
+                    self._sgd_bucket(idx, 1)          # unpacked on c1
                 n_calls += 2
             return n_calls
         # sparse options: nothing is staged, the whole bucket is handed over at flush time
@@ -236,6 +253,16 @@ class HotPathGPU(object):
         self._check("sparsification", L.sgb_comm_sparsification(
             c._h, ptrs, sizes, n, self.residuals[idx].data_ptr(), float(self.spars), int(topk), stream))
         return 1
+
+    def _sgd_bucket(self, idx, which_stream):
+        if not self.update_on_arrival:
+            return
+        L = self.lib
+        side = L.sgb_comm_stream(self.comm._h, which_stream)
+        pp, gp, mp, sizes, n = self.bucket_sgd[idx]
+        scale = float(np.float32(1.0) / np.float32(self.world))
+        self._check("sgd", L.sgb_sgd_update_multi_f32(pp, gp, mp, sizes, n, self.lr, self.momentum, 0.0,
+                                                       self.weight_decay, 0, scale, side))
 
     def run_step(self):
         """Enqueues one full step on the current stream (+ the communicator's
@@ -250,6 +277,8 @@ class HotPathGPU(object):
             elif name == "sync_and_update":
                 if self.comm is not None:
                     self._check("wait", L.sgb_comm_wait(self.comm._h, stream))
+                if self.update_on_arrival:
+                    continue                  # every bucket was updated as it arrived
                 pp, gp, mp, sizes, n = self.sgd_tables
                 scale = float(np.float32(1.0) / np.float32(self.world))
                 self._check("sgd", L.sgb_sgd_update_multi_f32(pp, gp, mp, sizes, n, self.lr, self.momentum, 0.0,

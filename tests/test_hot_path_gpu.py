@@ -84,3 +84,39 @@ def test_small_config_steps_match_oracle(which):
         for name in p["params"]:
             close(got["d:" + name], host["d:" + name], 2e-5, "grad " + name)
             close(got[name], host[name], 1e-6, "param " + name)
+
+
+@pytest.mark.parametrize("dist_option", ["plain", "half"])
+def test_step_with_communicator_graph_and_update_on_arrival(dist_option):
+    """One-rank communicator in the loop: bucketed synchronisation on the side
+    streams, per-bucket SGD as each bucket lands, the whole step replayed from a
+    CUDA graph.  Must equal the oracle's step (a one-rank all-reduce is the
+    identity; fp16 transport rounds the gradients once)."""
+    from oracle.path import OraclePath
+    from singa_b200.communicator import Communicator, NcclIdHolder
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import build_plan, fuse_plan
+    plan = fuse_plan(build_plan(batch=2, image=64, num_classes=10, blocks=(1, 1, 1, 1)))
+    comm = Communicator(torch.cuda.current_device(), 1, NcclIdHolder(), buffSize=4194304)
+    try:
+        gpu = HotPathGPU(plan, communicator=comm, world=1, seed=9, dist_option=dist_option, threshold=20000)
+        assert gpu.update_on_arrival and len(gpu.events) > 3
+        host = gpu.host_copy()
+        ref = OraclePath(plan, host, dist_option=dist_option)
+        ref.run_step()
+        ref.run_step()
+        gpu.run_step()
+        g = gpu.capture()
+        g.replay()
+        torch.cuda.synchronize()
+        got = gpu.host_copy()
+        tol = 2e-3 if dist_option == "half" else 1e-6
+        for p in plan["params"]:
+            close(got[p], host[p], tol, "param " + p)
+        gpu.release_graph()
+        del g
+    finally:
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        comm.close()
