@@ -343,8 +343,9 @@ def kernel_launches(path):
         n += per.get(name, 0)
     if path.comm is not None:
         for kind, idx in path.events:
-            if kind == "fused":
-                n += 2 * ((len(idx) + 71) // 72)  # pack and unpack launches at flush
+            if kind == "fused" and path.dist_option == "half":
+                n += 2 * ((len(idx) + 71) // 72)  # pack+cast and unpack+cast launches at flush
+            # fp32 buckets are contiguous arena slices: reduced in place, no pack / unpack
             elif path.dist_option == "half":
                 n += 2                           # cast down, cast up
     if getattr(path, "update_on_arrival", False):

@@ -407,8 +407,10 @@ int sgb_comm_synch(sgb_comm *c, void *data, size_t n, int is_half,
  * pointers and reserves space, and the bytes are gathered by one multi-tensor
  * pack launch at flush time, so a staged tensor must stay allocated and
  * unchanged until the flush (it has to: the flush writes the result into it).
- * tensors / sizes are HOST arrays.  SGB_ERR_CAPACITY if the bucket would
- * overflow. */
+ * When the staged tensors are exactly contiguous in memory (gradients kept in
+ * one arena) and the flush list equals the staged list, the bucket is reduced
+ * in place and no pack / unpack pass runs.  tensors / sizes are HOST arrays.
+ * SGB_ERR_CAPACITY if the bucket would overflow. */
 int sgb_comm_fused_synch(sgb_comm *c, void *const *tensors, const size_t *sizes,
                          size_t count, int is_half, int send,
                          void *compute_stream);

@@ -314,6 +314,26 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
   // flush: everything staged so far is reduced; `tensors` receive the result
   const size_t total = total_of(sizes, count);
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
+  // Gradients that already sit back to back in memory (a gradient arena) need
+  // neither the pack nor the unpack pass: the bucket is reduced in place.
+  if (!is_half && !c->pend_half && c->pend_off == 0 && c->pend_ptrs.size() == count &&
+      c->send_off == total) {
+    bool in_place = true;
+    for (size_t i = 0; i < count && in_place; ++i) {
+      in_place = c->pend_ptrs[i] == tensors[i] && c->pend_sizes[i] == sizes[i] &&
+                 (i + 1 == count ||
+                  static_cast<char*>(tensors[i]) + sizes[i] * sizeof(float) == tensors[i + 1]);
+    }
+    if (in_place) {
+      c->pend_ptrs.clear();
+      c->pend_sizes.clear();
+      c->send_off = 0;
+      OK(before_collective(c, sgb::as_stream(compute_stream)));
+      NC(ncclAllReduce(tensors[0], tensors[0], total, ncclFloat, ncclSum, c->nccl, c->s));
+      OK(after_collective(c, false));
+      return SGB_OK;
+    }
+  }
   OK(pack_pending(c, sgb::as_stream(compute_stream)));
   OK(before_collective(c, sgb::as_stream(compute_stream)));
   if (c->send_off)

@@ -53,8 +53,25 @@ class HotPathGPU(object):
         def randn(shape, std=1.0, mean=0.0):
             return torch.randn(shape, generator=gen, device=dev) * std + mean
 
+        # Parameter gradients live back to back, in the order they are produced,
+        # in one arena: every bucket of the synchronisation policy is then a
+        # contiguous slice and is all-reduced in place (no pack / unpack pass).
+        names = self.plan["grad_order"]
+        sizes = [numel(T["d:" + n].shape) for n in names]
+        order = [names[i] for _, idx in plan_buckets(sizes, self.threshold) for i in idx]   # bucket by bucket
+        total = sum(sizes)
+        self.grad_arena = torch.empty(total, device=dev)
+        arena_view, off = {}, 0
+        for n in order:
+            cnt = numel(T["d:" + n].shape)
+            arena_view["d:" + n] = self.grad_arena[off:off + cnt].view(T["d:" + n].shape)
+            off += cnt
         for name, spec in T.items():
             k = spec.kind
+            if k == "pgrad" and name in arena_view:
+                self.t[name] = arena_view[name]
+                self.t[name].copy_(randn(spec.shape, 1e-3))
+                continue
             if k == "label":
                 self.t[name] = torch.randint(0, T["logits"].shape[1], spec.shape, generator=gen,
                                              device=dev, dtype=torch.int32)
