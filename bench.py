@@ -277,12 +277,12 @@ def main():
     peak, peak_kind = measured_peak()
     fam = {}
     alias = {"relu_bwd": "relu_bwd", "add_relu_bwd": "add_relu_bwd", "add_out": "join", "bn_bwd": "bn_bwd",
-             "bn_relu_bwd": "bn_relu_bwd", "maxpool_bwd": "maxpool_bwd", "avgpool_bwd": "avgpool_bwd", "sgd": "sgd"}
+             "bn_relu_bwd": "bn_relu_bwd", "bn_add_relu_bwd": "bn_add_relu_bwd", "maxpool_bwd": "maxpool_bwd", "avgpool_bwd": "avgpool_bwd", "sgd": "sgd"}
     for k, name in alias.items():
         if k in fam_ms and name in by_family and fam_ms[k] > 0:
             gbs = by_family[name] / fam_ms[k] / 1e6
             fam[name] = {"ms": round(fam_ms[k], 4), "GBps": round(gbs, 1), "frac": round(gbs / peak, 3)}
-    bn_keys = [k for k in ("bn_bwd", "bn_relu_bwd") if k in fam_ms]
+    bn_keys = [k for k in ("bn_bwd", "bn_relu_bwd", "bn_add_relu_bwd") if k in fam_ms]
     bn_bytes = sum(by_family[k] for k in bn_keys)
     bn_ms = sum(fam_ms[k] for k in bn_keys)
     bn_launches = sum(1 for o in plan["ops"] if o.kind in bn_keys)
@@ -310,7 +310,7 @@ def main():
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
                        "global_batch": BATCH * world, "dist_option": args.dist_option,
-                       "fusion": "bn+relu, join+relu" if fused else "none (one kernel per reference call)",
+                       "fusion": "bn+relu, join+relu(+bn)" if fused else "none (one kernel per reference call)",
                        "cuda_graph": use_graph, "bucket_elems": 4194304, "threshold_elems": 2097152,
                        "l2": "inputs larger than L2: %.1f GB touched per step vs 126 MB" % (total_alg / 1e9),
                        "excluded": "cuDNN/cuBLAS contractions (conv, linear): stand-in gradients",
@@ -334,7 +334,7 @@ def main():
 def kernel_launches(path):
     """Kernels of this library launched per step (NCCL's own are not counted)."""
     per = {"sgb_relu_backward_f32": 1, "sgb_add_relu_backward_f32": 1, "sgb_binary_f32": 1,
-           "sgb_bn_backward_f32": 2, "sgb_bn_relu_backward_f32": 2, "sgb_maxpool_backward_f32": 1,
+           "sgb_bn_backward_f32": 2, "sgb_bn_relu_backward_f32": 2, "sgb_bn_add_relu_backward_f32": 1, "sgb_maxpool_backward_f32": 1,
            "sgb_avgpool_backward_f32": 1, "sgb_softmax_rows_f32": 1, "sgb_cross_entropy_f32": 1,
            "sgb_sum_all_f32": 2, "sgb_softmax_cross_entropy_bwd_f32": 1,
            "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1}

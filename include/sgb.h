@@ -224,6 +224,21 @@ int sgb_bn_backward_f32(const float *x, const float *dy, const float *scale,
                         const float *mean, const float *invstd, float *dx,
                         float *dscale, float *dbias, int N, int C, int HW,
                         void *ws, size_t ws_bytes, void *stream);
+/* Gradient join + ReLU backward + batch-norm backward in one pass:
+ *   joined = relu_in > 0 ? (dy_a + dy_b) : 0        (also written out: the
+ *            shortcut branch of a residual block reads it)
+ *   (dx, dscale, dbias) = batch-norm backward of `joined`
+ * Equals sgb_add_relu_backward_f32 followed by sgb_bn_backward_f32 bit for
+ * bit in `joined`, and within rounding of the sums elsewhere; it saves one
+ * read of the joined gradient (the sequence "+=" join (autograd.py:204),
+ * ReLUBackward, GpuBatchNormBackward at the end of every residual block). */
+int sgb_bn_add_relu_backward_f32(const float *x, const float *dy_a,
+                                 const float *dy_b, const float *relu_in,
+                                 const float *scale, const float *mean,
+                                 const float *invstd, float *joined, float *dx,
+                                 float *dscale, float *dbias, int N, int C,
+                                 int HW, void *ws, size_t ws_bytes,
+                                 void *stream);
 /* Forward partner: training-mode batch norm.  y = scale * (x - mean) * invstd
  * + bias with batch statistics; save_mean / save_invstd (= 1/sqrt(biased var
  * + eps)) are what sgb_bn_backward_f32 consumes; running_mean / running_var

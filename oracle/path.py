@@ -29,8 +29,12 @@ class OraclePath(object):
                 t[a["dx"]][...] = cpu.relu_backward(t[a["dy_a"]] + t[a["dy_b"]], t[a["x"]])
             elif k == "add_out":
                 t[a["out"]][...] = t[a["a"]] + t[a["b"]]
-            elif k in ("bn_bwd", "bn_relu_bwd"):
-                dy = t[a["dy"]]
+            elif k in ("bn_bwd", "bn_relu_bwd", "bn_add_relu_bwd"):
+                if k == "bn_add_relu_bwd":
+                    t[a["joined"]][...] = cpu.relu_backward(t[a["dy_a"]] + t[a["dy_b"]], t[a["relu_x"]])
+                    dy = t[a["joined"]]
+                else:
+                    dy = t[a["dy"]]
                 if k == "bn_relu_bwd":
                     dy = cpu.relu_backward(dy, t[a["relu_x"]])
                 dx, ds, db = cpu.bn_backward(dy, t[a["x"]], t[a["scale"]], t[a["mean"]], t[a["invstd"]])

@@ -208,13 +208,18 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // grid.x = C * CS with cluster dimension CS: the CS CTAs of a cluster share
 // channel blockIdx.x / CS.  A "unit" is one float4 (VEC) or one float.
 // Dynamic shared memory: 2 * per_cta units (x share, then dy share).
-template <bool VEC, bool MASK, int T>
+// ADD (only with VEC): the incoming gradient is the join dy + dy_b masked by
+// the ReLU input; it is formed while staging, kept in shared memory for the
+// two later phases and ALSO written to `joined` for the other consumers of the
+// join (the shortcut branch), which replaces a separate join+ReLU kernel.
+template <bool VEC, bool MASK, int T, bool ADD = false>
 __global__ void __launch_bounds__(T)
 bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ relu_in, const float* __restrict__ scale,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       float* __restrict__ dx, float* __restrict__ dscale,
-                      float* __restrict__ dbias, BnShape sh, int per_cta) {
+                      float* __restrict__ dbias, BnShape sh, int per_cta,
+                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
   extern __shared__ __align__(16) float stage[];
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
@@ -235,7 +240,40 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const size_t chan_off = static_cast<size_t>(c) * sh.HW;
 
   // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
-  {
+  if (VEC && ADD) {
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1;) {
+      // two units per round: x by asynchronous copy, the three gradient-side
+      // operands through registers (six independent 16-byte loads in flight)
+      Vec4f va[2], vb[2], vr[2];
+      size_t offs[2];
+      int ls[2], cnt = 0;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (u < u1) {
+          offs[j] = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4;
+          ls[j] = (u - u0) * 4;
+          cp_async16(sx + ls[j], x + offs[j]);
+          va[j].u = ld128(dy + offs[j]);
+          vb[j].u = ld128(dy_b + offs[j]);
+          vr[j].u = ld128(relu_in + offs[j]);
+          u += T;
+          w.next();
+          cnt = j + 1;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (j < cnt) {
+          Vec4f g;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) g.f[k] = vr[j].f[k] > 0 ? (va[j].f[k] + vb[j].f[k]) : 0.0f;
+          *reinterpret_cast<uint4*>(sg + ls[j]) = g.u;
+          st128(joined + offs[j], g.u);
+        }
+      }
+    }
+  } else {
     UnitWalk w(first, T, hwu);
     for (int u = first; u < u1; u += T, w.next()) {
       const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * kW;
@@ -254,7 +292,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   // fused ReLU: while the copies fly, read the ReLU input and keep only the
   // sign decisions, 4 bits per unit (a share is at most 16 units per thread)
   unsigned long long keep = 0;
-  if (VEC && MASK) {
+  if (VEC && MASK && !ADD) {
     UnitWalk w(first, T, hwu);
     int slot = 0;
     for (int u = first; u < u1;) {
@@ -295,7 +333,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         Vec4f vx, vg;
         vx.u = *reinterpret_cast<const uint4*>(sx + l);
         vg.u = *reinterpret_cast<const uint4*>(sg + l);
-        if (MASK) {
+        if (MASK && !ADD) {
           const unsigned bits = static_cast<unsigned>(keep >> slot);
 #pragma unroll
           for (int k = 0; k < 4; ++k) vg.f[k] = (bits >> k) & 1u ? vg.f[k] : 0.0f;
@@ -524,11 +562,12 @@ int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int 
   return 0;
 }
 
-template <bool VEC, bool MASK, int T>
+template <bool VEC, bool MASK, int T, bool ADD = false>
 int launch_cluster_t(const float* x, const float* dy, const float* relu_in, const float* scale,
                      const float* mean, const float* invstd, float* dx, float* dscale,
-                     float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s) {
-  auto kernel = bn_bwd_cluster_kernel<VEC, MASK, T>;
+                     float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s,
+                     const float* dy_b = nullptr, float* joined = nullptr) {
+  auto kernel = bn_bwd_cluster_kernel<VEC, MASK, T, ADD>;
   const size_t smem = static_cast<size_t>(per_cta) * (VEC ? 16 : 4) * 2;
   // Opt in to > 48 KB of dynamic shared memory once per device and kernel
   // instantiation (the attribute sticks to the function in that context), so
@@ -557,7 +596,7 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, dy, relu_in, scale, mean, invstd, dx, dscale,
-                                     dbias, sh, per_cta);
+                                     dbias, sh, per_cta, dy_b, joined);
   if (e != cudaSuccess) return note_cuda_error(e);
   return launch_status();
 }
@@ -599,6 +638,14 @@ bn_bwd_peract_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     dx[off] = k * (dy[off] - a - (x[off] - mu) * b);
   }
 }
+
+// join + ReLU backward + batch-norm backward.  Uses the single-pass cluster
+// kernel when the shape allows it; otherwise the three steps run as separate
+// kernels (same values).
+int bn_add_relu_backward(const float* x, const float* dy_a, const float* dy_b, const float* relu_in,
+                         const float* scale, const float* mean, const float* invstd, float* joined,
+                         float* dx, float* dscale, float* dbias, int N, int C, int HW, void* ws,
+                         size_t ws_bytes, void* stream);
 
 template <bool MASK>
 int bn_backward(const float* x, const float* dy, const float* relu_in, const float* scale,
@@ -658,6 +705,38 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
                                                            partial, slices, dx, dscale, dbias, sh);
   }
   return launch_status();
+}
+
+int bn_add_relu_backward(const float* x, const float* dy_a, const float* dy_b, const float* relu_in,
+                         const float* scale, const float* mean, const float* invstd, float* joined,
+                         float* dx, float* dscale, float* dbias, int N, int C, int HW, void* ws,
+                         size_t ws_bytes, void* stream) {
+  if (N < 0 || C < 0 || HW < 0) return SGB_ERR_SIZE;
+  if (N == 0 || C == 0 || HW == 0) return SGB_OK;
+  if (!x || !dy_a || !dy_b || !relu_in || !scale || !mean || !invstd || !joined || !dx || !dscale ||
+      !dbias)
+    return SGB_ERR_NULL;
+  const long long per_channel = static_cast<long long>(N) * HW;
+  if (per_channel > 0x7fffffffLL || C > 65535) return SGB_ERR_SIZE;
+  const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(dy_a) && aligned16(dy_b) &&
+                   aligned16(relu_in) && aligned16(joined) && aligned16(dx);
+  if (vec) {
+    int per_cta = 0;
+    const int cs = cluster_plan(per_channel / 4, 16, &per_cta, C);
+    if (cs > 0 && static_cast<long long>(C) * cs <= 0x7fffffffLL) {
+      const BnShape sh{N, C, HW};
+      cudaStream_t s = as_stream(stream);
+      if (per_cta > 2048)
+        return launch_cluster_t<true, true, 512, true>(x, dy_a, relu_in, scale, mean, invstd, dx, dscale,
+                                                       dbias, sh, cs, per_cta, s, dy_b, joined);
+      return launch_cluster_t<true, true, 256, true>(x, dy_a, relu_in, scale, mean, invstd, dx, dscale,
+                                                     dbias, sh, cs, per_cta, s, dy_b, joined);
+    }
+  }
+  int st = sgb_add_relu_backward_f32(dy_a, dy_b, relu_in, joined, static_cast<size_t>(N) * C * HW, stream);
+  if (st != SGB_OK) return st;
+  return bn_backward<false>(x, joined, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW, ws,
+                            ws_bytes, stream);
 }
 
 // ------------------------------------------------------------ forward (training)
@@ -975,6 +1054,15 @@ int sgb_bn_backward_f32(const float* x, const float* dy, const float* scale, con
                         int C, int HW, void* ws, size_t ws_bytes, void* stream) {
   return bn_backward<false>(x, dy, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
                             ws, ws_bytes, stream);
+}
+
+int sgb_bn_add_relu_backward_f32(const float* x, const float* dy_a, const float* dy_b,
+                                 const float* relu_in, const float* scale, const float* mean,
+                                 const float* invstd, float* joined, float* dx, float* dscale,
+                                 float* dbias, int N, int C, int HW, void* ws, size_t ws_bytes,
+                                 void* stream) {
+  return bn_add_relu_backward(x, dy_a, dy_b, relu_in, scale, mean, invstd, joined, dx, dscale, dbias, N,
+                              C, HW, ws, ws_bytes, stream);
 }
 
 int sgb_bn_forward_training_f32(const float* x, const float* scale, const float* bias,

@@ -159,6 +159,13 @@ class HotPathGPU(object):
                                        (p(a["x"]), p(a["dy"]), p(a["relu_x"]), p(a["scale"]), p(a["mean"]),
                                         p(a["invstd"]), p(a["dx"]), p(a["dscale"]), p(a["dbias"]), n, c, h * w,
                                         ws.data_ptr(), ws.numel(), S)))
+            elif k == "bn_add_relu_bwd":
+                n, c, h, w = t[a["x"]].shape
+                assert L.sgb_bn_backward_workspace_bytes(n, c, h * w) <= ws.numel()
+                self.calls.append(("sgb_bn_add_relu_backward_f32",
+                                   (p(a["x"]), p(a["dy_a"]), p(a["dy_b"]), p(a["relu_x"]), p(a["scale"]),
+                                    p(a["mean"]), p(a["invstd"]), p(a["joined"]), p(a["dx"]), p(a["dscale"]),
+                                    p(a["dbias"]), n, c, h * w, ws.data_ptr(), ws.numel(), S)))
             elif k == "maxpool_bwd":
                 self.calls.append(("sgb_maxpool_backward_f32",
                                    (p(a["x"]), p(a["y"]), p(a["dy"]), p(a["dx"])) + geom(a["x"], a["kernel"], a["stride"], a["pad"]) + (S,)))

@@ -42,6 +42,7 @@ def main(argv=None):
     ap.add_argument("--shape", default="32,256,56,56")
     ap.add_argument("--n", type=int, default=1 << 26)
     ap.add_argument("--relu", action="store_true", help="bn: fused ReLU mask")
+    ap.add_argument("--join", action="store_true", help="bn: fused gradient join + ReLU mask")
     ap.add_argument("--mode", default="compat", help="topk key: compat | magnitude")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -61,7 +62,14 @@ def main(argv=None):
         sc, mu, r = torch.ones(C, device=dev), torch.zeros(C, device=dev), torch.ones(C, device=dev)
         dx, ds, db = torch.empty_like(x), torch.empty(C, device=dev), torch.empty(C, device=dev)
         ws = torch.empty(max(L.sgb_bn_backward_workspace_bytes(N, C, H * W), 256), dtype=torch.uint8, device=dev)
-        if a.relu:
+        if a.join:
+            rx, dyb, jo = torch.randn(shape, device=dev), torch.randn(shape, device=dev) * 1e-2, torch.empty_like(x)
+            fn = lambda: _lib.call("sgb_bn_add_relu_backward_f32", x.data_ptr(), dy.data_ptr(), dyb.data_ptr(),
+                                   rx.data_ptr(), sc.data_ptr(), mu.data_ptr(), r.data_ptr(), jo.data_ptr(),
+                                   dx.data_ptr(), ds.data_ptr(), db.data_ptr(), N, C, H * W, ws.data_ptr(),
+                                   ws.numel(), stream)
+            nbytes = 24 * x.numel() + 20 * C
+        elif a.relu:
             fn = lambda: _lib.call("sgb_bn_relu_backward_f32", x.data_ptr(), dy.data_ptr(), rx.data_ptr(),
                                    sc.data_ptr(), mu.data_ptr(), r.data_ptr(), dx.data_ptr(), ds.data_ptr(),
                                    db.data_ptr(), N, C, H * W, ws.data_ptr(), ws.numel(), stream)

@@ -36,13 +36,15 @@ def conv_out(h, k, stride, pad):
     return (h + 2 * pad - k) // stride + 1
 
 
-def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4, 6, 3)):
+def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4, 6, 3), join_bn=False):
     """Returns dict(tensors, ops, params, grad_order, stats).
 
     fused=False: one op per reference call (ReLUBackward, GpuBatchNormBackward,
     ``+=`` join, ...).  fused=True: the join is folded into the following
     ReLUBackward and ReLUBackward into the following GpuBatchNormBackward
-    (same results, fewer passes over memory)."""
+    (same results, fewer passes over memory).  join_bn=True (with fused) also
+    folds the join + ReLUBackward at a block's end into the batch-norm
+    backward after it; see fuse_plan for why that is not the default."""
     T, ops, params = {}, [], []
     B = batch
 
@@ -140,19 +142,27 @@ def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4,
         n, p4, pl = blk["name"], blk["planes"] * 4, blk["planes"]
         shape3 = (B, p4, blk["h3"], blk["h3"])
         d_add = scratch(n + ".d_add", shape3)
-        if pending_join is not None:
+        join = None
+        if pending_join is not None and not join_bn:
             ops.append(Op("add_relu_bwd", dict(dy_a=pending_join[0], dy_b=pending_join[1], x=n + ".relu3.x", dx=d_add)))
+            pending_join = None
+        elif pending_join is not None:
+            # folded into the batch-norm backward that follows (bn3 reads d_add first)
+            join = dict(dy_a=pending_join[0], dy_b=pending_join[1], relu_x=n + ".relu3.x", joined=d_add)
             pending_join = None
         else:
             ops.append(Op("relu_bwd", dict(dy=dcur, x=n + ".relu3.x", dx=d_add)))
 
-        def bn_bwd(bnname, dy, relu_x=None):
+        def bn_bwd(bnname, dy, relu_x=None, join=None):
             c, hh = T[bnname + ".x"].shape[1], T[bnname + ".x"].shape[2]
             dx = scratch(bnname + ".dx", (B, c, hh, hh))
             args = dict(dy=dy, x=bnname + ".x", scale=bnname + ".scale", mean=bnname + ".mean",
                         invstd=bnname + ".invstd", dx=dx, dscale="d:" + bnname + ".scale",
                         dbias="d:" + bnname + ".bias")
-            if relu_x is not None and fused:
+            if join is not None:
+                del args["dy"]
+                ops.append(Op("bn_add_relu_bwd", dict(args, **join)))
+            elif relu_x is not None and fused:
                 ops.append(Op("bn_relu_bwd", dict(args, relu_x=relu_x)))
             else:
                 if relu_x is not None:
@@ -165,7 +175,7 @@ def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4,
             return dx
 
         # main branch: bn3 <- conv3 <- relu2 <- bn2 <- conv2 <- relu1 <- bn1 <- conv1
-        bn_bwd(n + ".bn3", d_add)
+        bn_bwd(n + ".bn3", d_add, join=join)
         ready(n + ".conv3.W")
         g2 = syn(n + ".conv3.dgrad", (B, pl, blk["h2"], blk["h2"]))      # cudnn bwd-data output
         bn_bwd(n + ".bn2", g2, relu_x=n + ".relu2.x")
@@ -215,23 +225,33 @@ READS = {
     "relu_bwd": ("dy", "x"), "add_relu_bwd": ("dy_a", "dy_b", "x"), "add_out": ("a", "b"),
     "bn_bwd": ("dy", "x", "scale", "mean", "invstd"),
     "bn_relu_bwd": ("dy", "relu_x", "x", "scale", "mean", "invstd"),
+    "bn_add_relu_bwd": ("dy_a", "dy_b", "relu_x", "x", "scale", "mean", "invstd"),
     "maxpool_bwd": ("x", "y", "dy"), "avgpool_bwd": ("dy",), "softmax": ("x",), "ce_fwd": ("p", "t"),
     "sum_all": ("x",), "ce_bwd": ("p", "t"), "ce_grad": ("p", "t"), "scale": ("x",), "sum_rows": ("M",),
     "conv_bias_bwd": ("dy",),
 }
 
 
-def fuse_plan(plan):
+def fuse_plan(plan, join_bn=False):
     """Peephole fusion over a recorded op list (the counterpart of a pass over
     the reference's buffered Graph nodes, keyed on the op kinds):
 
       add_out(a, b -> t) ; relu_bwd(dy=t, x -> dx)       =>  add_relu_bwd(a, b, x -> dx)
       relu_bwd(dy, x=r -> m) ; bn_bwd(dy=m, ...)         =>  bn_relu_bwd(dy, relu_x=r, ...)
+      add_relu_bwd(a, b, x=r -> t) ; bn_bwd(dy=t, ...)   =>  bn_add_relu_bwd(a, b, relu_x=r, joined=t, ...)
+                                                             (only with join_bn=True)
       ce_bwd(p, t -> g) ; scale(g, c)                    =>  ce_grad(p, t, c -> g)
 
     A pair is fused only when the intermediate tensor has no other reader;
-    the intermediate then disappears from the plan.  Results are unchanged
-    bit for bit (the fused kernels perform the same roundings)."""
+    the intermediate then disappears from the plan.  The last rule is the
+    exception: the joined gradient `t` stays (the shortcut branch reads it
+    later) and is written by the fused op, which must be its FIRST reader.
+    It is off by default because it does not pay on B200: it saves 4 of 28
+    bytes per element but moves the join's 16 bytes from a streaming kernel
+    that runs at the copy bandwidth into the batch-norm kernel that reaches
+    about 0.7 of it (measured 130 us fused against 58 + 67 us at 32x256x56x56).
+    Results are unchanged bit for bit (the fused kernels perform the same
+    roundings)."""
     ops = list(plan["ops"])
     readers = {}
     for i, op in enumerate(ops):
@@ -255,13 +275,21 @@ def fuse_plan(plan):
             dead.add(j)
             T.pop(a["dy"], None)
             op = Op("bn_relu_bwd", dict(a, dy=src["dy"], relu_x=src["x"]))
+        elif join_bn and k == "bn_bwd" and a["dy"] in producer and out[producer[a["dy"]]].kind == "add_relu_bwd" \
+                and producer[a["dy"]] not in dead and readers.get(a["dy"], [None])[0] == i:
+            j = producer[a["dy"]]
+            src = out[j].args
+            dead.add(j)
+            rest = {key: v for key, v in a.items() if key != "dy"}
+            op = Op("bn_add_relu_bwd", dict(rest, dy_a=src["dy_a"], dy_b=src["dy_b"], relu_x=src["x"],
+                                            joined=a["dy"]))
         elif k == "scale" and a["x"] in producer and ops[producer[a["x"]]].kind == "ce_bwd":
             j = producer[a["x"]]
             src = ops[j].args
             dead.add(j)
             op = Op("ce_grad", dict(p=src["p"], t=src["t"], scale=a["c"], grad=a["x"]))
         out.append(op)
-        for key in ("dx", "out", "grad", "y", "loss", "v"):
+        for key in ("dx", "out", "grad", "y", "loss", "v", "joined"):
             if key in op.args and isinstance(op.args[key], str):
                 producer[op.args[key]] = i
     # a fused relu_bwd may itself have consumed an add_out: drop everything marked dead
@@ -301,6 +329,9 @@ def algorithmic_bytes(plan, world=1):
         elif op.kind == "bn_relu_bwd":
             s = T[a["x"]].shape
             add("bn_relu_bwd", 16 * numel(s) + 20 * s[1])
+        elif op.kind == "bn_add_relu_bwd":
+            s = T[a["x"]].shape                   # reads x, dy_a, dy_b, relu_x; writes joined, dx
+            add("bn_add_relu_bwd", 24 * numel(s) + 20 * s[1])
         elif op.kind == "maxpool_bwd":
             add("maxpool_bwd", 4 * (2 * numel(T[a["x"]].shape) + 2 * numel(T[a["y"]].shape)))
         elif op.kind == "avgpool_bwd":
@@ -321,7 +352,7 @@ def algorithmic_bytes(plan, world=1):
 # ---------------------------------------------------------------- small configs
 def build_mlp_plan(batch=256, dims=(784, 4096, 4096, 10)):
     """Backward + update path of the reference MLP (Linear-ReLU-Linear-ReLU-Linear,
-    softmax cross entropy; examples/mlp/model.py shape family, BASELINE config 1).
+    softmax cross entropy; examples/mlp/model.py shape family; benchmark configuration 1).
     Matmul gradients are stand-ins (cuBLAS); the bias gradients (SumRows), ReLU
     backward, softmax-CE and the SGD update are computed."""
     T, ops, params, order = {}, [], [], []
@@ -371,7 +402,7 @@ def build_mlp_plan(batch=256, dims=(784, 4096, 4096, 10)):
 
 
 def build_cnn_plan(batch=64, channels=32, num_classes=10):
-    """Backward + update path of the small CNN of BASELINE config 2:
+    """Backward + update path of the small CNN of benchmark configuration 2:
     conv5x5(32)+bias -> ReLU -> maxpool2 -> conv5x5(32)+bias -> ReLU -> maxpool2
     -> linear 500 -> ReLU -> linear 10, on 1x28x28 inputs.  Convolution and
     matmul gradients are stand-ins; conv-bias and linear-bias gradients, ReLU /

@@ -375,6 +375,24 @@ def GpuBatchNormReLUBackward(cbnh, dy, relu_in, x, bnScale, mean, var):
     return [dx, ds, db]
 
 
+def GpuBatchNormAddReLUBackward(cbnh, dy_a, dy_b, relu_in, x, bnScale, mean, var):
+    """The end of a residual block in one pass: the gradient join dy_a + dy_b
+    (autograd.py:204 "+="), ReLUBackward against relu_in, GpuBatchNormBackward.
+    Returns [joined, dx, dbnScale, dbnBias]; ``joined`` is what the shortcut
+    branch consumes."""
+    _chk(dy_a, dy_b, relu_in, x, bnScale, mean, var)
+    n, c, hw = cbnh.batchsize, cbnh.channels, cbnh.height * cbnh.width
+    joined = torch.empty_like(dy_a)
+    dx = torch.empty_like(dy_a)
+    ds = torch.empty_like(bnScale)
+    db = torch.empty_like(bnScale)
+    need = _lib.lib().sgb_bn_backward_workspace_bytes(n, c, hw)
+    ws, wsn = _ws_args(dy_a.device, need)
+    _lib.call("sgb_bn_add_relu_backward_f32", _p(x), _p(dy_a), _p(dy_b), _p(relu_in), _p(bnScale),
+              _p(mean), _p(var), _p(joined), _p(dx), _p(ds), _p(db), n, c, hw, ws, wsn, _stream())
+    return [joined, dx, ds, db]
+
+
 class CudnnPoolingHandle(object):
     """Fields of singa's PoolingHandle (src/model/operation/pooling.h:41-78,
     pooling.cc:27-52)."""

@@ -189,6 +189,29 @@ def test_batchnorm_relu_fused_equals_unfused(sw, oracle, shape):
         close(host(a), b, what="fused bn+relu %s" % (shape,))
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 4, 4), (4, 5, 7, 7), (8, 16, 14, 14), (32, 64, 28, 28), (32, 64, 7, 7),
+                                   (2, 6, 3, 2), (32, 256, 56, 56), (32, 64, 112, 112)])
+def test_batchnorm_join_relu_fused_equals_unfused(sw, oracle, shape):
+    rng = np.random.default_rng(sum(shape) + 2)
+    x, dy_a, scale = bn_case(rng, shape)
+    dy_b = rng.standard_normal(shape).astype(np.float32) * np.float32(1e-2)
+    relu_in = rng.standard_normal(shape).astype(np.float32)
+    relu_in[0, 0].flat[0] = 0.0
+    mean, invstd = oracle.bn_stats(x)
+    h = sw.CudnnBatchNormHandle(0.9, dev(x))
+    joined = sw.AddReLUBackward(dev(dy_a), dev(dy_b), dev(relu_in))
+    unfused = sw.GpuBatchNormBackward(h, joined, dev(x), dev(scale), dev(mean), dev(invstd))
+    fused = sw.GpuBatchNormAddReLUBackward(h, dev(dy_a), dev(dy_b), dev(relu_in), dev(x), dev(scale), dev(mean),
+                                           dev(invstd))
+    for a, b in zip(fused, [joined] + unfused):
+        assert torch.equal(a, b)
+    want_joined = oracle.relu_backward(dy_a + dy_b, relu_in)
+    assert np.array_equal(host(fused[0]), want_joined)
+    want = oracle.bn_backward(want_joined, x, scale, mean, invstd)
+    for a, b in zip(fused[1:], want):
+        close(host(a), b, what="fused join+relu+bn %s" % (shape,))
+
+
 def test_batchnorm_backward_resnet_stem_size(sw, oracle):
     shape = (32, 64, 112, 112)
     rng = np.random.default_rng(11)

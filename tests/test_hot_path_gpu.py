@@ -15,13 +15,14 @@ def close(got, want, rtol, what):
     assert err <= rtol * scale, "%s: rel err %.3e" % (what, err / scale)
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "join_bn"])
 @pytest.mark.parametrize("graph", [False, True])
 def test_small_resnet_step_matches_oracle(fused, graph):
     from oracle.path import OraclePath
     from singa_b200.hot_path import HotPathGPU
     from singa_b200.resnet50_path import build_plan
-    plan = build_plan(batch=4, image=64, num_classes=10, fused=fused, blocks=(2, 1, 1, 1))
+    plan = build_plan(batch=4, image=64, num_classes=10, fused=bool(fused), blocks=(2, 1, 1, 1),
+                      join_bn=fused == "join_bn")
     gpu = HotPathGPU(plan, communicator=None, world=1, seed=5)
     host = gpu.host_copy()
     ref = OraclePath(plan, host)
@@ -62,7 +63,7 @@ def test_fused_and_unfused_plans_agree_bitwise():
 
 @pytest.mark.parametrize("which", ["mlp", "cnn"])
 def test_small_config_steps_match_oracle(which):
-    """BASELINE configs 1 (MLP 784-4096-4096-10, batch 256) and 2 (small CNN,
+    """The two small reference configurations: 1 (MLP 784-4096-4096-10, batch 256) and 2 (small CNN,
     batch 64) at their full sizes: one backward + SGD-momentum step, eager and
     fused, against the oracle executor."""
     from oracle.path import OraclePath

@@ -65,6 +65,11 @@ def test_peephole_pass_reproduces_the_hand_fused_plan():
         by_pass = fuse_plan(build_plan(fused=False, **kw))
         assert key(by_hand) == key(by_pass)
         assert set(by_pass["tensors"]) == set(by_hand["tensors"])
+        by_hand = build_plan(fused=True, join_bn=True, **kw)
+        by_pass = fuse_plan(build_plan(fused=False, **kw), join_bn=True)
+        assert key(by_hand) == key(by_pass)
+        assert any(o.kind == "bn_add_relu_bwd" for o in by_pass["ops"])
+        assert not any(o.kind == "add_relu_bwd" for o in by_pass["ops"])
     # an intermediate with a second reader must not be fused away
     from singa_b200.resnet50_path import Op
     plan = build_plan(batch=2, image=64, num_classes=10, blocks=(1, 1, 1, 1))
