@@ -135,6 +135,33 @@ int sgb_cast_f16_f32_scaled(const void *in, float scale, float *out, size_t n,
 int sgb_axpy_f32(float alpha, const float *x, float *y, size_t n, void *stream);
 int sgb_axpy_dev_alpha_f32(const float *alpha_dev, const float *x, float *y,
                            size_t n, void *stream);
+/* fp16 data, fp32 alpha and arithmetic, one rounding per element
+ * (Axpy<half, lang::Cuda>, tensor_math_cuda.h:1051-1071, cublasAxpyEx). */
+int sgb_axpy_f16(float alpha, const void *x, void *y, size_t n, void *stream);
+int sgb_axpy_dev_alpha_f16(const float *alpha_dev, const void *x, void *y,
+                           size_t n, void *stream);
+
+/* BLAS-1 reductions with the result in DEVICE memory (capturable, no host
+ * round trip) and a fixed summation order.  They stand in for the cuBLAS
+ * calls of Dot / Asum / Nrm2 / Amax / Amin<float, lang::Cuda>
+ * (tensor_math_cuda.h:1001-1029, 1075-1102).  amax / amin write the 0-based
+ * index of the first element with the largest / smallest |x| (the reference
+ * subtracts 1 from cublasIsamax / Isamin).  Workspace: query below. */
+size_t sgb_blas1_workspace_bytes(size_t n);
+int sgb_dot_f32(const float *x, const float *y, float *out, size_t n, void *ws,
+                size_t ws_bytes, void *stream);
+int sgb_asum_f32(const float *x, float *out, size_t n, void *ws,
+                 size_t ws_bytes, void *stream);
+int sgb_nrm2_f32(const float *x, float *out, size_t n, void *ws,
+                 size_t ws_bytes, void *stream);
+int sgb_amax_f32(const float *x, int32_t *index_out, size_t n, void *ws,
+                 size_t ws_bytes, void *stream);
+int sgb_amin_f32(const float *x, int32_t *index_out, size_t n, void *ws,
+                 size_t ws_bytes, void *stream);
+/* Row-major M (nrow x ncol): out = M * diag(v) when side_right, else
+ * diag(v) * M (DGMM<float, lang::Cuda>, tensor_math_cuda.h:1112-1129). */
+int sgb_dgmm_f32(int side_right, const float *M, const float *v, float *out,
+                 size_t nrow, size_t ncol, void *stream);
 
 /* Strided gather out[i] = in[offset(i)] over an nDim-dimensional shape/stride
  * (element strides; 0 = broadcast).  Replaces cuda::traverse_unary_transform
@@ -144,6 +171,18 @@ int sgb_axpy_dev_alpha_f32(const float *alpha_dev, const float *x, float *y,
 int sgb_strided_copy_f32(const float *in, float *out, size_t n, int nDim,
                          const int *shape_host, const int *stride_host,
                          void *stream);
+int sgb_strided_copy_f16(const void *in, void *out, size_t n, int nDim,
+                         const int *shape_host, const int *stride_host,
+                         void *stream);
+/* The same gather with shape/stride in DEVICE memory - the literal calling
+ * convention of cuda::traverse_unary_transform (math_kernel.h:95-100), for an
+ * adapter that keeps that signature. */
+int sgb_strided_copy_dev_f32(const float *in, float *out, size_t n, int nDim,
+                             const int *shape_dev, const int *stride_dev,
+                             void *stream);
+int sgb_strided_copy_dev_f16(const void *in, void *out, size_t n, int nDim,
+                             const int *shape_dev, const int *stride_dev,
+                             void *stream);
 
 /* Sparsification helpers with the reference's exact semantics
  * (math_kernel.h:180-186; math_kernel.cu:628-650):
@@ -210,6 +249,19 @@ int sgb_softmax_cross_entropy_bwd_f32(int int_target, size_t batch, size_t dim,
 int sgb_softmax_cross_entropy_grad_f32(int int_target, size_t batch, size_t dim,
                                        const float *p, const int32_t *t,
                                        float scale, float *grad, void *stream);
+
+/* fp16 forms.  Softmax computes in fp32 and rounds once on store.  The two
+ * cross-entropy kernels keep the half-precision arithmetic of the overloads
+ * they replace (math_kernel.cu:500-537, 588-611): probabilities floored at
+ * half(1e-7), weights converted with round-down, loss and grad in __half. */
+int sgb_softmax_rows_f16(const void *x, void *y, size_t nrow, size_t ncol,
+                         void *stream);
+int sgb_cross_entropy_f16(int int_target, size_t batch, size_t dim,
+                          const void *p, const int32_t *t, void *loss,
+                          void *stream);
+int sgb_softmax_cross_entropy_bwd_f16(int int_target, size_t batch, size_t dim,
+                                      const void *p, const int32_t *t,
+                                      void *grad, void *stream);
 
 /* --------------------------------------------------- batch-norm backward */
 /* Training-mode backward from the saved batch mean and saved INVERSE standard

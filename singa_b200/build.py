@@ -13,6 +13,8 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libsgb.so")
+ADAPTER_SRC = os.path.join(HERE, "adapter", "singa_cuda_launchers.cu")
+ADAPTER_LIB = os.path.join(HERE, "libsgb_singa.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
@@ -60,7 +62,20 @@ def build(verbose=False, force=False):
     if _stale(LIB, objs):
         cmd = ["nvcc", "-shared", "-o", LIB] + objs + ["-lnccl", "-lcudart"]
         subprocess.check_call(cmd)
+    build_adapter()
     return LIB
+
+
+def build_adapter():
+    """libsgb_singa.so: the `singa::cuda::*` launchers (C++ linkage, the
+    reference's signatures) forwarding to libsgb.so, found through $ORIGIN."""
+    if _stale(ADAPTER_LIB, [ADAPTER_SRC, LIB, os.path.join(INCLUDE, "sgb.h")]):
+        cmd = ["nvcc"] + NVCC_FLAGS + ["-shared", ADAPTER_SRC, "-o", ADAPTER_LIB, "-L", HERE, "-lsgb",
+                                       "-Xlinker", "-rpath=$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed for the launcher adapter:\n%s" % r.stderr)
+    return ADAPTER_LIB
 
 
 if __name__ == "__main__":

@@ -388,8 +388,9 @@ struct Dims {
   int shape[8];
   int stride[8];
 };
+template <typename T>
 __global__ void __launch_bounds__(kBlock)
-strided_copy_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n, Dims d) {
+strided_copy_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, Dims d) {
   for (size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; i < n;
        i += static_cast<size_t>(gridDim.x) * kBlock) {
     size_t accu = n, rem = i, off = 0;
@@ -401,6 +402,65 @@ strided_copy_kernel(const float* __restrict__ in, float* __restrict__ out, size_
     }
     out[i] = in[off];
   }
+}
+
+// Same gather with shape / stride read from DEVICE memory (the calling
+// convention of the launcher this replaces); the few ints are staged in shared
+// memory once per CTA.
+template <typename T>
+__global__ void __launch_bounds__(kBlock)
+strided_copy_dev_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, int nd,
+                        const int* __restrict__ shape, const int* __restrict__ stride) {
+  __shared__ int sh[8], st[8];
+  if (threadIdx.x < nd) {
+    sh[threadIdx.x] = shape[threadIdx.x];
+    st[threadIdx.x] = stride[threadIdx.x];
+  }
+  __syncthreads();
+  for (size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * kBlock) {
+    size_t accu = n, rem = i, off = 0;
+    for (int k = 0; k < nd; ++k) {
+      accu /= sh[k];
+      size_t idx = rem / accu;
+      rem -= idx * accu;
+      off += idx * static_cast<size_t>(st[k]);
+    }
+    out[i] = in[off];
+  }
+}
+
+template <typename T>
+int strided_copy(const T* in, T* out, size_t n, int nDim, const int* shape_host,
+                 const int* stride_host, void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!in || !out || !shape_host || !stride_host) return SGB_ERR_NULL;
+  if (nDim < 1 || nDim > 8) return SGB_ERR_SIZE;
+  Dims d;
+  d.nd = nDim;
+  size_t prod = 1;
+  for (int k = 0; k < nDim; ++k) {
+    if (shape_host[k] <= 0 || stride_host[k] < 0) return SGB_ERR_SIZE;
+    d.shape[k] = shape_host[k];
+    d.stride[k] = stride_host[k];
+    prod *= static_cast<size_t>(shape_host[k]);
+  }
+  if (prod != n) return SGB_ERR_SIZE;
+  unsigned grid = capped_grid(n, kBlock, kCtasPerSm);
+  strided_copy_kernel<T><<<grid, kBlock, 0, as_stream(stream)>>>(in, out, n, d);
+  return launch_status();
+}
+
+template <typename T>
+int strided_copy_dev(const T* in, T* out, size_t n, int nDim, const int* shape_dev,
+                     const int* stride_dev, void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!in || !out || !shape_dev || !stride_dev) return SGB_ERR_NULL;
+  if (nDim < 1 || nDim > 8) return SGB_ERR_SIZE;
+  unsigned grid = capped_grid(n, kBlock, kCtasPerSm);
+  strided_copy_dev_kernel<T><<<grid, kBlock, 0, as_stream(stream)>>>(in, out, n, nDim, shape_dev,
+                                                                    stride_dev);
+  return launch_status();
 }
 
 }  // namespace
@@ -564,22 +624,19 @@ int sgb_axpy_dev_alpha_f32(const float* alpha_dev, const float* x, float* y, siz
 
 int sgb_strided_copy_f32(const float* in, float* out, size_t n, int nDim,
                          const int* shape_host, const int* stride_host, void* stream) {
-  if (n == 0) return SGB_OK;
-  if (!in || !out || !shape_host || !stride_host) return SGB_ERR_NULL;
-  if (nDim < 1 || nDim > 8) return SGB_ERR_SIZE;
-  Dims d;
-  d.nd = nDim;
-  size_t prod = 1;
-  for (int k = 0; k < nDim; ++k) {
-    if (shape_host[k] <= 0 || stride_host[k] < 0) return SGB_ERR_SIZE;
-    d.shape[k] = shape_host[k];
-    d.stride[k] = stride_host[k];
-    prod *= static_cast<size_t>(shape_host[k]);
-  }
-  if (prod != n) return SGB_ERR_SIZE;
-  unsigned grid = capped_grid(n, kBlock, kCtasPerSm);
-  strided_copy_kernel<<<grid, kBlock, 0, as_stream(stream)>>>(in, out, n, d);
-  return launch_status();
+  return strided_copy<float>(in, out, n, nDim, shape_host, stride_host, stream);
+}
+int sgb_strided_copy_f16(const void* in, void* out, size_t n, int nDim, const int* shape_host,
+                         const int* stride_host, void* stream) {
+  return strided_copy<__half>(H(in), HO(out), n, nDim, shape_host, stride_host, stream);
+}
+int sgb_strided_copy_dev_f32(const float* in, float* out, size_t n, int nDim,
+                             const int* shape_dev, const int* stride_dev, void* stream) {
+  return strided_copy_dev<float>(in, out, n, nDim, shape_dev, stride_dev, stream);
+}
+int sgb_strided_copy_dev_f16(const void* in, void* out, size_t n, int nDim, const int* shape_dev,
+                             const int* stride_dev, void* stream) {
+  return strided_copy_dev<__half>(H(in), HO(out), n, nDim, shape_dev, stride_dev, stream);
 }
 
 int sgb_sparsabs_f32(float thr, const float* in, float* out, size_t n, void* stream) {

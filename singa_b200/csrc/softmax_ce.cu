@@ -84,6 +84,78 @@ ce_bwd_kernel(int int_target, size_t dim, const float* __restrict__ p,
   }
 }
 
+// ------------------------------------------------------------------- fp16
+// Row softmax on fp16 data: fp32 arithmetic inside, one rounding on store.
+__global__ void __launch_bounds__(kBlock)
+softmax_rows_f16_kernel(const __half* __restrict__ x, __half* __restrict__ y, size_t ncol) {
+  __shared__ float sm[32];
+  const __half* xr = x + blockIdx.x * ncol;
+  __half* yr = y + blockIdx.x * ncol;
+  float m = __half2float(xr[0]);
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) m = fmaxf(m, __half2float(xr[c]));
+  m = warp_max(m);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) sm[w] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
+  float s = 0.f;
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) s += expf(__half2float(xr[c]) - m);
+  s = block_sum(s, sm);
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock)
+    yr[c] = __float2half_rn(expf(__half2float(xr[c]) - m) / s);
+}
+
+// fp16 cross entropy with the arithmetic of the fp16 kernel it replaces: all
+// steps in half precision, probabilities floored at half(1e-7), integer
+// weights converted with round-down, the per-sample sums formed serially.
+__global__ void ce_fwd_f16_kernel(int int_target, size_t batch, size_t dim,
+                                  const __half* __restrict__ p, const int* __restrict__ t,
+                                  __half* __restrict__ loss) {
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (i >= batch) return;
+  const __half eps = __float2half_rn(0.0000001f);
+  if (int_target) {
+    const __half pt = p[i * dim + t[i]];
+    loss[i] = __hneg(hlog(__hgt(pt, eps) ? pt : eps));
+  } else {
+    __half sum = __float2half_rn(0.f);
+    for (size_t j = 0; j < dim; ++j) sum = __hadd(sum, __int2half_rd(t[i * dim + j]));
+    __half l = __float2half_rn(0.f);
+    for (size_t j = 0; j < dim; ++j) {
+      const __half pj = p[i * dim + j];
+      l = __hsub(l, __hmul(__hdiv(__int2half_rd(t[i * dim + j]), sum), hlog(__hgt(pj, eps) ? pj : eps)));
+    }
+    loss[i] = l;
+  }
+}
+
+// grad = p - target in half precision; one CTA per sample row.  The integer
+// weights of an array target are small, so their half sum is exact in any
+// order as long as it stays below 2048.
+__global__ void __launch_bounds__(kBlock)
+ce_bwd_f16_kernel(int int_target, size_t dim, const __half* __restrict__ p,
+                  const int* __restrict__ t, __half* __restrict__ grad) {
+  __shared__ __half total;
+  const size_t row = blockIdx.x;
+  const __half* pr = p + row * dim;
+  __half* gr = grad + row * dim;
+  if (int_target) {
+    const size_t hot = static_cast<size_t>(t[row]);
+    for (size_t j = threadIdx.x; j < dim; j += kBlock)
+      gr[j] = j == hot ? __hsub(pr[j], __int2half_rn(1)) : pr[j];
+  } else {
+    const int* tr = t + row * dim;
+    if (threadIdx.x == 0) {
+      __half sum = __float2half_rn(0.f);
+      for (size_t j = 0; j < dim; ++j) sum = __hadd(sum, __int2half_rd(tr[j]));
+      total = sum;
+    }
+    __syncthreads();
+    for (size_t j = threadIdx.x; j < dim; j += kBlock)
+      gr[j] = __hsub(pr[j], __hdiv(__int2half_rd(tr[j]), total));
+  }
+}
+
 }  // namespace
 }  // namespace sgb
 
@@ -126,6 +198,35 @@ int sgb_softmax_cross_entropy_grad_f32(int int_target, size_t batch, size_t dim,
   if (batch > 0x7fffffffu) return SGB_ERR_SIZE;
   ce_bwd_kernel<true><<<static_cast<unsigned>(batch), kBlock, 0, as_stream(stream)>>>(
       int_target, dim, p, t, grad, scale);
+  return launch_status();
+}
+
+int sgb_softmax_rows_f16(const void* x, void* y, size_t nrow, size_t ncol, void* stream) {
+  if (nrow == 0 || ncol == 0) return SGB_OK;
+  if (!x || !y) return SGB_ERR_NULL;
+  if (nrow > 0x7fffffffu) return SGB_ERR_SIZE;
+  softmax_rows_f16_kernel<<<static_cast<unsigned>(nrow), kBlock, 0, as_stream(stream)>>>(
+      static_cast<const __half*>(x), static_cast<__half*>(y), ncol);
+  return launch_status();
+}
+
+int sgb_cross_entropy_f16(int int_target, size_t batch, size_t dim, const void* p, const int32_t* t,
+                          void* loss, void* stream) {
+  if (batch == 0) return SGB_OK;
+  if (!p || !t || !loss) return SGB_ERR_NULL;
+  if (dim == 0) return SGB_ERR_SIZE;
+  ce_fwd_f16_kernel<<<static_cast<unsigned>(ceil_div(batch, 128)), 128, 0, as_stream(stream)>>>(
+      int_target, batch, dim, static_cast<const __half*>(p), t, static_cast<__half*>(loss));
+  return launch_status();
+}
+
+int sgb_softmax_cross_entropy_bwd_f16(int int_target, size_t batch, size_t dim, const void* p,
+                                      const int32_t* t, void* grad, void* stream) {
+  if (batch == 0 || dim == 0) return SGB_OK;
+  if (!p || !t || !grad) return SGB_ERR_NULL;
+  if (batch > 0x7fffffffu) return SGB_ERR_SIZE;
+  ce_bwd_f16_kernel<<<static_cast<unsigned>(batch), kBlock, 0, as_stream(stream)>>>(
+      int_target, dim, static_cast<const __half*>(p), t, static_cast<__half*>(grad));
   return launch_status();
 }
 

@@ -156,11 +156,14 @@ def Axpy(alpha, inp, out):
     """core_tensor.i:345-347: ``out += alpha * in``; alpha is a python float
     or a one-element device tensor."""
     _chk(inp, out)
+    sfx = _suffix(inp)
+    assert out.dtype == inp.dtype
     if isinstance(alpha, torch.Tensor):
         _chk(alpha)
-        _lib.call("sgb_axpy_dev_alpha_f32", _p(alpha), _p(inp), _p(out), inp.numel(), _stream())
+        alpha = alpha if alpha.dtype == _F32 else alpha.float()   # AsType(kFloat32), tensor_math_cuda.h:1056
+        _lib.call("sgb_axpy_dev_alpha_" + sfx, _p(alpha), _p(inp), _p(out), inp.numel(), _stream())
     else:
-        _lib.call("sgb_axpy_f32", float(alpha), _p(inp), _p(out), inp.numel(), _stream())
+        _lib.call("sgb_axpy_" + sfx, float(alpha), _p(inp), _p(out), inp.numel(), _stream())
     return out
 
 
@@ -173,10 +176,10 @@ def Transform(t_storage, shape, stride):
     n = 1
     for s in shape:
         n *= s
-    out = torch.empty(tuple(shape), dtype=_F32, device=t_storage.device)
+    out = torch.empty(tuple(shape), dtype=t_storage.dtype, device=t_storage.device)
     sh = (C.c_int * len(shape))(*shape)
     st = (C.c_int * len(shape))(*stride)
-    _lib.call("sgb_strided_copy_f32", _p(t_storage), _p(out), n, len(shape),
+    _lib.call("sgb_strided_copy_" + _suffix(t_storage), _p(t_storage), _p(out), n, len(shape),
               C.cast(sh, C.c_void_p), C.cast(st, C.c_void_p), _stream())
     return out
 
@@ -241,6 +244,54 @@ def SumAll(t):
     return out
 
 
+def _blas1(fn, out_dtype, *tensors):
+    _chk(*tensors)
+    n = tensors[0].numel()
+    out = torch.empty(1, dtype=out_dtype, device=tensors[0].device)
+    ws, wsn = _ws_args(tensors[0].device, _lib.lib().sgb_blas1_workspace_bytes(n))
+    _lib.call(fn, *([_p(t) for t in tensors] + [_p(out), n, ws, wsn, _stream()]))
+    return out
+
+
+def Dot(a, b):
+    """Dot<float, lang::Cuda> (tensor_math_cuda.h:1084-1094, the Tensor*
+    overload): one-element DEVICE tensor, no host synchronisation."""
+    assert a.numel() == b.numel()
+    return _blas1("sgb_dot_f32", _F32, a, b)
+
+
+def Asum(t):
+    """Asum<float, lang::Cuda> (tensor_math_cuda.h:1023-1029): sum of |x|."""
+    return _blas1("sgb_asum_f32", _F32, t)
+
+
+def Nrm2(t):
+    """Nrm2<float, lang::Cuda> (tensor_math_cuda.h:1097-1102)."""
+    return _blas1("sgb_nrm2_f32", _F32, t)
+
+
+def Amax(t):
+    """Amax<float, lang::Cuda> (tensor_math_cuda.h:1001-1009): 0-based index of
+    the first element with the largest magnitude (int32 device tensor)."""
+    return _blas1("sgb_amax_f32", _I32, t)
+
+
+def Amin(t):
+    """Amin<float, lang::Cuda> (tensor_math_cuda.h:1012-1020): smallest magnitude."""
+    return _blas1("sgb_amin_f32", _I32, t)
+
+
+def DGMM(side_right, M, v):
+    """DGMM<float, lang::Cuda> (tensor_math_cuda.h:1112-1129): M * diag(v) when
+    side_right else diag(v) * M, row-major M."""
+    _chk(M, v)
+    nrow, ncol = M.shape
+    assert v.numel() == (ncol if side_right else nrow)
+    out = torch.empty_like(M)
+    _lib.call("sgb_dgmm_f32", int(bool(side_right)), _p(M), _p(v), _p(out), nrow, ncol, _stream())
+    return out
+
+
 def RowMax(t):
     _chk(t)
     v = torch.empty(t.shape[0], dtype=_F32, device=t.device)
@@ -273,7 +324,7 @@ def SoftMax(t, axis=None):
         for s in t.shape[:axis]:
             nrow *= s
     y = torch.empty_like(t)
-    _lib.call("sgb_softmax_rows_f32", _p(t), _p(y), nrow, t.numel() // max(nrow, 1), _stream())
+    _lib.call("sgb_softmax_rows_" + _suffix(t), _p(t), _p(y), nrow, t.numel() // max(nrow, 1), _stream())
     return y
 
 
@@ -288,8 +339,8 @@ def CrossEntropyFwd(p, t):
     """core_tensor.i:387."""
     _chk(p, t)
     batch, dim, it = _ce_dims(p, t)
-    loss = torch.empty(batch, dtype=_F32, device=p.device)
-    _lib.call("sgb_cross_entropy_f32", it, batch, dim, _p(p), _p(t), _p(loss), _stream())
+    loss = torch.empty(batch, dtype=p.dtype, device=p.device)
+    _lib.call("sgb_cross_entropy_" + _suffix(p), it, batch, dim, _p(p), _p(t), _p(loss), _stream())
     return loss
 
 
@@ -298,7 +349,7 @@ def SoftmaxCrossEntropyBwd(p, t):
     _chk(p, t)
     batch, dim, it = _ce_dims(p, t)
     g = torch.empty_like(p)
-    _lib.call("sgb_softmax_cross_entropy_bwd_f32", it, batch, dim, _p(p), _p(t), _p(g), _stream())
+    _lib.call("sgb_softmax_cross_entropy_bwd_" + _suffix(p), it, batch, dim, _p(p), _p(t), _p(g), _stream())
     return g
 
 

@@ -185,5 +185,26 @@ def main(root):
     print("wrote", out)
 
 
+def launcher_symbols():
+    """Mangled names of the `singa::cuda::*` launchers (those taking a stream)
+    exported by the reference's math_kernel.cu once compiled here
+    (oracle/ref_build.py -> oracle/_ref/libref_cuda.so), one per line: the
+    symbol contract of the drop-in launcher library."""
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    lib = os.path.join(os.path.dirname(os.path.dirname(here)), "oracle", "_ref", "libref_cuda.so")
+    if not os.path.exists(lib):
+        print("skipped launcher symbols:", lib, "not built")
+        return
+    rows = subprocess.run(["nm", "-D", "--defined-only", lib], capture_output=True, text=True, check=True).stdout
+    names = sorted(r.split()[2] for r in rows.splitlines()
+                   if "_ZN5singa4cuda" in r and "P11CUstream_st" in r and r.split()[1] == "T")
+    out = os.path.join(here, "singa_cuda_launcher_symbols.txt")
+    with open(out, "w") as f:
+        f.write("\n".join(names) + "\n")
+    print("wrote", out, len(names))
+
+
 if __name__ == "__main__":
     main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    launcher_symbols()
