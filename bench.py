@@ -132,6 +132,103 @@ def reference_main(args, rank, world):
     print(json.dumps(line))
 
 
+def sparse_main(args, rank, world, local):
+    """Sparse gradient exchange: every step each rank selects from a fresh flat
+    gradient (plus its residual), all ranks exchange [index | value] payloads
+    and every rank scatter-adds all payloads into the dense result.  One JSON
+    line: steps/s of the whole job, per-step time (max over ranks), payload."""
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("SGB_BENCH_WATCHDOG_S", "900")), exit=True)
+    import torch
+    import torch.distributed as dist
+    from singa_b200 import _lib
+    from singa_b200.communicator import Communicator, NcclIdHolder
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+    _lib.lib()
+    torch.cuda.set_device(local)
+    multi = world > 1
+    if multi:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    box = [NcclIdHolder().id if rank == 0 else None]
+    if multi:
+        dist.broadcast_object_list(box, src=0)
+    n = args.elements
+    comm = Communicator(local, world, NcclIdHolder(box[0]), buffSize=n)
+    topk = args.workload == "sparse_topk"
+    spars = 0.01 if topk else 2e-3
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    fresh = min(K, 20)                       # distinct gradients held on the device (0.4 GB each)
+    gen = torch.Generator(device="cuda")
+    grads = []
+    for step in range(fresh):
+        gen.manual_seed(20 * rank + step)
+        grads.append(torch.randn(n, device="cuda", generator=gen) * 1e-3)
+    work = torch.empty(n, device="cuda")
+    acc = torch.zeros(n, device="cuda")
+
+    def step(k):
+        work.copy_(grads[k % fresh])         # the exchange overwrites its input with the dense result
+        comm.sparsification(work, acc, spars, topk)
+        comm.wait()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+
+    for k in range(W):
+        step(k)
+    acc.zero_()
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0.record()
+    for k in range(K):
+        step(k)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / K
+    if multi:
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    # the copy of the fresh gradient is part of the loop but not of the exchange: time it alone
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for k in range(K):
+        work.copy_(grads[k % fresh])
+    c1.record()
+    torch.cuda.synchronize()
+    copy_ms = c0.elapsed_time(c1) / K
+    nnz = int((work != 0).sum().item())
+    peak, peak_kind = measured_peak()
+    alg = 16.0 * n                            # read g, read acc, write acc, write dense result
+    ex_ms = ms - copy_ms
+    if rank == 0:
+        print(json.dumps({
+            "metric": "sparse_gradient_exchange_elements_per_sec", "value": n * world / (ex_ms / 1e3),
+            "unit": "elements/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ex_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "elements_per_gpu": n, "spars": spars, "residual": True,
+                       "topk_mode": "compat" if topk else None, "fresh_gradients": fresh,
+                       "loop_ms_incl_gradient_copy": ms, "dense_nonzeros_after_last_step": nnz,
+                       "l2": "inputs larger than L2: 0.4 GB per operand"},
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": round(alg / ex_ms / 1e6, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(alg / ex_ms / 1e6 / peak, 4), "peak_kind": peak_kind, "traffic": None,
+                         "algorithmic_bytes_per_step": alg},
+        }), flush=True)
+    torch.cuda.synchronize()
+    comm.close()
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -141,6 +238,10 @@ def main():
     ap.add_argument("--dist-option", default="plain", choices=["plain", "half"])
     ap.add_argument("--call-pattern", action="store_true",
                     help="one kernel per reference call (no cross-op fusion)")
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "sparse_topk", "sparse_threshold"],
+                    help="resnet50 (headline) or the sparse gradient exchange microbench: a flat 1e8-element "
+                         "fp32 gradient N(0, 1e-3^2), residual accumulation on, top-K ratio 0.01 / threshold 2e-3")
+    ap.add_argument("--elements", type=int, default=100000000)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -149,6 +250,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         return reference_main(args, rank, world)
+    if args.workload != "resnet50":
+        return sparse_main(args, rank, world, local)
 
     import faulthandler
     # A rank that stops making progress ends itself with a traceback instead of

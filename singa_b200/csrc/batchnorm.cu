@@ -212,11 +212,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // the ReLU input; it is formed while staging, kept in shared memory for the
 // two later phases and ALSO written to `joined` for the other consumers of the
 // join (the shortcut branch), which replaces a separate join+ReLU kernel.
-// REG (only with VEC): x and dy travel through registers instead of
-// asynchronous copies; the two sums are accumulated as the data arrive and the
-// (masked) values are parked in shared memory for phase 3, so the separate
-// reduction pass over shared memory disappears.
-template <bool VEC, bool MASK, int T, bool ADD = false, bool REG = false>
+template <bool VEC, bool MASK, int T, bool ADD = false>
 __global__ void __launch_bounds__(T)
 bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ relu_in, const float* __restrict__ scale,
@@ -243,42 +239,8 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
   const size_t chan_off = static_cast<size_t>(c) * sh.HW;
 
-  float s_dy = 0.f, s_dyx = 0.f;
   // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
-  if (VEC && REG && !ADD) {
-    constexpr int kB = MASK ? 3 : 4;                 // units per round: 8-9 independent 16-byte loads
-    UnitWalk w(first, T, hwu);
-    for (int u = first; u < u1;) {
-      Vec4f vx[kB], vg[kB], vr[kB];
-      int ls[kB], cnt = 0;
-#pragma unroll
-      for (int j = 0; j < kB; ++j) {
-        if (u < u1) {
-          const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4;
-          ls[j] = (u - u0) * 4;
-          vx[j].u = ld128(x + off);
-          vg[j].u = ld128(dy + off);
-          if (MASK) vr[j].u = ld128(relu_in + off);
-          u += T;
-          w.next();
-          cnt = j + 1;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kB; ++j) {
-        if (j < cnt) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (MASK) vg[j].f[k] = vr[j].f[k] > 0 ? vg[j].f[k] : 0.0f;
-            s_dy += vg[j].f[k];
-            s_dyx += vg[j].f[k] * (vx[j].f[k] - mu);
-          }
-          *reinterpret_cast<uint4*>(sx + ls[j]) = vx[j].u;
-          *reinterpret_cast<uint4*>(sg + ls[j]) = vg[j].u;
-        }
-      }
-    }
-  } else if (VEC && ADD) {
+  if (VEC && ADD) {
     UnitWalk w(first, T, hwu);
     for (int u = first; u < u1;) {
       // two units per round: x by asynchronous copy, the three gradient-side
@@ -330,7 +292,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   // fused ReLU: while the copies fly, read the ReLU input and keep only the
   // sign decisions, 4 bits per unit (a share is at most 16 units per thread)
   unsigned long long keep = 0;
-  if (VEC && MASK && !ADD && !REG) {
+  if (VEC && MASK && !ADD) {
     UnitWalk w(first, T, hwu);
     int slot = 0;
     for (int u = first; u < u1;) {
@@ -359,10 +321,11 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       }
     }
   }
-  if (VEC && !REG) cp_async_wait_all();
+  if (VEC) cp_async_wait_all();
 
   // phase 2: partial sums over the share (each thread re-reads what it staged)
-  if (!(VEC && REG && !ADD)) {
+  float s_dy = 0.f, s_dyx = 0.f;
+  {
     int slot = 0;
     for (int u = first; u < u1; u += T, slot += 4) {
       const int l = (u - u0) * kW;
@@ -599,12 +562,12 @@ int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int 
   return 0;
 }
 
-template <bool VEC, bool MASK, int T, bool ADD = false, bool REG = false>
+template <bool VEC, bool MASK, int T, bool ADD = false>
 int launch_cluster_t(const float* x, const float* dy, const float* relu_in, const float* scale,
                      const float* mean, const float* invstd, float* dx, float* dscale,
                      float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s,
                      const float* dy_b = nullptr, float* joined = nullptr) {
-  auto kernel = bn_bwd_cluster_kernel<VEC, MASK, T, ADD, REG>;
+  auto kernel = bn_bwd_cluster_kernel<VEC, MASK, T, ADD>;
   const size_t smem = static_cast<size_t>(per_cta) * (VEC ? 16 : 4) * 2;
   // Opt in to > 48 KB of dynamic shared memory once per device and kernel
   // instantiation (the attribute sticks to the function in that context), so
@@ -642,12 +605,6 @@ template <bool VEC, bool MASK>
 int launch_cluster(const float* x, const float* dy, const float* relu_in, const float* scale,
                    const float* mean, const float* invstd, float* dx, float* dscale,
                    float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s) {
-  // Small shares with the fused mask: loads through registers (sums formed as
-  // the data arrive, no sign-bit bookkeeping) measure 7-9 % faster than the
-  // asynchronous copies; for large shares the copies win by 20 %.
-  if (VEC && MASK && per_cta <= 2048)
-    return launch_cluster_t<VEC, MASK, 256, false, VEC && MASK>(x, dy, relu_in, scale, mean, invstd, dx,
-                                                                dscale, dbias, sh, cs, per_cta, s);
   // at most 16 units per thread (the fused mask keeps 4 bits per unit in 64 bits)
   if (per_cta > 2048)
     return launch_cluster_t<VEC, MASK, 512>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias,
