@@ -196,6 +196,7 @@ def sparse_main(args, rank, world, local):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
+    nnz = int((work != 0).sum().item())       # non-zeros of the last dense result
     # the copy of the fresh gradient is part of the loop but not of the exchange: time it alone
     c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     c0.record()
@@ -204,7 +205,6 @@ def sparse_main(args, rank, world, local):
     c1.record()
     torch.cuda.synchronize()
     copy_ms = c0.elapsed_time(c1) / K
-    nnz = int((work != 0).sum().item())
     peak, peak_kind = measured_peak()
     alg = 16.0 * n                            # read g, read acc, write acc, write dense result
     ex_ms = ms - copy_ms

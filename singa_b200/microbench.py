@@ -73,6 +73,8 @@ def main(argv=None):
     ap.add_argument("--relu", action="store_true", help="bn: fused ReLU mask")
     ap.add_argument("--join", action="store_true", help="bn: fused gradient join + ReLU mask")
     ap.add_argument("--mode", default="compat", help="topk key: compat | magnitude")
+    ap.add_argument("--graph", action="store_true",
+                    help="time a CUDA-graph replay of the calls (no host launch cost; same buffers every call)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args(argv)
@@ -185,7 +187,14 @@ def main(argv=None):
                                    mode, idx.data_ptr(), val.data_ptr(), ws.data_ptr(), ws.numel(), stream)
         nbytes = 12 * n
 
-    ms = timed(fn, a.iters, a.warmup)
+    if a.graph:
+        def fn_s(i, st):
+            nonlocal stream
+            stream = st
+            fn()
+        ms = timed_graph(fn_s, a.iters)
+    else:
+        ms = timed(fn, a.iters, a.warmup)
     print(json.dumps({"case": a.case, "shape": a.shape if a.case in ("bn", "maxpool", "avgpool") else n,
                       "fused_relu": bool(a.relu), "algorithmic_bytes": nbytes, "us": round(ms * 1e3, 2),
                       "GBps": round(nbytes / ms / 1e6, 1)}))
