@@ -97,8 +97,10 @@ def test_elementwise_not_slower_than_reference_launcher(libs, op):
     record(op + "_25.7M", ours, ref, 12 * n, 1.05)
 
 
-@pytest.mark.parametrize("shape", [(32, 64, 112, 112), (32, 256, 56, 56), (32, 512, 28, 28), (32, 1024, 14, 14),
-                                   (32, 2048, 7, 7)])
+# every distinct batch-norm shape of ResNet-50 at batch 32
+@pytest.mark.parametrize("shape", [(32, 64, 112, 112), (32, 64, 56, 56), (32, 256, 56, 56), (32, 128, 56, 56),
+                                   (32, 128, 28, 28), (32, 512, 28, 28), (32, 256, 28, 28), (32, 256, 14, 14),
+                                   (32, 1024, 14, 14), (32, 512, 14, 14), (32, 512, 7, 7), (32, 2048, 7, 7)])
 def test_batchnorm_backward_not_slower_than_cudnn(libs, shape):
     L, _, rd = libs
     N, Cc, H, W = shape
@@ -143,3 +145,44 @@ def test_pooling_backward_not_slower_than_cudnn(libs):
             alg = 4 * (nx + ny)
         ref = graph_time(lambda q, s: rd.refcudnn_pooling(1, is_max, *args, p(x[q]), p(y[q]), p(dy[q]), p(dx[q]), s), sets)
         record(name, ours, ref, alg, 1.0)
+
+
+def test_topk_selection_not_slower_than_reference_sort(libs):
+    """Top-K selection step of the sparse exchange at the benchmark size: the
+    reference generates indices and sorts all 10^8 (value, index) pairs
+    (communicator.cc:741-750 -> generateindex, sortbykey); the new path selects
+    with a three-pass radix select.  Event-timed, eager (Thrust allocates)."""
+    L, rc, _ = libs
+    n = 100000000
+    k = L.sgb_topk_count(0.01, n)
+    g = torch.randn(n, device="cuda") * 1e-3
+    acc = torch.zeros(n, device="cuda")
+    scratch = torch.empty(n, device="cuda")
+    idx, val = torch.empty(n, dtype=torch.int32, device="cuda"), torch.empty(n, device="cuda")
+    ws = torch.empty(L.sgb_sparse_workspace_bytes(n), dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) * 1e3
+            best = t if best is None or t < best else best
+        return best
+
+    ours = timed(lambda: L.sgb_sparse_topk_f32(p(g), p(acc), p(scratch), n, k, 1, p(idx), p(val), p(ws), ws.numel(),
+                                               None), 5)
+    key = torch.empty(n, device="cuda")
+
+    def reference():
+        key.copy_(g)
+        rc.ref_generateindex(C.c_size_t(n), p(idx), None)
+        rc.ref_sortbykey(C.c_size_t(n), p(key), p(idx), None)
+
+    ref = timed(reference, 2)
+    record("topk_select_1e8_k1e6", ours, ref, 12 * n, 1.0)
