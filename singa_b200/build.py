@@ -60,7 +60,7 @@ def build(verbose=False, force=False):
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(lambda s: _compile(s, verbose), sources()))
     if _stale(LIB, objs):
-        cmd = ["nvcc", "-shared", "-o", LIB] + objs + ["-lnccl", "-lcudart"]
+        cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] + objs + ["-lnccl", "-lcudart"]
         subprocess.check_call(cmd)
     build_adapter()
     return LIB

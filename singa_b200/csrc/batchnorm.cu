@@ -439,18 +439,39 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   float* sg = stage + static_cast<size_t>(sh.N) * run;
   const size_t sample_stride = static_cast<size_t>(sh.C) * sh.HW;
   const size_t base = static_cast<size_t>(c0) * sh.HW;
-  for (int u = threadIdx.x; u < units; u += kBlock) {
-    const int n = u / run4, q = u - n * run4;
-    const size_t off = n * sample_stride + base + 4 * static_cast<size_t>(q);
-    cp_async16(sx + 4 * u, x + off);
-    if (MASK) {
-      Vec4f g, m;
-      g.u = ld128(dy + off);
-      m.u = ld128(relu_in + off);
+  UnitWalk wl(threadIdx.x, kBlock, run4);
+  if (MASK) {
+    // x by asynchronous copy; dy and the ReLU input through registers, four
+    // units (eight independent 16-byte loads) per round
+    for (int u = threadIdx.x; u < units;) {
+      Vec4f vg[4], vm[4];
+      int us[4], cnt = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) g.f[k] = m.f[k] > 0 ? g.f[k] : 0.0f;
-      *reinterpret_cast<uint4*>(sg + 4 * u) = g.u;
-    } else {
+      for (int j = 0; j < 4; ++j) {
+        if (u < units) {
+          const size_t off = wl.n * sample_stride + base + 4 * static_cast<size_t>(wl.q);
+          cp_async16(sx + 4 * u, x + off);
+          vg[j].u = ld128(dy + off);
+          vm[j].u = ld128(relu_in + off);
+          us[j] = u;
+          u += kBlock;
+          wl.next();
+          cnt = j + 1;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < cnt) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) vg[j].f[k] = vm[j].f[k] > 0 ? vg[j].f[k] : 0.0f;
+          *reinterpret_cast<uint4*>(sg + 4 * us[j]) = vg[j].u;
+        }
+      }
+    }
+  } else {
+    for (int u = threadIdx.x; u < units; u += kBlock, wl.next()) {
+      const size_t off = wl.n * sample_stride + base + 4 * static_cast<size_t>(wl.q);
+      cp_async16(sx + 4 * u, x + off);
       cp_async16(sg + 4 * u, dy + off);
     }
   }
@@ -463,11 +484,13 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const float mu = mean[c];
   const int per = sh.N * sh.HW;
   float s_dy = 0.f, s_dyx = 0.f;
-  for (int e = t; e < per; e += kSub) {
-    const int n = e / sh.HW, i = e - n * sh.HW;
-    const int l = n * run + g * sh.HW + i;
-    s_dy += sg[l];
-    s_dyx += sg[l] * (sx[l] - mu);
+  {
+    UnitWalk w(t, kSub, sh.HW);                       // (sample, position) without a division per step
+    for (int e = t; e < per; e += kSub, w.next()) {
+      const int l = w.n * run + g * sh.HW + w.q;
+      s_dy += sg[l];
+      s_dyx += sg[l] * (sx[l] - mu);
+    }
   }
   // reduce inside the sub-group (kSub is a multiple of 32: whole warps per channel)
   s_dy = warp_sum(s_dy);
@@ -497,16 +520,20 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   }
   __syncthreads();
   const float k_ = coef[g][0], am = coef[g][1], bm = coef[g][2];
-  for (int e = t; e < per; e += kSub) {
-    const int n = e / sh.HW, i = e - n * sh.HW;
-    const int l = n * run + g * sh.HW + i;
-    sg[l] = k_ * (sg[l] - am - (sx[l] - mu) * bm);          // dx in place
+  {
+    UnitWalk w(t, kSub, sh.HW);
+    for (int e = t; e < per; e += kSub, w.next()) {
+      const int l = w.n * run + g * sh.HW + w.q;
+      sg[l] = k_ * (sg[l] - am - (sx[l] - mu) * bm);        // dx in place
+    }
   }
   __syncthreads();
-  for (int u = threadIdx.x; u < units; u += kBlock) {
-    const int n = u / run4, q = u - n * run4;
-    const size_t off = n * sample_stride + base + 4 * static_cast<size_t>(q);
-    st128(dx + off, *reinterpret_cast<const uint4*>(sg + 4 * u));
+  {
+    UnitWalk w(threadIdx.x, kBlock, run4);
+    for (int u = threadIdx.x; u < units; u += kBlock, w.next()) {
+      const size_t off = w.n * sample_stride + base + 4 * static_cast<size_t>(w.q);
+      st128(dx + off, *reinterpret_cast<const uint4*>(sg + 4 * u));
+    }
   }
 }
 
@@ -670,9 +697,7 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
   if (!vec && HW > 1 && aligned16(x) && aligned16(dy) && aligned16(dx) && (!MASK || aligned16(relu_in))) {
     // odd planes: groups of adjacent channels make 16-byte runs (7x7 layers)
     const int G = (HW % 2) ? 4 : 2;
-    // worth it only when the groups still fill the machine (fewer, larger CTAs otherwise lose)
-    if ((HW * G) % 4 == 0 && C % G == 0 && static_cast<long long>(G) * per_channel * 8 <= 100 * 1024 &&
-        C / G >= 2 * sm_count()) {
+    if ((HW * G) % 4 == 0 && C % G == 0 && static_cast<long long>(G) * per_channel * 8 <= 100 * 1024) {
       if (G == 4)
         return launch_group<MASK, 4>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
       return launch_group<MASK, 2>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);

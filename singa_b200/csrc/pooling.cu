@@ -247,10 +247,16 @@ struct StemPlan {
   int bands;
 };
 
+// WC: plane width known at compile time (0 = use the run-time value); with a
+// constant width the row / column splits below compile to multiply-shift
+// sequences instead of integer divisions, a quarter of the kernel's instructions.
+template <int WC>
 __global__ void __launch_bounds__(kBlock)
 maxpool_bwd_k3s2p1_kernel(const float* __restrict__ x, const float* __restrict__ dy,
-                          float* __restrict__ dx, int H, int W, int OH, int OW, int rows) {
+                          float* __restrict__ dx, int H, int W_rt, int OH, int OW_rt, int rows) {
   extern __shared__ float smem[];
+  const int W = WC ? WC : W_rt;
+  const int OW = WC ? WC / 2 : OW_rt;
   const int pitch = W + 4;                       // xs[r][4 + c] = x[xr0 + r][c], xs[r][3] = -FLT_MAX
   const int wp = OW + 1;                         // winner / dy pitch (one never-matching pad column)
   const int h_lo = blockIdx.y * rows, h_hi = min(h_lo + rows, H);
@@ -510,8 +516,17 @@ int sgb_maxpool_backward_f32(const float* x, const float* y, const float* dy, fl
       const size_t bytes = (static_cast<size_t>(rows + 3) * (W + 4) +
                             2 * static_cast<size_t>((rows >> 1) + 2) * (p.OW + 1)) * sizeof(float);
       if (bytes <= 48 * 1024 && nbands <= 65535) {
-        maxpool_bwd_k3s2p1_kernel<<<dim3(static_cast<unsigned>(planes), nbands), kBlock, bytes, s>>>(
-            x, dy, dx, H, W, p.OH, p.OW, rows);
+        const dim3 g(static_cast<unsigned>(planes), nbands);
+#define SGB_STEM_W(WW)                                                                              \
+  if (W == WW && p.OW == WW / 2) {                                                                  \
+    maxpool_bwd_k3s2p1_kernel<WW><<<g, kBlock, bytes, s>>>(x, dy, dx, H, W, p.OH, p.OW, rows);      \
+    return launch_status();                                                                         \
+  }
+        SGB_STEM_W(112)
+        SGB_STEM_W(56)
+        SGB_STEM_W(32)
+#undef SGB_STEM_W
+        maxpool_bwd_k3s2p1_kernel<0><<<g, kBlock, bytes, s>>>(x, dy, dx, H, W, p.OH, p.OW, rows);
         return launch_status();
       }
     }
