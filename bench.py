@@ -413,7 +413,7 @@ def main():
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
                        "global_batch": BATCH * world, "dist_option": args.dist_option,
-                       "fusion": "bn+relu, join+relu(+bn)" if fused else "none (one kernel per reference call)",
+                       "fusion": "bn+relu, join+relu, softmax+ce+grad" if fused else "none (one kernel per reference call)",
                        "cuda_graph": use_graph, "bucket_elems": 4194304, "threshold_elems": 2097152,
                        "l2": "inputs larger than L2: %.1f GB touched per step vs 126 MB" % (total_alg / 1e9),
                        "excluded": "cuDNN/cuBLAS contractions (conv, linear): stand-in gradients",
@@ -439,8 +439,8 @@ def kernel_launches(path):
     per = {"sgb_relu_backward_f32": 1, "sgb_add_relu_backward_f32": 1, "sgb_binary_f32": 1,
            "sgb_bn_backward_f32": 2, "sgb_bn_relu_backward_f32": 2, "sgb_bn_add_relu_backward_f32": 1, "sgb_maxpool_backward_f32": 1,
            "sgb_avgpool_backward_f32": 1, "sgb_softmax_rows_f32": 1, "sgb_cross_entropy_f32": 1,
-           "sgb_sum_all_f32": 2, "sgb_softmax_cross_entropy_bwd_f32": 1,
-           "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1}
+           "sgb_sum_all_f32": 1, "sgb_softmax_cross_entropy_bwd_f32": 1,
+           "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_softmax_cross_entropy_fused_f32": 1, "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1}
     n = 0
     for name, args in path.calls:
         n += per.get(name, 0)

@@ -250,6 +250,17 @@ int sgb_softmax_cross_entropy_grad_f32(int int_target, size_t batch, size_t dim,
                                        const float *p, const int32_t *t,
                                        float scale, float *grad, void *stream);
 
+/* The loss head of python/singa/autograd.py:1306-1322 (SoftMax, CrossEntropyFwd,
+ * SoftmaxCrossEntropyBwd, "dx /= N") for integer targets in ONE launch:
+ *   prob = softmax(logits) (optional, may be NULL), loss[i] = -log(max(prob[i,
+ *   t[i]], FLT_MIN)), grad = (prob - onehot(t)) * scale.
+ * Bit-identical to sgb_softmax_rows_f32 + sgb_cross_entropy_f32 +
+ * sgb_softmax_cross_entropy_grad_f32. */
+int sgb_softmax_cross_entropy_fused_f32(const float *logits, const int32_t *t,
+                                        size_t batch, size_t dim, float scale,
+                                        float *prob, float *loss, float *grad,
+                                        void *stream);
+
 /* fp16 forms.  Softmax computes in fp32 and rounds once on store.  The two
  * cross-entropy kernels keep the half-precision arithmetic of the overloads
  * they replace (math_kernel.cu:500-537, 588-611): probabilities floored at

@@ -47,6 +47,10 @@ class OraclePath(object):
                 t[a["dx"]][...] = cpu.avgpool_backward(t[a["dy"]], t[a["dx"]].shape, a["kernel"], a["stride"], a["pad"])
             elif k == "softmax":
                 t[a["y"]][...] = cpu.softmax(t[a["x"]])
+            elif k == "softmax_ce":
+                t[a["y"]][...] = cpu.softmax(t[a["x"]])
+                t[a["loss"]][...] = cpu.cross_entropy_fwd(t[a["y"]], t[a["t"]])
+                t[a["grad"]][...] = cpu.softmax_cross_entropy_bwd(t[a["y"]], t[a["t"]]) * np.float32(a["scale"])
             elif k == "ce_fwd":
                 t[a["loss"]][...] = cpu.cross_entropy_fwd(t[a["p"]], t[a["t"]])
             elif k == "sum_all":

@@ -250,6 +250,12 @@ int sgb_sum_all_f32(const float* x, float* out, size_t n, void* ws, size_t ws_by
   if (!ws || ws_bytes < parts * sizeof(float)) return SGB_ERR_WORKSPACE;
   cudaStream_t s = as_stream(stream);
   float* partial = static_cast<float*>(ws);
+  if (parts == 1) {
+    // one CTA covers everything: its block sum IS the result (adding the zeros
+    // of a second pass would not change a bit), so write it straight to `out`
+    sumall_partial_kernel<<<1, kBlock, 0, s>>>(x, out, n);
+    return launch_status();
+  }
   sumall_partial_kernel<<<parts, kBlock, 0, s>>>(x, partial, n);
   sumall_finish_kernel<<<1, kBlock, 0, s>>>(partial, out, parts);
   return launch_status();

@@ -84,6 +84,41 @@ ce_bwd_kernel(int int_target, size_t dim, const float* __restrict__ p,
   }
 }
 
+// The whole loss head for integer targets in one launch, one CTA per sample:
+// row softmax, the sample's loss -log(max(p[t], FLT_MIN)) and the scaled
+// gradient (p - onehot) * scale.  Every value is formed by the same fp32
+// operations as in the three separate kernels above, so results are identical
+// bit for bit.
+__global__ void __launch_bounds__(kBlock)
+softmax_ce_fused_kernel(const float* __restrict__ x, const int* __restrict__ t,
+                        float* __restrict__ prob, float* __restrict__ loss,
+                        float* __restrict__ grad, size_t ncol, float scale) {
+  __shared__ float sm[32];
+  const size_t row = blockIdx.x;
+  const float* xr = x + row * ncol;
+  float m = xr[0];
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) m = fmaxf(m, xr[c]);
+  m = warp_max(m);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) sm[w] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
+  float s = 0.f;
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) s += expf(xr[c] - m);
+  s = block_sum(s, sm);
+  const size_t hot = static_cast<size_t>(t[row]);
+  for (size_t c = threadIdx.x; c < ncol; c += kBlock) {
+    const float p = expf(xr[c] - m) / s;
+    if (prob) prob[row * ncol + c] = p;
+    float g = p;
+    if (c == hot) {
+      g = g - 1.0f;
+      loss[row] = -logf(fmaxf(p, FLT_MIN));
+    }
+    grad[row * ncol + c] = g * scale;
+  }
+}
+
 // ------------------------------------------------------------------- fp16
 // Row softmax on fp16 data: fp32 arithmetic inside, one rounding on store.
 __global__ void __launch_bounds__(kBlock)
@@ -198,6 +233,17 @@ int sgb_softmax_cross_entropy_grad_f32(int int_target, size_t batch, size_t dim,
   if (batch > 0x7fffffffu) return SGB_ERR_SIZE;
   ce_bwd_kernel<true><<<static_cast<unsigned>(batch), kBlock, 0, as_stream(stream)>>>(
       int_target, dim, p, t, grad, scale);
+  return launch_status();
+}
+
+int sgb_softmax_cross_entropy_fused_f32(const float* logits, const int32_t* t, size_t batch, size_t dim,
+                                        float scale, float* prob, float* loss, float* grad,
+                                        void* stream) {
+  if (batch == 0 || dim == 0) return SGB_OK;
+  if (!logits || !t || !loss || !grad) return SGB_ERR_NULL;
+  if (batch > 0x7fffffffu) return SGB_ERR_SIZE;
+  softmax_ce_fused_kernel<<<static_cast<unsigned>(batch), kBlock, 0, as_stream(stream)>>>(
+      logits, t, prob, loss, grad, dim, scale);
   return launch_status();
 }
 

@@ -175,6 +175,11 @@ class HotPathGPU(object):
             elif k == "softmax":
                 r, c = t[a["x"]].shape
                 self.calls.append(("sgb_softmax_rows_f32", (p(a["x"]), p(a["y"]), r, c, S)))
+            elif k == "softmax_ce":
+                r, c = t[a["x"]].shape
+                self.calls.append(("sgb_softmax_cross_entropy_fused_f32",
+                                   (p(a["x"]), p(a["t"]), r, c, float(np.float32(a["scale"])), p(a["y"]),
+                                    p(a["loss"]), p(a["grad"]), S)))
             elif k == "ce_fwd":
                 r, c = t[a["p"]].shape
                 self.calls.append(("sgb_cross_entropy_f32", (1, r, c, p(a["p"]), p(a["t"]), p(a["loss"]), S)))

@@ -121,12 +121,15 @@ def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4,
         return tensor(name, shape, "grad")
 
     # head: loss forward, softmax-CE backward (+1/N), bias gradient, avg-pool backward
-    ops.append(Op("softmax", dict(x="logits", y="prob")))
-    ops.append(Op("ce_fwd", dict(p="prob", t="labels", loss="loss_vec")))
-    ops.append(Op("sum_all", dict(x="loss_vec", out="loss")))
     if fused:
-        ops.append(Op("ce_grad", dict(p="prob", t="labels", scale=1.0 / B, grad="dlogits")))
+        ops.append(Op("softmax_ce", dict(x="logits", t="labels", y="prob", loss="loss_vec", grad="dlogits",
+                                         scale=1.0 / B)))
+        ops.append(Op("sum_all", dict(x="loss_vec", out="loss")))
     else:
+        ops.append(Op("softmax", dict(x="logits", y="prob")))
+        ops.append(Op("ce_fwd", dict(p="prob", t="labels", loss="loss_vec")))
+        ops.append(Op("sum_all", dict(x="loss_vec", out="loss")))
+    if not fused:
         ops.append(Op("ce_bwd", dict(p="prob", t="labels", grad="dlogits")))
         ops.append(Op("scale", dict(x="dlogits", c=1.0 / B)))
     ops.append(Op("sum_rows", dict(M="dlogits", v="d:fc.b")))
@@ -228,7 +231,7 @@ READS = {
     "bn_add_relu_bwd": ("dy_a", "dy_b", "relu_x", "x", "scale", "mean", "invstd"),
     "maxpool_bwd": ("x", "y", "dy"), "avgpool_bwd": ("dy",), "softmax": ("x",), "ce_fwd": ("p", "t"),
     "sum_all": ("x",), "ce_bwd": ("p", "t"), "ce_grad": ("p", "t"), "scale": ("x",), "sum_rows": ("M",),
-    "conv_bias_bwd": ("dy",),
+    "conv_bias_bwd": ("dy",), "softmax_ce": ("x", "t"),
 }
 
 
@@ -241,6 +244,8 @@ def fuse_plan(plan, join_bn=False):
       add_relu_bwd(a, b, x=r -> t) ; bn_bwd(dy=t, ...)   =>  bn_add_relu_bwd(a, b, relu_x=r, joined=t, ...)
                                                              (only with join_bn=True)
       ce_bwd(p, t -> g) ; scale(g, c)                    =>  ce_grad(p, t, c -> g)
+      softmax(x -> p) ; ce_fwd(p, t -> l) ; ... ; ce_grad(p, t, c -> g)
+                                                         =>  softmax_ce(x, t, c -> p, l, g)   (at softmax's place)
 
     A pair is fused only when the intermediate tensor has no other reader;
     the intermediate then disappears from the plan.  The last rule is the
@@ -294,7 +299,34 @@ def fuse_plan(plan, join_bn=False):
                 producer[op.args[key]] = i
     # a fused relu_bwd may itself have consumed an add_out: drop everything marked dead
     fused_ops = [op for i, op in enumerate(out) if i not in dead]
+    fused_ops = _fuse_loss_head(fused_ops)
     return dict(plan, ops=fused_ops, tensors=T)
+
+
+def _fuse_loss_head(ops):
+    """softmax ; ce_fwd ; (ops that touch neither p nor the gradient) ; ce_grad on
+    the same probabilities and integer targets -> one softmax_ce op where the
+    softmax stood.  The probabilities stay an output (later readers keep working)."""
+    ops = list(ops)
+    for i, op in enumerate(ops):
+        if op.kind != "softmax":
+            continue
+        pname = op.args["y"]
+        fwd = next((j for j in range(i + 1, len(ops)) if ops[j].kind == "ce_fwd" and ops[j].args["p"] == pname), None)
+        grd = next((j for j in range(i + 1, len(ops)) if ops[j].kind == "ce_grad" and ops[j].args["p"] == pname), None)
+        if fwd is None or grd is None or fwd > grd or ops[fwd].args["t"] != ops[grd].args["t"]:
+            continue
+        gname, lname = ops[grd].args["grad"], ops[fwd].args["loss"]
+        between = [ops[j] for j in range(i + 1, grd) if j != fwd]
+        touched = set()
+        for o in between:
+            touched.update(v for v in o.args.values() if isinstance(v, str))
+        if gname in touched or pname in touched:
+            continue
+        fused = Op("softmax_ce", dict(x=op.args["x"], t=ops[fwd].args["t"], y=pname, loss=lname, grad=gname,
+                                      scale=ops[grd].args["scale"]))
+        return ops[:i] + [fused] + [o for j, o in enumerate(ops[i + 1:], i + 1) if j not in (fwd, grd)]
+    return ops
 
 
 def numel(shape):
@@ -340,6 +372,8 @@ def algorithmic_bytes(plan, world=1):
             add("softmax_ce", 8 * numel(T[a["p"]].shape))
         elif op.kind == "softmax":
             add("softmax_ce", 8 * numel(T[a["x"]].shape))
+        elif op.kind == "softmax_ce":
+            add("softmax_ce", 12 * numel(T[a["x"]].shape))       # read logits, write prob and grad
         elif op.kind == "scale":
             add("softmax_ce", 8 * numel(T[a["x"]].shape))
         elif op.kind == "sum_rows":

@@ -10,6 +10,7 @@ path: a CPU tensor raises ``ValueError``.
 
 Tensors must be contiguous, as ``singa::Tensor`` blocks are on this path.
 """
+import numpy as np
 import torch
 
 from . import _lib
@@ -365,6 +366,20 @@ def SoftmaxCrossEntropyGrad(p, t, scale):
 
 
 # ------------------------------------------------------------ operation handles
+def SoftMaxCrossEntropyFused(logits, t, scale):
+    """The loss head of autograd.SoftMaxCrossEntropy (python/singa/autograd.py:
+    1306-1322) for integer targets in one launch.  Returns (prob, loss per
+    sample, grad) with grad = (prob - onehot) * scale."""
+    _chk(logits, t)
+    assert t.dtype == _I32 and t.numel() == logits.shape[0], "one int32 target per sample"
+    batch, dim = logits.shape
+    prob, grad = torch.empty_like(logits), torch.empty_like(logits)
+    loss = torch.empty(batch, dtype=_F32, device=logits.device)
+    _lib.call("sgb_softmax_cross_entropy_fused_f32", _p(logits), _p(t), batch, dim, float(np.float32(scale)),
+              _p(prob), _p(loss), _p(grad), _stream())
+    return prob, loss, grad
+
+
 class CudnnBatchNormHandle(object):
     """Shape record with the fields of singa's BatchNormHandle
     (src/model/operation/batchnorm.h:38-60); no cuDNN descriptors are needed."""

@@ -98,6 +98,19 @@ def test_softmax_cross_entropy_random(sw, oracle, shape):
           what="loss sum")
 
 
+@pytest.mark.parametrize("shape", [(256, 10), (64, 10), (32, 1000), (1, 7), (5, 4099)])
+def test_fused_loss_head_equals_the_three_kernels(sw, shape):
+    rng = np.random.default_rng(shape[1] + 1)
+    logits = dev((rng.standard_normal(shape) * 3).astype(np.float32))
+    t = dev(rng.integers(0, shape[1], shape[0]).astype(np.int32))
+    inv = float(np.float32(1.0) / np.float32(shape[0]))
+    p = sw.SoftMax(logits)
+    loss = sw.CrossEntropyFwd(p, t)
+    grad = sw.SoftmaxCrossEntropyGrad(p, t, inv)
+    fp, fl, fg = sw.SoftMaxCrossEntropyFused(logits, t, inv)
+    assert torch.equal(fp, p) and torch.equal(fl, loss) and torch.equal(fg, grad)
+
+
 # ------------------------------------------------------------------ batch norm
 def bn_case(rng, shape):
     x = (rng.standard_normal(shape) * 1.7 + 0.3).astype(np.float32)
