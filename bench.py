@@ -27,7 +27,7 @@ METRIC = "resnet50_backward_sync_update_images_per_sec"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the batch-norm
 # backward kernels, averaged per call over one step, from the ncu capture
 # summarised in profiles/bench_resnet50_launch_list.md (fused / call-pattern plan).
-NCU_BN_TRAFFIC_PER_CALL = {True: 77.7e6, False: 65.7e6}
+NCU_BN_TRAFFIC_PER_CALL = {True: 77.8e6, False: 65.5e6}
 BATCH = 32
 CPU_SAMPLE_BATCH = 8
 
@@ -435,15 +435,23 @@ def main():
 
 
 def kernel_launches(path):
-    """Kernels of this library launched per step (NCCL's own are not counted)."""
+    """Kernels of this library launched per step (NCCL's own are not counted).
+    Batch-norm backward is one launch, except when a channel (x and dy of all
+    samples) exceeds what a cluster of eight CTAs can stage (8 x 100 KB): then
+    it is the reduce + apply pair."""
     per = {"sgb_relu_backward_f32": 1, "sgb_add_relu_backward_f32": 1, "sgb_binary_f32": 1,
-           "sgb_bn_backward_f32": 2, "sgb_bn_relu_backward_f32": 2, "sgb_bn_add_relu_backward_f32": 1, "sgb_maxpool_backward_f32": 1,
+           "sgb_maxpool_backward_f32": 1,
            "sgb_avgpool_backward_f32": 1, "sgb_softmax_rows_f32": 1, "sgb_cross_entropy_f32": 1,
            "sgb_sum_all_f32": 1, "sgb_softmax_cross_entropy_bwd_f32": 1,
-           "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_softmax_cross_entropy_fused_f32": 1, "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1}
+           "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_softmax_cross_entropy_fused_f32": 1,
+           "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1}
     n = 0
     for name, args in path.calls:
-        n += per.get(name, 0)
+        if name in ("sgb_bn_backward_f32", "sgb_bn_relu_backward_f32", "sgb_bn_add_relu_backward_f32"):
+            N, _, HW = args[-6:-3]          # (..., N, C, HW, workspace, workspace bytes, stream)
+            n += 2 if N * HW * 8 > 8 * 100 * 1024 else 1
+        else:
+            n += per.get(name, 0)
     if path.comm is not None:
         for kind, idx in path.events:
             if kind == "fused" and path.dist_option == "half":
