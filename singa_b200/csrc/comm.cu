@@ -406,17 +406,26 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   const int W = c->world;
   OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
   c->dirty_c1 = true;
-  OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
+  // One tensor, or tensors that lie back to back in memory (a gradient arena),
+  // are selected from and scattered into IN PLACE: no copy into the send
+  // buffer and none back (16 B/element saved).  The selection has finished
+  // reading the gradient before the dense result is written: c1 -> s -> c2.
+  bool in_place = sgb::aligned16(tensors[0]);
+  for (size_t i = 1; i < count && in_place; ++i)
+    in_place = static_cast<const float*>(tensors[i]) == static_cast<const float*>(tensors[i - 1]) + sizes[i - 1];
+  float* grad = in_place ? static_cast<float*>(tensors[0]) : c->send;
+  float* dense = in_place ? static_cast<float*>(tensors[0]) : c->recv;
+  if (!in_place) OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
 
   size_t nnz_max = 0;
   if (!topk) {
-    OK(sgb::sparse_threshold_count(c->send, accumulation, n, spars, c->nnz_dev, c->ws,
+    OK(sgb::sparse_threshold_count(grad, accumulation, n, spars, c->nnz_dev, c->ws,
                                    c->ws_bytes, c->c1));
     NC(ncclAllGather(c->nnz_dev, c->nnz_dev + 1, 1, ncclInt, c->nccl, c->c1));
     CU(cudaMemcpyAsync(c->nnz_host, c->nnz_dev + 1, sizeof(int) * W, cudaMemcpyDeviceToHost, c->c1));
     CU(cudaEventRecord(c->ev_host, c->c1));
     // the compaction runs while the host waits for the counts
-    OK(sgb::sparse_threshold_write_packed(c->send, accumulation, n, spars, c->pay_send, c->ws, c->c1));
+    OK(sgb::sparse_threshold_write_packed(grad, accumulation, n, spars, c->pay_send, c->ws, c->c1));
     CU(cudaEventSynchronize(c->ev_host));
     for (int r = 0; r < W; ++r) {
       if (c->nnz_host[r] < 0 || static_cast<size_t>(c->nnz_host[r]) > n) return SGB_ERR_STATE;
@@ -426,7 +435,7 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
     nnz_max = static_cast<size_t>(sgb_topk_count(spars, n));
     for (int r = 0; r < W; ++r) c->nnz_host[r] = static_cast<int>(nnz_max);
     if (nnz_max)
-      OK(sgb_sparse_topk_f32(c->send, accumulation, c->sum, n, nnz_max, c->topk_mode, c->pay_send,
+      OK(sgb_sparse_topk_f32(grad, accumulation, c->sum, n, nnz_max, c->topk_mode, c->pay_send,
                              reinterpret_cast<float*>(c->pay_send) + nnz_max, c->ws, c->ws_bytes,
                              c->c1));
   }
@@ -435,14 +444,14 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   if (nnz_max)
     NC(ncclAllGather(c->pay_send, c->pay_recv, 2 * nnz_max, ncclFloat, c->nccl, c->s));
   OK(after_collective(c, true));
-  CU(cudaMemsetAsync(c->recv, 0, n * sizeof(float), c->c2));
+  CU(cudaMemsetAsync(dense, 0, n * sizeof(float), c->c2));
   for (int r = 0; r < W && nnz_max; ++r) {  // ranks in ascending order, as the reference
     const int* seg = c->pay_recv + static_cast<size_t>(r) * 2 * nnz_max;
     const size_t cnt = static_cast<size_t>(c->nnz_host[r]);
-    OK(sgb_scatter_add_f32(seg, reinterpret_cast<const float*>(seg) + cnt, cnt, nullptr, c->recv,
+    OK(sgb_scatter_add_f32(seg, reinterpret_cast<const float*>(seg) + cnt, cnt, nullptr, dense,
                            n, c->c2));
   }
-  OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c2));
+  if (!in_place) OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c2));
   return SGB_OK;
 }
 
