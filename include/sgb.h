@@ -428,7 +428,8 @@ int sgb_sparse_threshold_f32(const float *g, float *acc, size_t n, float thr,
  * sortbykey (thrust::sort_by_key of all n pairs) + the cusparseSaxpyi
  * residual update of Communicator::topKSparsAllReduce (communicator.cc:
  * 721-765; math_kernel.h:184,190) by a 3-pass radix select.  s = g + acc is
- * materialised in sum_scratch (n floats).  The k entries with the largest key
+ * formed once and kept in acc itself (sum_scratch is unused and may be NULL;
+ * the argument remains for ABI stability).  The k entries with the largest key
  * are written in ascending index order, ties broken by lower index;
  * acc = s with the selected entries zeroed.
  * mode 0: key = |s|.  mode 1: key = |(int)s|, which is what the reference's

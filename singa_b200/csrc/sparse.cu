@@ -134,8 +134,11 @@ __device__ __forceinline__ unsigned tile_exclusive(const unsigned (&c)[kVecPerTh
 
 // ------------------------------------------------------------ threshold mode
 // kept value of element i: s = g (+ acc); |s| >= thr ? s : 0; sent iff != 0.
+// With a residual buffer the count pass leaves s = g + acc IN acc, so that the
+// write pass reads 4 bytes per element instead of 8 and only has to zero the
+// entries it sends (the residual of every other element is s itself).
 __global__ void __launch_bounds__(kBlock)
-thr_count_kernel(const float* __restrict__ g, const float* __restrict__ acc, size_t n,
+thr_count_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n,
                  float thr, unsigned* __restrict__ tile_counts, bool vec) {
   __shared__ unsigned sm[32];
   const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
@@ -145,6 +148,7 @@ thr_count_kernel(const float* __restrict__ g, const float* __restrict__ acc, siz
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
     float s[4];
     load_sum4(g, acc, i, n, vec, s);      // out-of-range lanes are 0 and never counted
+    if (acc) store4(acc, i, n, vec, s);
 #pragma unroll
     for (int j = 0; j < 4; ++j) cnt += (fabsf(s[j]) >= thr && s[j] != 0.0f) ? 1u : 0u;
   }
@@ -243,8 +247,9 @@ scan_tiles_kernel(unsigned* __restrict__ a, unsigned* __restrict__ b, size_t til
   }
 }
 
+// `sum` is acc after the count pass (or g when there is no residual buffer).
 __global__ void __launch_bounds__(kBlock)
-thr_write_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n, float thr,
+thr_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t n, float thr,
                  const unsigned* __restrict__ tile_offsets, int* __restrict__ idx_out,
                  float* __restrict__ val_out, const SelectState* __restrict__ st, bool vec) {
   __shared__ unsigned sm[33];
@@ -258,7 +263,7 @@ thr_write_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n,
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
     c[r] = 0;
     float s[4], res[4];
-    load_sum4(g, acc, i, n, vec, s);
+    load_sum4(sum, nullptr, i, n, vec, s);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float k = fabsf(s[j]) >= thr ? s[j] : 0.0f;   // out-of-range lanes: s == 0 -> k == 0
@@ -266,7 +271,7 @@ thr_write_kernel(const float* __restrict__ g, float* __restrict__ acc, size_t n,
       kept[r][j] = k;
       c[r] += k != 0.0f ? 1u : 0u;
     }
-    if (acc) store4(acc, i, n, vec, res);
+    if (acc && c[r]) store4(acc, i, n, vec, res);         // untouched vectors already hold their residual
   }
   tile_exclusive(c, excl, sm);
   const unsigned tile_off = tile_offsets[blockIdx.x];
@@ -317,7 +322,7 @@ topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
       float s[4];
       if (PASS == 0) {
         load_sum4(g, acc, i, n, vec, s);
-        store4(sum, i, n, vec, s);
+        if (acc) store4(sum, i, n, vec, s);         // sum == acc: the residual buffer now holds g + acc
       } else {
         load_sum4(sum, nullptr, i, n, vec, s);
       }
@@ -496,6 +501,7 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
     const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
     unsigned ng = g0 + eg[r], ne = e0 + ee[r];
     float res[4];
+    bool any = false;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       bool sel = false;
@@ -510,10 +516,11 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
         val_out[pos] = s[r][j];
       }
       res[j] = sel ? 0.0f : s[r][j];  // s - s == 0 when sent
+      any = any || sel;
       if (flag[r][j] == 1) ++ng;
       if (flag[r][j] == 2) ++ne;
     }
-    if (acc) store4(acc, i, n, vec, res);
+    if (acc && any) store4(acc, i, n, vec, res);     // acc already holds s everywhere else
   }
 }
 
@@ -545,7 +552,7 @@ int check_common(const float* g, size_t n, const void* idx_out, const void* val_
 }  // namespace
 
 // ---- two-phase form used by the communicator (declared in sparse.cuh) ------
-int sparse_threshold_count(const float* g, const float* acc, size_t n, float thr, int* nnz_dev,
+int sparse_threshold_count(const float* g, float* acc, size_t n, float thr, int* nnz_dev,
                            void* ws, size_t ws_bytes, cudaStream_t s) {
   if (n == 0) {
     cudaError_t e = cudaMemsetAsync(nnz_dev, 0, sizeof(int), s);
@@ -568,7 +575,7 @@ int sparse_threshold_write_packed(const float* g, float* acc, size_t n, float th
   if (n == 0) return SGB_OK;
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
-  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, payload, nullptr, w.state, aligned16(g) && (!acc || aligned16(acc)));
+  thr_write_kernel<<<tiles, kBlock, 0, s>>>(acc ? acc : g, acc, n, thr, w.tile_counts, payload, nullptr, w.state, aligned16(g) && (!acc || aligned16(acc)));
   return launch_status();
 }
 
@@ -607,7 +614,7 @@ int sgb_sparse_threshold_f32(const float* g, float* acc, size_t n, float thr, in
   scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_counts, nullptr, tiles, w.state, 1);
   cudaError_t e = cudaMemcpyAsync(nnz_dev, &w.state->nnz, sizeof(int), cudaMemcpyDeviceToDevice, s);
   if (e != cudaSuccess) return note_cuda_error(e);
-  thr_write_kernel<<<tiles, kBlock, 0, s>>>(g, acc, n, thr, w.tile_counts, idx_out, val_out, w.state, aligned16(g) && (!acc || aligned16(acc)));
+  thr_write_kernel<<<tiles, kBlock, 0, s>>>(acc ? acc : g, acc, n, thr, w.tile_counts, idx_out, val_out, w.state, aligned16(g) && (!acc || aligned16(acc)));
   return launch_status();
 }
 
@@ -616,7 +623,7 @@ int sgb_sparse_topk_f32(const float* g, float* acc, float* sum_scratch, size_t n
                         void* stream) {
   if (n == 0 || k == 0) return SGB_OK;
   if (mode != 0 && mode != 1) return SGB_ERR_UNSUPPORTED;
-  if (!sum_scratch) return SGB_ERR_NULL;
+  (void)sum_scratch;   // kept in the signature; the sum lives in acc (or is g itself without a residual)
   int st = check_common(g, n, idx_out, val_out, ws, ws_bytes);
   if (st != SGB_OK) return st;
   if (k > n) k = n;
@@ -624,18 +631,19 @@ int sgb_sparse_topk_f32(const float* g, float* acc, float* sum_scratch, size_t n
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
   const unsigned hgrid = capped_grid(tiles, 1, 8);
-  const bool vec = aligned16(g) && (!acc || aligned16(acc)) && aligned16(sum_scratch);
+  const bool vec = aligned16(g) && (!acc || aligned16(acc));
+  float* sum = acc ? acc : const_cast<float*>(g);
   cudaError_t e = cudaMemsetAsync(w.hist, 0, kBins1 * sizeof(unsigned), s);
   if (e != cudaSuccess) return note_cuda_error(e);
-  topk_hist_kernel<0><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist, vec);
+  topk_hist_kernel<0><<<hgrid, kBlock, 0, s>>>(g, acc, sum, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<0><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
-  topk_hist_kernel<1><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist, vec);
+  topk_hist_kernel<1><<<hgrid, kBlock, 0, s>>>(g, acc, sum, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<1><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
-  topk_hist_kernel<2><<<hgrid, kBlock, 0, s>>>(g, acc, sum_scratch, n, mode, w.state, w.hist, vec);
+  topk_hist_kernel<2><<<hgrid, kBlock, 0, s>>>(g, acc, sum, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<2><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));
-  topk_count_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, n, mode, w.state, w.tile_gt, w.tile_eq, vec);
+  topk_count_kernel<<<tiles, kBlock, 0, s>>>(sum, n, mode, w.state, w.tile_gt, w.tile_eq, vec);
   scan_tiles_kernel<<<1, 1024, 0, s>>>(w.tile_gt, w.tile_eq, tiles, w.state, 0);
-  topk_write_kernel<<<tiles, kBlock, 0, s>>>(sum_scratch, acc, n, mode, w.state, w.tile_gt,
+  topk_write_kernel<<<tiles, kBlock, 0, s>>>(sum, acc, n, mode, w.state, w.tile_gt,
                                              w.tile_eq, idx_out, val_out, vec);
   return launch_status();
 }

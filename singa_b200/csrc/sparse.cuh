@@ -7,7 +7,7 @@
 namespace sgb {
 
 // Phase 1: per-tile counts + scan; the payload length lands in *nnz_dev.
-int sparse_threshold_count(const float* g, const float* acc, size_t n, float thr, int* nnz_dev,
+int sparse_threshold_count(const float* g, float* acc, size_t n, float thr, int* nnz_dev,
                            void* ws, size_t ws_bytes, cudaStream_t s);
 
 // Phase 2: residual update and packed payload [idx(nnz) | val(nnz)] written to
