@@ -156,6 +156,55 @@ class DistOpt(object):
         self._update_all(self._sync_dense(clipped(grad_stream), threshold, self.all_reduce_half,
                                           self.fused_all_reduce_half))
 
+    def _divide_by_world(self, t):
+        sw.DivFloatWithRet(t, self.world_size, t)
+
+    def backward_and_partial_update(self, grad_stream, threshold=2097152):
+        """opt.py:922-992 (asynchronous variant): every parameter is updated with
+        its LOCAL gradient first; then ONE partition of the PARAMETERS - the
+        ``self.partial``-th bucket in production order, cycling - is all-reduced
+        and averaged.  A partition is a tensor above ``threshold`` or a bucket of
+        smaller ones, exactly as in ``backward_and_update``."""
+        self.partial = getattr(self, "partial", 0) + 1
+        names, params, grads = [], [], []
+        k, acc, bucket, reduced = 0, 0, [], []
+        picked = []                                   # (kind, tensors) of the partition to exchange
+        for name, p, g in grad_stream:
+            names.append(name)
+            params.append(p)
+            grads.append(g)
+            if p.numel() > threshold:
+                k += 1
+                if k == self.partial:
+                    picked.append(("direct", [p]))
+            else:
+                bucket.append(p)
+                acc += p.numel()
+                if acc > threshold:
+                    k += 1
+                    if k == self.partial:
+                        picked.append(("fused", bucket))
+                    acc, bucket = 0, []
+        if bucket:
+            k += 1
+            if k == self.partial:
+                picked.append(("fused", bucket))
+        # local update of everything (grad_scale 1: no averaging of gradients in this mode)
+        self.opt.apply_many(names, params, grads, 1.0)
+        for kind, tensors in picked:
+            if kind == "direct":
+                self.all_reduce(tensors[0])
+            else:
+                self.fused_all_reduce(tensors, send=False)
+                self.fused_all_reduce(tensors)
+            reduced = tensors
+        self.wait()
+        for r in reduced:
+            self._divide_by_world(r)                   # "r /= world_size" on the exchanged parameters
+        if k == self.partial:
+            self.partial = 0
+        self.opt.step()
+
     def backward_and_sparse_update(self, grad_stream, threshold=2097152, spars=0.05, topK=False,
                                    corr=True):
         """opt.py:994-1094: sparsified synchronisation with local residuals."""

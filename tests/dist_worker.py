@@ -113,6 +113,33 @@ def main():
             assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), accs[rank].view(np.uint32)), \
                 ("residual", topk, mode, step)
 
+    # (g) DistOpt.backward_and_partial_update through the real communicator:
+    # local SGD-momentum updates, then one partition of the parameters averaged
+    from oracle import cpu as ocpu
+    psizes = [1000, 2048000, 2048, 2048, 1048576, 2359296, 512, 64, 2400000, 9408]
+    plan = ocomm.plan_buckets(psizes)
+
+    def pgrads(r, step):
+        rng = np.random.default_rng(7000 + 10 * step + r)
+        return [(rng.standard_normal(k) * 1e-2).astype(np.float32) for k in psizes]
+    dopt = opt.DistOpt(opt.SGD(lr=0.1, momentum=0.9), communicator=comm)
+    params = [torch.zeros(k, device="cuda") for k in psizes]
+    want = [[np.zeros(k, np.float32) for k in psizes] for _ in range(world)]
+    mom = [[np.zeros(k, np.float32) for k in psizes] for _ in range(world)]
+    for step in range(len(plan) + 1):
+        mine = [dev(a) for a in pgrads(rank, step)]
+        dopt.backward_and_partial_update((("q%d" % i, p_, g_) for i, (p_, g_) in enumerate(zip(params, mine))))
+        for r in range(world):
+            for i, g_ in enumerate(pgrads(r, step)):
+                ocpu.sgd_update(want[r][i], g_.copy(), mom[r][i], 0.1, momentum=0.9)
+        for i in plan[step % len(plan)][1]:
+            avg = ocomm.divide_by_world(ocomm.allreduce_sum([want[r][i] for r in range(world)]), world)
+            for r in range(world):
+                want[r][i][...] = avg
+    torch.cuda.synchronize()
+    for i, p_ in enumerate(params):
+        close(p_.cpu().numpy(), want[rank][i], 1e-5, "partial update, parameter %d" % i)
+
     # (f) host-side failure injection: a bucket that overflows is refused, not written
     big = torch.zeros(4194304, device="cuda")
     comm.fusedSynch([big], False)

@@ -92,6 +92,56 @@ def worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def partial_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    from singa_b200.opt import DistOpt, plan_buckets
+
+    class HostDistOpt(DistOpt):
+        def _divide_by_world(self, t):                 # the product scales on the GPU; same fp32 product here
+            t.mul_(float(np.float32(1.0) / np.float32(self.world_size)))
+
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    comm = GlooCommunicator(rank, world, 4194304)
+    opt = HostDistOpt(OracleSGD(0.1, 0.9), communicator=comm)
+    params = [torch.zeros(n) for n in SIZES]
+    nparts = len(plan_buckets(SIZES))
+    for step in range(nparts + 2):                     # one full cycle of partitions and a bit more
+        grads = [torch.from_numpy(g) for g in grads_of(rank, step)]
+        opt.backward_and_partial_update((("p%d" % i, p, g) for i, (p, g) in enumerate(zip(params, grads))))
+        assert opt.partial == (step + 1) % nparts
+    exchanges = sum(1 for k, _ in comm.log if k in ("flush", "synch"))
+    assert exchanges == nparts + 2                     # exactly one partition per step
+    out[rank] = [p.numpy().copy() for p in params]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_partial_update_two_ranks_over_gloo():
+    """backward_and_partial_update: local updates everywhere, then one partition
+    of the PARAMETERS (cycling through the bucket plan) is summed over the ranks
+    and divided by the world size."""
+    from oracle import comm as ocomm, cpu
+    world = 2
+    manager = mp.Manager()
+    out = manager.dict()
+    mp.spawn(partial_worker, args=(world, free_port(), out), nprocs=world, join=True)
+    plan = ocomm.plan_buckets(SIZES)
+    params = [[np.zeros(n, np.float32) for n in SIZES] for _ in range(world)]
+    moments = [[np.zeros(n, np.float32) for n in SIZES] for _ in range(world)]
+    for step in range(len(plan) + 2):
+        for r in range(world):
+            for i, g in enumerate(grads_of(r, step)):
+                cpu.sgd_update(params[r][i], g.copy(), moments[r][i], 0.1, momentum=0.9)
+        _, members = plan[step % len(plan)]
+        for i in members:
+            avg = ocomm.divide_by_world(params[0][i] + params[1][i], world)
+            for r in range(world):
+                params[r][i][...] = avg
+    for r in range(world):
+        for got, want in zip(out[r], params[r]):
+            assert np.array_equal(got, want)
+
+
 def free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
