@@ -26,7 +26,9 @@ struct SelectState {
   unsigned threshold;    // final key T
   unsigned quota;        // number of key == T elements to take (lowest indices)
   int nnz;               // payload length (threshold mode: count; top-K: K)
-  int pad[3];
+  unsigned max_key;      // largest key seen by pass 0 (zeroed with the histogram before every call)
+  unsigned skip1;        // 1: every key is below 2^10, pass 1 (bits 10..19) has nothing to decide
+  int pad;
 };
 
 // Workspace layout (all 256-byte aligned segments).
@@ -310,8 +312,10 @@ topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
   constexpr int kBins = PASS == 0 ? kBins1 : kBins23;
   constexpr int kShift = PASS == 0 ? 20 : (PASS == 1 ? 10 : 0);
   __shared__ unsigned sh[kBins];
+  if (PASS == 1 && st->skip1) return;               // uniform for the whole grid
   for (int b = threadIdx.x; b < kBins; b += kBlock) sh[b] = 0;
   __syncthreads();
+  unsigned top = 0;                                  // PASS 0: largest key of this thread
   const unsigned prefix = PASS == 0 ? 0u : st->prefix;
   const unsigned hi_mask = PASS == 0 ? 0u : (PASS == 1 ? 0xfff00000u : 0xfffffc00u);
   for (size_t tile = blockIdx.x; tile * kTile < n; tile += gridDim.x) {
@@ -333,6 +337,7 @@ topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
         const unsigned key = make_key(s[j], mode);
         take[j] = i + j < n && (key & hi_mask) == prefix;
         bin[j] = (key >> kShift) & (kBins - 1);
+        if (PASS == 0 && i + j < n) top = max(top, key);
       }
       // Fast path: every lane of the warp takes all four of its elements and
       // they all fall into one bin (always true when every key ties): one
@@ -352,6 +357,10 @@ topk_hist_kernel(const float* __restrict__ g, const float* __restrict__ acc,
   __syncthreads();
   for (int b = threadIdx.x; b < kBins; b += kBlock)
     if (sh[b]) atomicAdd(&hist[b], sh[b]);
+  if (PASS == 0) {
+    top = __reduce_max_sync(0xffffffffu, top);
+    if ((threadIdx.x & 31) == 0 && top) atomicMax(const_cast<unsigned*>(&st->max_key), top);
+  }
 }
 
 // One CTA: find the bin, counted from the top, in which the cumulative count
@@ -367,6 +376,7 @@ topk_pick_kernel(unsigned* __restrict__ hist, SelectState* __restrict__ st, unsi
   constexpr int kShift = PASS == 0 ? 20 : (PASS == 1 ? 10 : 0);
   constexpr int kPer = kBins / 1024;                 // 4 or 1 bins per thread
   __shared__ unsigned warp_tot[32];
+  if (PASS == 1 && st->skip1) return;                // prefix and remaining stand; the histogram is still clear
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   // thread t owns descending bins  kBins-1 - t*kPer - j,  j = 0 .. kPer-1
   unsigned mine[kPer], local = 0;
@@ -415,6 +425,9 @@ topk_pick_kernel(unsigned* __restrict__ hist, SelectState* __restrict__ st, unsi
     const unsigned prefix = prefix0 | (static_cast<unsigned>(b) << kShift);
     st->prefix = prefix;
     st->remaining = remaining;
+    // Keys that all fit in the lowest digit (the integer-truncated keys of small
+    // gradients) leave the middle digit zero everywhere: skip that pass.
+    if (PASS == 0) st->skip1 = st->max_key < (1u << 10) ? 1u : 0u;
     if (PASS == 2) {
       st->threshold = prefix;
       st->quota = remaining;
@@ -465,6 +478,15 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
                   float* __restrict__ val_out, bool vec) {
   __shared__ unsigned sm[33];
   const unsigned T = st->threshold, quota = st->quota;
+  // A tile that holds no key above T and no key == T that is still within the
+  // quota sends nothing, and its residual (acc already holds g + acc) stays as
+  // it is: leave before reading a byte.  The counts are differences of the
+  // scanned offsets; the last tile has no successor and always runs.
+  if (blockIdx.x + 1 < gridDim.x) {
+    const unsigned g_lo = gt_off[blockIdx.x], e_lo = eq_off[blockIdx.x];
+    const unsigned n_gt = gt_off[blockIdx.x + 1] - g_lo, n_eq = eq_off[blockIdx.x + 1] - e_lo;
+    if (n_gt == 0 && (n_eq == 0 || e_lo >= quota)) return;
+  }
   const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
   float s[kVecPerThread][4];
   unsigned cg[kVecPerThread], ce[kVecPerThread], eg[kVecPerThread], ee[kVecPerThread];
@@ -633,7 +655,8 @@ int sgb_sparse_topk_f32(const float* g, float* acc, float* sum_scratch, size_t n
   const unsigned hgrid = capped_grid(tiles, 1, 8);
   const bool vec = aligned16(g) && (!acc || aligned16(acc));
   float* sum = acc ? acc : const_cast<float*>(g);
-  cudaError_t e = cudaMemsetAsync(w.hist, 0, kBins1 * sizeof(unsigned), s);
+  // histogram and the selection state behind it (one contiguous region)
+  cudaError_t e = cudaMemsetAsync(w.hist, 0, align256(kBins1 * sizeof(unsigned)) + sizeof(SelectState), s);
   if (e != cudaSuccess) return note_cuda_error(e);
   topk_hist_kernel<0><<<hgrid, kBlock, 0, s>>>(g, acc, sum, n, mode, w.state, w.hist, vec);
   topk_pick_kernel<0><<<1, 1024, 0, s>>>(w.hist, w.state, static_cast<unsigned>(k));

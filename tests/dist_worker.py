@@ -100,10 +100,19 @@ def main():
             gs = [(np.random.default_rng(20 * r + step).standard_normal(n) * scale).astype(np.float32)
                   for r in range(world)]
             g = dev(gs[rank])
-            parts = [g[:100001], g[100001:]] if step == 1 else [g]   # fused form: two tensors, one residual
+            # step 0: one tensor; step 1: two tensors back to back (exchanged in place);
+            # step 2: two tensors apart in memory (copied through the communicator's buffers)
+            if step == 1:
+                parts = [g[:100001], g[100001:]]
+            elif step == 2:
+                parts = [g[:100001].clone(), g[100001:].clone()]
+            else:
+                parts = [g]
             comm.fusedSparsification(parts, d_acc, spars, topk)
             comm.wait()
             torch.cuda.synchronize()
+            if step == 2:
+                g = torch.cat(parts)
             if topk:
                 dense, accs, _ = ocomm.sparse_topk_step(gs, accs, spars, mode)
             else:

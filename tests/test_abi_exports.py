@@ -20,7 +20,7 @@ def test_status_strings_and_version():
     lib = _lib.lib()
     assert lib.sgb_version() >= 100
     assert lib.sgb_status_string(0) == b"ok"
-    for code in range(-8, 0):
+    for code in range(-9, 0):
         assert lib.sgb_status_string(code) != b"unknown status"
 
 
