@@ -155,9 +155,8 @@ int half_init(sgb_comm* c) {
 }
 
 int sparse_init(sgb_comm* c) {
-  if (c->sum) return SGB_OK;
+  if (c->pay_send) return SGB_OK;
   const size_t n = c->max_elems;
-  CU(cudaMalloc(&c->sum, n * sizeof(float)));
   CU(cudaMalloc(&c->pay_send, 2 * n * sizeof(int)));
   CU(cudaMalloc(&c->pay_recv, 2 * n * sizeof(int) * static_cast<size_t>(c->world)));
   c->ws_bytes = sgb_sparse_workspace_bytes(n);
@@ -435,7 +434,7 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
     nnz_max = static_cast<size_t>(sgb_topk_count(spars, n));
     for (int r = 0; r < W; ++r) c->nnz_host[r] = static_cast<int>(nnz_max);
     if (nnz_max)
-      OK(sgb_sparse_topk_f32(grad, accumulation, c->sum, n, nnz_max, c->topk_mode, c->pay_send,
+      OK(sgb_sparse_topk_f32(grad, accumulation, nullptr, n, nnz_max, c->topk_mode, c->pay_send,
                              reinterpret_cast<float*>(c->pay_send) + nnz_max, c->ws, c->ws_bytes,
                              c->c1));
   }

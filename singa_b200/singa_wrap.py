@@ -565,10 +565,9 @@ def sparse_topk(g, acc, k, mode="magnitude"):
     k = min(int(k), n)
     idx = torch.empty(max(k, 1), dtype=_I32, device=g.device)
     val = torch.empty(max(k, 1), dtype=_F32, device=g.device)
-    scratch = torch.empty(max(n, 1), dtype=_F32, device=g.device)
     need = _lib.lib().sgb_sparse_workspace_bytes(n)
     ws, wsn = _ws_args(g.device, need)
-    _lib.call("sgb_sparse_topk_f32", _p(g), None if acc is None else _p(acc), _p(scratch), n, k,
+    _lib.call("sgb_sparse_topk_f32", _p(g), None if acc is None else _p(acc), None, n, k,
               {"magnitude": 0, "compat": 1}[mode], _p(idx), _p(val), ws, wsn, _stream())
     return idx[:k], val[:k]
 
