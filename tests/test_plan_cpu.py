@@ -79,3 +79,27 @@ def test_peephole_pass_reproduces_the_hand_fused_plan():
     extra = Op("sum_all", dict(x=ops[i].args["dx"], out="loss"))
     fused = fuse_plan(dict(plan, ops=ops[:i + 2] + [extra] + ops[i + 2:]))
     assert any(o.kind == "relu_bwd" and o.args["dx"] == ops[i].args["dx"] for o in fused["ops"])
+
+
+def test_traffic_totals_and_idempotent_fusion():
+    call = build_plan(fused=False)
+    fused = fuse_plan(call)
+    gb = lambda p: sum(algorithmic_bytes(p)[0].values()) / 1e9
+    assert abs(gb(call) - 10.898) < 1e-3 and abs(gb(fused) - 8.4635) < 1e-3
+    again = fuse_plan(fused)
+    assert [o.kind for o in again["ops"]] == [o.kind for o in fused["ops"]]
+    kinds = [o.kind for o in fused["ops"]]
+    assert kinds.count("softmax_ce") == 1 and "softmax" not in kinds and "ce_fwd" not in kinds
+    assert kinds.count("bn_relu_bwd") == 33 and kinds.count("bn_bwd") == 20 and kinds.count("add_relu_bwd") == 15
+
+
+def test_loss_head_is_not_fused_across_a_use_of_the_gradient():
+    from singa_b200.resnet50_path import Op
+    plan = build_plan(batch=2, image=64, num_classes=10, blocks=(1, 1, 1, 1))
+    ops = list(plan["ops"])
+    i = next(k for k, o in enumerate(ops) if o.kind == "ce_fwd")
+    # an op between the loss and the gradient that reads the gradient buffer blocks the rewrite
+    blocker = Op("sum_all", dict(x="dlogits", out="loss"))
+    fused = fuse_plan(dict(plan, ops=ops[:i + 1] + [blocker] + ops[i + 1:]))
+    kinds = [o.kind for o in fused["ops"]]
+    assert "softmax_ce" not in kinds and "softmax" in kinds and "ce_grad" in kinds
