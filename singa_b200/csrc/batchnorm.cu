@@ -117,6 +117,11 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     partial[static_cast<size_t>(c) * gridDim.x + slice] = make_float2(s_dy, s_dyx);
 }
 
+// Units (16-byte vectors, or floats when !VEC) per thread of the apply pass:
+// the coefficient lookup and the barrier are paid once per CTA, so more units
+// per CTA make them cheaper per byte.
+constexpr int kApplyUnits = 4;
+
 template <bool VEC, bool MASK>
 __global__ void __launch_bounds__(kBlock)
 bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
@@ -130,24 +135,28 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const int c = sh.C - 1 - blockIdx.y;
   // issue this thread's loads first, so that their latency overlaps the
   // partial-sum lookup below
-  const int unit = blockIdx.x * kBlock + threadIdx.x;
   constexpr int kW = VEC ? 4 : 1;
   const int hwu = sh.HW / kW, total = sh.N * hwu;
-  const bool live = unit < total;
-  size_t off = 0;
-  Vec4f vx, vg, vm;
-  vx.f[0] = vg.f[0] = vm.f[0] = 0.f;
-  if (live) {
-    const int n = unit / hwu, q = unit - n * hwu;
-    off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + static_cast<size_t>(q) * kW;
-    if (VEC) {
-      vx.u = ld128(x + off);
-      vg.u = ld128(dy + off);
-      if (MASK) vm.u = ld128(relu_in + off);
-    } else {
-      vx.f[0] = x[off];
-      vg.f[0] = dy[off];
-      if (MASK) vm.f[0] = relu_in[off];
+  const int unit0 = blockIdx.x * (kBlock * kApplyUnits) + threadIdx.x;
+  size_t off[kApplyUnits];
+  Vec4f vx[kApplyUnits], vg[kApplyUnits], vm[kApplyUnits];
+  UnitWalk w(min(unit0, total - 1), kBlock, hwu);
+#pragma unroll
+  for (int j = 0; j < kApplyUnits; ++j) {
+    vx[j].f[0] = vg[j].f[0] = vm[j].f[0] = 0.f;
+    off[j] = 0;
+    if (unit0 + j * kBlock < total) {
+      off[j] = (static_cast<size_t>(w.n) * sh.C + c) * sh.HW + static_cast<size_t>(w.q) * kW;
+      if (VEC) {
+        vx[j].u = ld128(x + off[j]);
+        vg[j].u = ld128(dy + off[j]);
+        if (MASK) vm[j].u = ld128(relu_in + off[j]);
+      } else {
+        vx[j].f[0] = x[off[j]];
+        vg[j].f[0] = dy[off[j]];
+        if (MASK) vm[j].f[0] = relu_in[off[j]];
+      }
+      w.next();
     }
   }
   if (threadIdx.x < 32) {
@@ -175,21 +184,24 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     }
   }
   __syncthreads();
-  if (!live) return;
   const float k = coef[0], a = coef[1], b = coef[2], mu = coef[3];
-  if (VEC) {
-    Vec4f o;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float g = vg.f[j];
-      if (MASK) g = vm.f[j] > 0 ? g : 0.0f;
-      o.f[j] = k * (g - a - (vx.f[j] - mu) * b);
+  for (int j = 0; j < kApplyUnits; ++j) {
+    if (unit0 + j * kBlock >= total) break;
+    if (VEC) {
+      Vec4f o;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float g = vg[j].f[i];
+        if (MASK) g = vm[j].f[i] > 0 ? g : 0.0f;
+        o.f[i] = k * (g - a - (vx[j].f[i] - mu) * b);
+      }
+      st128(dx + off[j], o.u);
+    } else {
+      float g = vg[j].f[0];
+      if (MASK) g = vm[j].f[0] > 0 ? g : 0.0f;
+      dx[off[j]] = k * (g - a - (vx[j].f[0] - mu) * b);
     }
-    st128(dx + off, o.u);
-  } else {
-    float g = vg.f[0];
-    if (MASK) g = vm.f[0] > 0 ? g : 0.0f;
-    dx[off] = k * (g - a - (vx.f[0] - mu) * b);
   }
 }
 
@@ -719,7 +731,7 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
   float2* partial = static_cast<float2*>(ws);
   const int total = static_cast<int>(vec ? per_channel / 4 : per_channel);
   const int per_slice = static_cast<int>(ceil_div(total, slices));
-  const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock)), C);
+  const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock * kApplyUnits)), C);
   if (vec) {
     bn_bwd_reduce_kernel<true, MASK><<<g1, kBlock, 0, s>>>(x, dy, relu_in, mean, partial, sh, per_slice);
     bn_bwd_apply_kernel<true, MASK><<<g2, kBlock, 0, s>>>(x, dy, relu_in, scale, mean, invstd,
@@ -1047,7 +1059,7 @@ int bn_backward_static(const float* x, const float* dy, const float* scale, cons
   const BnShape sh{N, C, HW};
   const int total = static_cast<int>(vec ? per_channel / 4 : per_channel);
   const int per_slice = static_cast<int>(ceil_div(total, slices));
-  const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock)), C);
+  const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock * kApplyUnits)), C);
   // pass 1 writes partial[c * slices + k] for every k < slices before pass 2
   // (same stream) reads exactly those entries, so nothing has to be cleared
   if (vec) {
