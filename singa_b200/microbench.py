@@ -181,9 +181,8 @@ def main(argv=None):
                                    val.data_ptr(), nnz.data_ptr(), ws.data_ptr(), ws.numel(), stream)
         else:
             k = L.sgb_topk_count(0.01, n)
-            scratch = torch.empty(n, device=dev)
             mode = {"magnitude": 0, "compat": 1}[a.mode]
-            fn = lambda: _lib.call("sgb_sparse_topk_f32", g.data_ptr(), acc.data_ptr(), scratch.data_ptr(), n, k,
+            fn = lambda: _lib.call("sgb_sparse_topk_f32", g.data_ptr(), acc.data_ptr(), None, n, k,
                                    mode, idx.data_ptr(), val.data_ptr(), ws.data_ptr(), ws.numel(), stream)
         nbytes = 12 * n
 

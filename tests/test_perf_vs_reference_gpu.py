@@ -157,7 +157,6 @@ def test_topk_selection_not_slower_than_reference_sort(libs):
     k = L.sgb_topk_count(0.01, n)
     g = torch.randn(n, device="cuda") * 1e-3
     acc = torch.zeros(n, device="cuda")
-    scratch = torch.empty(n, device="cuda")
     idx, val = torch.empty(n, dtype=torch.int32, device="cuda"), torch.empty(n, device="cuda")
     ws = torch.empty(L.sgb_sparse_workspace_bytes(n), dtype=torch.uint8, device="cuda")
 
@@ -175,7 +174,7 @@ def test_topk_selection_not_slower_than_reference_sort(libs):
             best = t if best is None or t < best else best
         return best
 
-    ours = timed(lambda: L.sgb_sparse_topk_f32(p(g), p(acc), p(scratch), n, k, 1, p(idx), p(val), p(ws), ws.numel(),
+    ours = timed(lambda: L.sgb_sparse_topk_f32(p(g), p(acc), None, n, k, 1, p(idx), p(val), p(ws), ws.numel(),
                                                None), 5)
     key = torch.empty(n, device="cuda")
 
