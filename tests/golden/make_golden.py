@@ -179,6 +179,41 @@ def main(root):
         "shape": [10, 10],
     }
 
+    # --- tensor math fixtures and small known answers (CUDA variants of the tests)
+    tm = "test/singa/test_tensor_math.cc"
+    fixture = lines(root, tm, 40, 43)
+    g["tensor_math"] = {
+        "source": tm + ":41-42 (fixture), :87-100 (ReLU), :856-864 (L2), :952-967 (MultColumn), "
+                       ":1016-1047 (MultRow, DivRow), :1049-1082 (SumRows, SumColumns), :1084-1097 (strided Exp), "
+                       ":1161-1173 (RowMax), :1254-1283 (SoftPlus, SoftSign)",
+        "dat1": c_array(fixture, "dat1"), "dat2": c_array(fixture, "dat2"), "shape": [3, 2],
+        "relu_shift": 2.0, "relu_expect_first3": expects(lines(root, tm, 87, 100), "dptr1"),
+        "mult_column_x": c_array(lines(root, tm, 952, 967), "x"),
+        "mult_row_x": c_array(lines(root, tm, 1016, 1031), "x"),
+        "div_row_x": c_array(lines(root, tm, 1033, 1047), "x"),
+        "row_max_in": c_array(lines(root, tm, 1161, 1173), "data1"),
+        "row_max_expect": expects(lines(root, tm, 1161, 1173), "dptr1"),
+        "soft_in": c_array(lines(root, tm, 1254, 1267), "data"),
+        "softsign_expect": expects(lines(root, tm, 1269, 1283), "dptr"),
+        # strided Exp: a (3,2) reshaped to (1,3,2) written through the (1,2,0) transpose of a (2,1,3)
+        # tensor; the test checks y[0], y[2], y[4] = exp(dat1[0]), exp(dat1[4]), exp(dat1[3])
+        "exp_stride_checks": [[0, 0], [2, 4], [4, 3]],
+    }
+
+    # --- legacy Dense backward on CUDA: bias gradient = column sums of dy
+    dn = "test/singa/test_dense.cc"
+    g["dense_bias_grad"] = {
+        "source": dn + ":176-242",
+        "dy": c_array(lines(root, dn, 176, 242), "dy"), "shape": [3, 3],
+    }
+
+    # --- SoftMax(axis): shapes and the 2-D view each axis maps to
+    cases = re.findall(r"_run_test\(dev, (\[[^\]]*\]), (-?\d+), (\[[^\]]*\])\)", lines(root, "test/python/test_api.py", 204, 244))
+    g["softmax_axis"] = {
+        "source": "test/python/test_api.py:204-244 (inputs uniform[0,1) + 1000, compared with a 2-D numpy softmax)",
+        "cases": [[json.loads(a), int(b), json.loads(c)] for a, b, c in cases],
+    }
+
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json")
     with open(out, "w") as f:
         json.dump(g, f, indent=1)

@@ -152,6 +152,52 @@ def test_set_axpy_transform(sw):
     assert np.array_equal(tr, m.T)
 
 
+def test_tensor_math_fixture_goldens(sw, golden):
+    """The CUDA variants of the reference's tensor-math tests on its own fixture
+    (test_tensor_math.cc) and the legacy Dense bias gradient (test_dense.cc)."""
+    g = golden["tensor_math"]
+    a = np.array(g["dat1"], np.float32)
+    m = a.reshape(g["shape"])
+    shifted = sw.scalar("add", dev(a), -g["relu_shift"])
+    np.testing.assert_array_equal(host(sw.ReLU(shifted))[:3], np.array(g["relu_expect_first3"], np.float32))
+    np.testing.assert_array_equal(host(sw.SumRows(dev(m))), m.sum(axis=0))
+    np.testing.assert_array_equal(host(sw.SumColumns(dev(m))), m.sum(axis=1))
+    # L2 = Nrm2 / size
+    np.testing.assert_allclose(host(sw.Nrm2(dev(a)))[0] / a.size, np.sqrt((a * a).sum()) / a.size, rtol=1e-6)
+    # MultColumn (diag(v) * M), MultRow and DivRow (M * diag(v), M * diag(1/v))
+    vc = np.array(g["mult_column_x"], np.float32)
+    np.testing.assert_array_equal(host(sw.DGMM(False, dev(m), dev(vc))), m * vc[:, None])
+    vr = np.array(g["mult_row_x"], np.float32)
+    np.testing.assert_array_equal(host(sw.DGMM(True, dev(m), dev(vr))), m * vr[None, :])
+    inv = sw.scalar("rdiv", dev(np.array(g["div_row_x"], np.float32)), 1.0)      # 1 / v, as DivRow forms it
+    np.testing.assert_allclose(host(sw.DGMM(True, dev(m), inv)), m / vr[None, :], rtol=1e-6)
+    rm = np.array(g["row_max_in"], np.float32).reshape(2, 2)
+    np.testing.assert_array_equal(host(sw.RowMax(dev(rm))), np.array(g["row_max_expect"], np.float32))
+    si = np.array(g["soft_in"], np.float32)
+    np.testing.assert_allclose(host(sw.unary("softplus", dev(si))), [np.log(2.0), np.log(np.e + 1.0)], atol=1e-5)
+    np.testing.assert_array_equal(host(sw.unary("softsign", dev(si))), np.array(g["softsign_expect"], np.float32))
+    # strided Exp: exp of the fixture seen as (1,3,2), written through a (1,2,0)-transposed (2,1,3) tensor
+    # = the contiguous materialisation of the transposed view; the test checks three entries
+    y = host(sw.unary("exp", sw.Transform(dev(a), (2, 1, 3), (1, 2, 2))))
+    ref = np.exp(a.reshape(1, 3, 2)).transpose(2, 0, 1).reshape(-1)
+    np.testing.assert_allclose(y.reshape(-1), ref, rtol=1e-6)
+    for out_i, dat_i in g["exp_stride_checks"]:
+        np.testing.assert_allclose(y.reshape(-1)[out_i], np.exp(a[dat_i]), rtol=1e-5)
+    d = golden["dense_bias_grad"]
+    dy = np.array(d["dy"], np.float32).reshape(d["shape"])
+    np.testing.assert_array_equal(host(sw.SumRows(dev(dy))), dy.sum(axis=0))
+
+
+def test_softmax_axis_goldens(sw, golden):
+    rng = np.random.default_rng(0)
+    for shape, axis, two_d in golden["softmax_axis"]["cases"]:
+        x = (rng.random(shape) + 1000).astype(np.float32)
+        x2 = x.reshape(two_d)
+        e = np.exp(x2 - x2.max())
+        want = (e / e.sum(axis=1, keepdims=True)).reshape(shape)
+        np.testing.assert_array_almost_equal(host(sw.SoftMax(dev(x), axis)), want)
+
+
 def test_cpu_tensor_is_rejected(sw):
     with pytest.raises(ValueError):
         sw.ReLU(torch.zeros(4))

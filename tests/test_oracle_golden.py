@@ -131,6 +131,38 @@ def test_sum_rows_columns(oracle):
     np.testing.assert_allclose(oracle.conv_bias_backward(dy), dy.sum(axis=(0, 2, 3)), rtol=1e-5, atol=1e-6)
 
 
+def test_tensor_math_fixture_goldens(golden, oracle):
+    """The reference's tensor-math fixture (test_tensor_math.cc): ReLU of the
+    shifted fixture, SumRows / SumColumns, and the legacy Dense bias gradient
+    (test_dense.cc: column sums of dy)."""
+    g = golden["tensor_math"]
+    a = np.array(g["dat1"], np.float32)
+    r = oracle.relu(a - np.float32(g["relu_shift"]))
+    np.testing.assert_array_equal(r[:3], np.array(g["relu_expect_first3"], np.float32))
+    m = a.reshape(g["shape"])
+    np.testing.assert_array_equal(oracle.sum_rows(m), np.array([9.0, 12.0], np.float32))      # 1+3+5, 2+4+6
+    np.testing.assert_array_equal(oracle.sum_columns(m), np.array([3.0, 7.0, 11.0], np.float32))
+    d = golden["dense_bias_grad"]
+    dy = np.array(d["dy"], np.float32).reshape(d["shape"])
+    np.testing.assert_array_equal(oracle.sum_rows(dy), np.array([6.0, 6.0, 6.0], np.float32))
+
+
+def test_softmax_axis_goldens(golden, oracle):
+    """test_api.py:204-244: SoftMax(axis) equals a 2-D softmax of the reshaped
+    input (rows = product of the leading axes)."""
+    rng = np.random.default_rng(0)
+    for shape, axis, two_d in golden["softmax_axis"]["cases"]:
+        x = (rng.random(shape) + 1000).astype(np.float32)
+        x2 = x.reshape(two_d)
+        e = np.exp(x2 - x2.max())
+        want = (e / e.sum(axis=1, keepdims=True)).reshape(shape)
+        ax = axis % len(shape)
+        rows = int(np.prod(shape[:ax])) if ax else 1
+        assert [rows, x.size // rows] == two_d
+        got = oracle.softmax(x.reshape(rows, -1)).reshape(shape)
+        np.testing.assert_array_almost_equal(got, want)
+
+
 def test_dist_constant_golden(golden):
     # test/python/test_dist.py: grad=1, param=10 -> 10 - 0.1 in all six modes.
     from oracle import comm
