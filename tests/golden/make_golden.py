@@ -130,6 +130,14 @@ def main(root):
         "x": lit["data"], "dy": lit["data"], "scale": [1] * lit["C"],
         "dx": lit["dx_truth"], "decimal": 6,
     }
+    lit = py_func_literals(root, rel, "test_batchnorm_training_gpu")
+    g["batchnorm_training_api"] = {
+        "source": rel + ":31-54 (numpy model), %d-%d" % tuple(lit["_lines"]),
+        "x": lit["x_0"], "x_shape": [2, 2, 2, 2], "scale": lit["s_0"], "bias": lit["b_0"],
+        "running_mean": lit["rm_0"], "running_var": lit["rv_0"], "momenta": [0.0, 1.0, 0.2],
+        "random_case": {"shape": [10, 10, 20, 20], "momentum": 0.2},
+        "decimals": {"y": 4, "batch_mean": 6, "running_mean": 6, "saved_inv_std": 3, "running_var": 4},
+    }
     lit = py_func_literals(root, rel, "test_dnnl_pooling_max")
     g["maxpool_api"] = {
         "source": rel + ":%d-%d" % tuple(lit["_lines"]),

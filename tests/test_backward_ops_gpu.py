@@ -139,6 +139,44 @@ def test_batchnorm_golden(sw, oracle, golden):
     np.testing.assert_array_almost_equal(host(dx), np.array(g["dx"], np.float32), decimal=g["decimal"])
 
 
+def _bn_training_model(x, scale, bias, rm, rv, momentum, e=1e-5):
+    """The numpy statement of training-mode batch norm that the reference's API
+    test checks cuDNN against (test/python/test_api.py:31-54), in float64."""
+    x = x.astype(np.float64)
+    axes = (0, 2, 3)
+    bm, bv = x.mean(axis=axes), x.var(axis=axes)
+    shape = (1, -1, 1, 1)
+    y = (x - bm.reshape(shape)) / np.sqrt(bv.reshape(shape) + e) * scale.reshape(shape) + bias.reshape(shape)
+    m = x.size // x.shape[1]
+    return (y, momentum * bm + (1 - momentum) * rm, momentum * bv * m / (m - 1) + (1 - momentum) * rv, bm,
+            1.0 / np.sqrt(bv))
+
+
+def test_batchnorm_training_api_golden(sw, oracle, golden):
+    g = golden["batchnorm_training_api"]
+    dec = g["decimals"]
+    cases = [(np.array(g["x"], np.float32).reshape(g["x_shape"]), np.array(g["scale"], np.float32),
+              np.array(g["bias"], np.float32), np.array(g["running_mean"], np.float32),
+              np.array(g["running_var"], np.float32), m) for m in g["momenta"]]
+    rng = np.random.default_rng(0)
+    shp = g["random_case"]["shape"]
+    cases.append((rng.random(shp, dtype=np.float32),) + tuple(rng.random(shp[1], dtype=np.float32) for _ in range(4))
+                 + (g["random_case"]["momentum"],))
+    for x, s0, b0, rm0, rv0, mom in cases:
+        y1, rm1, rv1, bm1, bv1 = _bn_training_model(x, s0, b0, rm0, rv0, mom)
+        h = sw.CudnnBatchNormHandle(mom, dev(x))
+        rm, rv = dev(rm0), dev(rv0)
+        y, bm, bv = sw.GpuBatchNormForwardTraining(h, dev(x), dev(s0), dev(b0), rm, rv)
+        np.testing.assert_array_almost_equal(host(y), y1, decimal=dec["y"])
+        np.testing.assert_array_almost_equal(host(bm), bm1, decimal=dec["batch_mean"])
+        np.testing.assert_array_almost_equal(host(rm), rm1, decimal=dec["running_mean"] - 1)
+        np.testing.assert_array_almost_equal(host(bv), bv1, decimal=dec["saved_inv_std"])
+        np.testing.assert_array_almost_equal(host(rv), rv1, decimal=dec["running_var"])
+        om, oi = oracle.bn_stats(x)
+        np.testing.assert_array_almost_equal(om, bm1, decimal=dec["batch_mean"])
+        np.testing.assert_array_almost_equal(oi, bv1, decimal=dec["saved_inv_std"])
+
+
 BN_SHAPES = [(1, 1, 1, 1), (2, 3, 4, 4), (4, 5, 7, 7), (3, 2, 5, 3), (8, 16, 14, 14), (32, 64, 28, 28),
              (32, 2048, 7, 7), (32, 64, 56, 56), (16, 100), (256, 4096), (7, 3),
              (3, 8, 5, 5), (2, 6, 3, 2), (32, 512, 7, 7), (5, 12, 3, 3), (32, 256, 56, 56)]

@@ -131,6 +131,19 @@ def test_sum_rows_columns(oracle):
     np.testing.assert_allclose(oracle.conv_bias_backward(dy), dy.sum(axis=(0, 2, 3)), rtol=1e-5, atol=1e-6)
 
 
+def test_batchnorm_training_api_golden(golden, oracle):
+    """test_api.py:31-54, 107-161: batch mean and saved inverse std (no epsilon)
+    of the training-mode forward, which is what the backward consumes."""
+    g = golden["batchnorm_training_api"]
+    x = np.array(g["x"], np.float32).reshape(g["x_shape"])
+    mean, invstd = oracle.bn_stats(x)
+    x64 = x.astype(np.float64)
+    np.testing.assert_array_almost_equal(mean, x64.mean(axis=(0, 2, 3)), decimal=6)
+    np.testing.assert_array_almost_equal(invstd, 1.0 / np.sqrt(x64.var(axis=(0, 2, 3))), decimal=3)
+    np.testing.assert_allclose(mean, [5.5, 11.0])
+    np.testing.assert_allclose(invstd, [1.0 / 4.5, 1.0 / 9.0], rtol=1e-6)
+
+
 def test_tensor_math_fixture_goldens(golden, oracle):
     """The reference's tensor-math fixture (test_tensor_math.cc): ReLU of the
     shifted fixture, SumRows / SumColumns, and the legacy Dense bias gradient
