@@ -208,6 +208,23 @@ def main(root):
         "exp_stride_checks": [[0, 0], [2, 4], [4, 3]],
     }
 
+    # --- cuDNN softmax layer tests: row softmax of a literal input, 1-D and 2-D
+    sm = "test/singa/test_cudnn_softmax.cc"
+    g["softmax_cudnn"] = {
+        "source": sm + ":44-68 (1-D), :104-132 (2-D); expectation = exp(x) / sum(exp(x)) per row",
+        "x": c_array(lines(root, sm, 44, 68), "x"), "shapes": [[1, 6], [2, 3]],
+    }
+
+    # --- AsType float <-> int on CUDA
+    tc = "test/singa/test_tensor.cc"
+    g["astype"] = {
+        "source": tc + ":73-110; test/python/test_tensor.py:405-425 (uniform(-5, 5) floats truncate toward zero)",
+        "float_in": c_array(lines(root, tc, 73, 90), "data"),
+        "int_expect": expects(lines(root, tc, 73, 90), "dptr2"),
+        "int_in": [int(v) for v in c_array(lines(root, tc, 92, 110), "data")],
+        "float_expect": expects(lines(root, tc, 92, 110), "dptr2"),
+    }
+
     # --- legacy Dense backward on CUDA: bias gradient = column sums of dy
     dn = "test/singa/test_dense.cc"
     g["dense_bias_grad"] = {

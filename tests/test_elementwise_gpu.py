@@ -188,6 +188,27 @@ def test_tensor_math_fixture_goldens(sw, golden):
     np.testing.assert_array_equal(host(sw.SumRows(dev(dy))), dy.sum(axis=0))
 
 
+def test_astype_goldens(sw, golden):
+    g = golden["astype"]
+    t = sw.AsType(dev(np.array(g["float_in"], np.float32)), torch.int32)
+    np.testing.assert_array_equal(host(t), np.array(g["int_expect"], np.int32))
+    t = sw.AsType(dev(np.array(g["int_in"], np.int32)), torch.float32)
+    np.testing.assert_array_equal(host(t), np.array(g["float_expect"], np.float32))
+    rng = np.random.default_rng(3)
+    f = (rng.random((2, 3)) * 10 - 5).astype(np.float32)           # the python test's distribution
+    i = sw.AsType(dev(f), torch.int32)
+    np.testing.assert_array_equal(host(i), f.astype(np.int32))
+    np.testing.assert_array_equal(host(sw.AsType(i, torch.float32)), f.astype(np.int32).astype(np.float32))
+
+
+def test_softmax_cudnn_layer_golden(sw, golden):
+    g = golden["softmax_cudnn"]
+    for shape in g["shapes"]:
+        x = np.array(g["x"], np.float32).reshape(shape)
+        e = np.exp(x.astype(np.float64))
+        np.testing.assert_allclose(host(sw.SoftMax(dev(x))), e / e.sum(axis=1, keepdims=True), rtol=1e-6)
+
+
 def test_softmax_axis_goldens(sw, golden):
     rng = np.random.default_rng(0)
     for shape, axis, two_d in golden["softmax_axis"]["cases"]:

@@ -160,6 +160,14 @@ def test_tensor_math_fixture_goldens(golden, oracle):
     np.testing.assert_array_equal(oracle.sum_rows(dy), np.array([6.0, 6.0, 6.0], np.float32))
 
 
+def test_softmax_cudnn_layer_golden(golden, oracle):
+    g = golden["softmax_cudnn"]
+    for shape in g["shapes"]:
+        x = np.array(g["x"], np.float32).reshape(shape)
+        e = np.exp(x.astype(np.float64))
+        np.testing.assert_allclose(oracle.softmax(x), e / e.sum(axis=1, keepdims=True), rtol=1e-6)
+
+
 def test_softmax_axis_goldens(golden, oracle):
     """test_api.py:204-244: SoftMax(axis) equals a 2-D softmax of the reshaped
     input (rows = product of the leading axes)."""
