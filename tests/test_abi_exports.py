@@ -54,11 +54,13 @@ def test_launcher_library_exports_the_reference_symbols():
     ctypes.CDLL(build.ADAPTER_LIB)       # resolves libsgb.so through its $ORIGIN runpath
 
 
-def test_cpp_communicator_header_compiles_links_and_runs(tmp_path):
-    """include/sgb_communicator.hpp (the C++ mirror of singa::Communicator's
-    public interface) compiles warning-free as C++17 without CUDA headers, every
-    method instantiates, and the program links against libsgb.so.  The run only
-    asks for the size of the NCCL id (no GPU)."""
+def test_cpp_headers_compile_link_and_run(tmp_path):
+    """include/sgb_communicator.hpp and include/sgb_operations.hpp (the C++
+    mirrors of singa::Communicator and of the batch-norm / pooling / conv-bias
+    operation handles and functions) compile warning-free as C++17 without CUDA
+    headers, everything instantiates, and the program links against libsgb.so.
+    The run checks the handles' size arithmetic and asks for the size of the
+    NCCL id (no GPU)."""
     import os
     import shutil
     import subprocess
@@ -70,8 +72,21 @@ def test_cpp_communicator_header_compiles_links_and_runs(tmp_path):
     src = tmp_path / "use_communicator.cc"
     src.write_text(r'''
 #include "sgb_communicator.hpp"
+#include "sgb_operations.hpp"
 int main(int argc, char**) {
+  // handle arithmetic needs no GPU: the reference's own size rules
+  sgb::CudnnBatchNormHandle bn(0.9f, {32, 64, 56, 56}), bn2(0.9f, {16, 100});
+  sgb::CudnnPoolingHandle mp({32, 64, 112, 112}, {3, 3}, {2, 2}, {1, 1}, true);
+  if (bn.is_2d || !bn2.is_2d || bn2.height != 1 || bn.height * bn.width != 3136) return 3;
+  if (mp.pooled_height != 56 || mp.pooled_width != 56 || !mp.is_max_pooling) return 4;
   if (argc > 1) {   // instantiated for the compiler and linker only: needs a GPU and its NCCL peers to run
+    sgb::GpuBatchNormForwardTraining(bn, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                     nullptr, 0, nullptr);
+    sgb::GpuBatchNormBackward(bn, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                              bn.workspace_bytes(), nullptr);
+    sgb::GpuPoolingForward(mp, nullptr, nullptr, nullptr);
+    sgb::GpuPoolingBackward(mp, nullptr, nullptr, nullptr, nullptr, nullptr);
+    sgb::GpuConvBackwardb(nullptr, nullptr, 1, 1, 1, 1, nullptr, 0, nullptr);
     sgb::NcclIdHolder id;
     sgb::Communicator c(0, 1, id, 1024);
     sgb::TensorRef t{nullptr, 0, false};

@@ -1,7 +1,10 @@
-"""The C++ mirror of singa::Communicator (include/sgb_communicator.hpp) driven
-from a C++ program on one GPU (world size 1): every public method runs, and a
+"""The C++ mirrors of singa::Communicator (include/sgb_communicator.hpp) and of
+the operation handles (include/sgb_operations.hpp) driven from a C++ program
+on one GPU.  Communicator, world size 1: every public method runs, and a
 one-rank exchange must return its input (all-reduce of one rank, fp16 round
-trip of fp16-exact values, top-K with ratio 1, threshold 0)."""
+trip of fp16-exact values, top-K with ratio 1, threshold 0).  Operations: the
+reference's own max-pooling vectors (test_cudnn_pooling.cc) and closed-form
+batch-norm / conv-bias cases on the input of its BN API test."""
 import os
 import shutil
 import subprocess
@@ -17,6 +20,53 @@ PROGRAM = r'''
 #include <cstdio>
 #include <vector>
 #include "sgb_communicator.hpp"
+#include "sgb_operations.hpp"
+
+static float* to_dev(const std::vector<float>& h) {
+  float* d;
+  cudaMalloc(&d, (h.size() ? h.size() : 1) * sizeof(float));
+  cudaMemcpy(d, h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice);
+  return d;
+}
+static bool near(const float* dev, const std::vector<float>& want, float tol, const char* what) {
+  std::vector<float> got(want.size());
+  cudaMemcpy(got.data(), dev, want.size() * sizeof(float), cudaMemcpyDeviceToHost);
+  for (size_t i = 0; i < want.size(); ++i)
+    if (std::fabs(got[i] - want[i]) > tol) { std::printf("%s[%zu]: %g vs %g\n", what, i, got[i], want[i]); return false; }
+  return true;
+}
+
+static bool operations() {
+  bool ok = true;
+  // max pooling: the reference's vectors
+  const std::vector<float> px = {POOL_X}, py = {POOL_Y}, pdy = {POOL_DY}, pdx = {POOL_DX};
+  sgb::CudnnPoolingHandle ph({1, 1, 3, 3}, {2, 2}, {1, 1}, {0, 0}, true);
+  float *x = to_dev(px), *y = to_dev(py), *dy = to_dev(pdy), *dx = to_dev(pdx);
+  cudaMemset(y, 0, py.size() * sizeof(float));
+  cudaMemset(dx, 0, pdx.size() * sizeof(float));
+  sgb::GpuPoolingForward(ph, x, y, nullptr);
+  sgb::GpuPoolingBackward(ph, dy, x, y, dx, nullptr);
+  ok = ok && near(y, py, 0.f, "pool y") && near(dx, pdx, 0.f, "pool dx");
+  // batch norm on the BN API test's input: mean (5.5, 11), inverse std (1/4.5, 1/9); with dy = 1
+  // everywhere dbias = 8, dscale = 0 and dx = 0
+  const std::vector<float> bx = {BN_X}, ones(16, 1.0f), two(2, 1.0f), zero2(2, 0.0f);
+  sgb::CudnnBatchNormHandle bh(0.1f, {2, 2, 2, 2});
+  void* ws;
+  cudaMalloc(&ws, bh.workspace_bytes() + 256);
+  float *bxd = to_dev(bx), *byd = to_dev(ones), *sc = to_dev(two), *bi = to_dev(zero2), *rm = to_dev(zero2),
+        *rv = to_dev(two), *mean = to_dev(zero2), *var = to_dev(zero2), *g = to_dev(ones), *bdx = to_dev(ones),
+        *ds = to_dev(two), *db = to_dev(two);
+  sgb::GpuBatchNormForwardTraining(bh, bxd, sc, bi, rm, rv, byd, mean, var, ws, bh.workspace_bytes(), nullptr);
+  ok = ok && near(mean, {5.5f, 11.0f}, 1e-6f, "bn mean") && near(var, {1.0f / 4.5f, 1.0f / 9.0f}, 1e-6f, "bn invstd");
+  ok = ok && near(rm, {0.55f, 1.1f}, 1e-6f, "running mean");
+  sgb::GpuBatchNormBackward(bh, g, bxd, sc, mean, var, bdx, ds, db, ws, bh.workspace_bytes(), nullptr);
+  ok = ok && near(db, {8.0f, 8.0f}, 0.f, "dbias") && near(ds, {0.0f, 0.0f}, 1e-5f, "dscale") &&
+       near(bdx, std::vector<float>(16, 0.0f), 1e-6f, "bn dx");
+  // conv bias gradient of dy = 1: N * H * W per channel
+  sgb::GpuConvBackwardb(g, db, 2, 2, 2, 2, ws, bh.workspace_bytes(), nullptr);
+  ok = ok && near(db, {8.0f, 8.0f}, 0.f, "conv db");
+  return ok && cudaDeviceSynchronize() == cudaSuccess;
+}
 
 static bool same(const float* dev, const std::vector<float>& want) {
   std::vector<float> got(want.size());
@@ -65,13 +115,14 @@ int main() {
   c.wait(nullptr);
   ok = ok && same(a, h) && same(b, h);
   if (cudaDeviceSynchronize() != cudaSuccess) return 3;
+  ok = ok && operations();
   std::printf(ok ? "ok\n" : "FAILED\n");
   return ok ? 0 : 1;
 }
 '''
 
 
-def test_cpp_communicator_world_1(tmp_path):
+def test_cpp_communicator_world_1_and_operation_mirrors(tmp_path, golden):
     if shutil.which("nvcc") is None:
         pytest.skip("nvcc not available on this box")
     import torch
@@ -79,7 +130,13 @@ def test_cpp_communicator_world_1(tmp_path):
     lib_path = build.build()
     libdir = os.path.dirname(lib_path)
     src, exe = tmp_path / "comm.cu", tmp_path / "comm"
-    src.write_text(PROGRAM)
+    lit = lambda v: ", ".join("%rf" % float(a) for a in v)
+    pool, bn = golden["maxpool_cudnn"], golden["batchnorm_training_api"]
+    program = PROGRAM
+    for key, vals in (("POOL_X", pool["x"]), ("POOL_Y", pool["y"]), ("POOL_DY", pool["dy"]), ("POOL_DX", pool["dx"]),
+                      ("BN_X", bn["x"])):
+        program = program.replace("{" + key + "}", "{" + lit(vals) + "}")
+    src.write_text(program)
     r = subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
                         os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-L", libdir, "-lsgb",
                         "-Xlinker", "-rpath=" + libdir], capture_output=True, text=True)
