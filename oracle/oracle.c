@@ -8,13 +8,16 @@
  * and the CPU leg of the benchmark do.
  *
  * Parity status: PINNED for the operations that the reference's own tests
- * hold golden vectors for (cross-entropy forward/backward, batch-norm
- * backward, max/avg pooling forward/backward, SGD/momentum/weight-decay,
- * ReLU forward/backward, row/column sums) - see tests/test_oracle_golden.py,
- * which replays those vectors.  UNPINNED by the reference (it has no test
- * that could detect a difference) for: pooling ties, top-K ordering/ties,
- * threshold compaction order, residual accumulation over several steps and
- * fp16 rounding; those follow the reference source as cited below.
+ * hold golden vectors for (cross-entropy forward/backward, row softmax,
+ * batch-norm statistics and backward, max/avg pooling forward/backward,
+ * SGD/momentum/weight-decay, ReLU forward/backward, row/column sums) - see
+ * tests/test_oracle_golden.py, which replays those vectors.  Pooling ties and
+ * the top-K index set, which no reference test pins, are pinned instead
+ * against the reference's own CUDA path run on a B200
+ * (tests/test_vs_reference_cuda_gpu.py).  UNPINNED by the reference (it has no
+ * test that could detect a difference) for: threshold compaction order,
+ * residual accumulation over several steps and fp16 rounding; those follow
+ * the reference source as cited below.
  *
  * Each function cites the reference file:line (paths inside apache/singa)
  * whose behaviour it follows.  Loops are OpenMP-parallel over independent
