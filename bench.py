@@ -248,6 +248,9 @@ def main():
                     help="resnet50 (headline) or the sparse gradient exchange microbench: a flat 1e8-element "
                          "fp32 gradient N(0, 1e-3^2), residual accumulation on, top-K ratio 0.01 / threshold 2e-3")
     ap.add_argument("--elements", type=int, default=100000000)
+    ap.add_argument("--pool-argmax", action="store_true",
+                    help="max-pool backward from the forward partner's arg-max record instead of (x, y): changes "
+                         "what the backward consumes, so it is not the default")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -289,8 +292,9 @@ def main():
     plan = build_plan(batch=BATCH, fused=False)        # the reference's call sequence ...
     if fused:
         plan = fuse_plan(plan)                         # ... rewritten by the peephole pass
-    path = HotPathGPU(plan, communicator=comm, world=world, seed=1000 + rank, dist_option=args.dist_option)
-    by_family, nparam = algorithmic_bytes(plan, world)
+    path = HotPathGPU(plan, communicator=comm, world=world, seed=1000 + rank, dist_option=args.dist_option,
+                      pool_argmax=args.pool_argmax)
+    by_family, nparam = algorithmic_bytes(plan, world, pool_argmax=args.pool_argmax)
 
     def barrier():
         torch.cuda.synchronize()
@@ -420,7 +424,7 @@ def main():
             "config": {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
                        "global_batch": BATCH * world, "dist_option": args.dist_option,
                        "fusion": "bn+relu, join+relu, softmax+ce+grad" if fused else "none (one kernel per reference call)",
-                       "cuda_graph": use_graph, "bucket_elems": 4194304, "threshold_elems": 2097152,
+                       "cuda_graph": use_graph, "pool_argmax_record": bool(args.pool_argmax), "bucket_elems": 4194304, "threshold_elems": 2097152,
                        "l2": "inputs larger than L2: %.1f GB touched per step vs 126 MB" % (total_alg / 1e9),
                        "excluded": "cuDNN/cuBLAS contractions (conv, linear): stand-in gradients",
                        "algorithmic_GB_per_step": round(total_alg / 1e9, 3),
@@ -446,7 +450,7 @@ def kernel_launches(path):
     samples) exceeds what a cluster of eight CTAs can stage (8 x 100 KB): then
     it is the reduce + apply pair."""
     per = {"sgb_relu_backward_f32": 1, "sgb_add_relu_backward_f32": 1, "sgb_binary_f32": 1,
-           "sgb_maxpool_backward_f32": 1,
+           "sgb_maxpool_backward_f32": 1, "sgb_maxpool_backward_argmax_f32": 1,
            "sgb_avgpool_backward_f32": 1, "sgb_softmax_rows_f32": 1, "sgb_cross_entropy_f32": 1,
            "sgb_sum_all_f32": 1, "sgb_softmax_cross_entropy_bwd_f32": 1,
            "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_softmax_cross_entropy_fused_f32": 1,

@@ -369,6 +369,23 @@ int sgb_avgpool_backward_f32(const float *dy, float *dx, int N, int C, int H,
                              int W, int kh, int kw, int ph, int pw, int sh,
                              int sw, void *stream);
 
+/* Arg-max forward partner (no reference counterpart as an interface; the
+ * reference recomputes the winners from x and y inside cudnnPoolingBackward).
+ * The forward also writes one byte per window: where its first maximum in
+ * raster order sits, (row offset << 4) | column offset from the window's
+ * unclipped corner (0xff: no cell).  The backward then reads only dy and that
+ * record - results identical to sgb_maxpool_backward_f32 bit for bit.
+ * kh, kw <= 15. */
+int sgb_maxpool_forward_argmax_f32(const float *x, float *y,
+                                   unsigned char *argmax, int N, int C, int H,
+                                   int W, int kh, int kw, int ph, int pw,
+                                   int sh, int sw, void *stream);
+int sgb_maxpool_backward_argmax_f32(const float *dy,
+                                    const unsigned char *argmax, float *dx,
+                                    int N, int C, int H, int W, int kh, int kw,
+                                    int ph, int pw, int sh, int sw,
+                                    void *stream);
+
 /* ------------------------------------------------- SGD update, multi-tensor */
 /* One fused pass of SGD.apply (python/singa/opt.py:269-310) over p, g, m:
  *   g *= grad_scale (DistOpt.update's grad /= world, opt.py:738-746)

@@ -337,6 +337,129 @@ maxpool_bwd_k3s2p1_kernel(const float* __restrict__ x, const float* __restrict__
   }
 }
 
+// ------------------------------------------------ arg-max forward partner
+// Max-pool forward that also records, per window, WHERE its (first, in raster
+// order) maximum sits: one byte, row offset in the high nibble and column
+// offset in the low nibble, both relative to the window's unclipped top-left
+// corner (oh*sh - ph, ow*sw - pw).  With that record the backward pass needs
+// neither x nor y: it reads dy and one byte per window.
+__global__ void __launch_bounds__(kBlock)
+maxpool_fwd_argmax_kernel(const float* __restrict__ x, float* __restrict__ y,
+                          unsigned char* __restrict__ arg, PoolShape p, size_t total) {
+  const size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x;
+  if (i >= total) return;
+  const int ow = static_cast<int>(i % p.OW);
+  const int oh = static_cast<int>((i / p.OW) % p.OH);
+  const size_t plane = i / (static_cast<size_t>(p.OW) * p.OH);
+  const float* xp = x + plane * p.H * p.W;
+  int h0, h1, w0, w1;
+  window(p, oh, ow, h0, h1, w0, w1);
+  const int hs = oh * p.sh - p.ph, ws = ow * p.sw - p.pw;
+  float best = -FLT_MAX;
+  int code = 0xff;                                  // matches no cell (empty or all -FLT_MAX window)
+  for (int h = h0; h < h1; ++h)
+    for (int w = w0; w < w1; ++w) {
+      const float v = xp[h * p.W + w];
+      if (v > best) {
+        best = v;
+        code = ((h - hs) << 4) | (w - ws);
+      }
+    }
+  y[i] = best;
+  arg[i] = static_cast<unsigned char>(code);
+}
+
+// Backward from the record, any geometry: one dx element per thread gathers,
+// in raster order of the windows, the dy of every covering window whose
+// record points at it.
+__global__ void __launch_bounds__(kBlock)
+maxpool_bwd_argmax_kernel(const float* __restrict__ dy, const unsigned char* __restrict__ arg,
+                          float* __restrict__ dx, PoolShape p, size_t total) {
+  const size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x;
+  if (i >= total) return;
+  const int w = static_cast<int>(i % p.W);
+  const int h = static_cast<int>((i / p.W) % p.H);
+  const size_t plane = i / (static_cast<size_t>(p.W) * p.H);
+  const float* gp = dy + plane * p.OH * p.OW;
+  const unsigned char* ap = arg + plane * p.OH * p.OW;
+  int oh_lo, oh_hi, ow_lo, ow_hi;
+  covering(h, p.ph, p.kh, p.sh, p.OH, oh_lo, oh_hi);
+  covering(w, p.pw, p.kw, p.sw, p.OW, ow_lo, ow_hi);
+  float acc = 0.f;
+  for (int oh = oh_lo; oh <= oh_hi; ++oh)
+    for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+      const int code = ap[oh * p.OW + ow];
+      const int wh = oh * p.sh - p.ph + (code >> 4), ww = ow * p.sw - p.pw + (code & 15);
+      if (code != 0xff && wh == h && ww == w) acc += gp[oh * p.OW + ow];
+    }
+  dx[i] = acc;
+}
+
+// Backward from the record for 3x3 / stride 2 / pad 1 (ResNet stem): the same
+// band / 2x4-patch scheme as maxpool_bwd_k3s2p1_kernel without its x staging
+// and winner search - the parked winners come straight from the record.
+template <int WC>
+__global__ void __launch_bounds__(kBlock)
+maxpool_bwd_argmax_k3s2p1_kernel(const float* __restrict__ dy, const unsigned char* __restrict__ arg,
+                                 float* __restrict__ dx, int H, int W_rt, int OH, int OW_rt, int rows) {
+  extern __shared__ float smem[];
+  const int W = WC ? WC : W_rt;
+  const int OW = WC ? WC / 2 : OW_rt;
+  const int wp = OW + 1;                         // winner / dy pitch (one never-matching pad column)
+  const int h_lo = blockIdx.y * rows, h_hi = min(h_lo + rows, H);
+  const int o_lo = h_lo >> 1, o_hi = min(h_hi >> 1, OH - 1);     // window rows [o_lo, o_hi]
+  const int norow = o_hi - o_lo + 1;
+  int* winner = reinterpret_cast<int*>(smem);
+  float* gs = reinterpret_cast<float*>(winner + ((rows >> 1) + 2) * wp);
+  const size_t plane = blockIdx.x;
+  const float* gp = dy + plane * OH * OW;
+  const unsigned char* ap = arg + plane * OH * OW;
+  float* dp = dx + plane * H * W;
+  for (int o = threadIdx.x; o < (norow + 1) * wp; o += kBlock) {
+    const int r = o / wp, c = o - r * wp;
+    const bool real = r < norow && c < OW;
+    float g = 0.0f;
+    int win = -2;
+    if (real) {
+      const int oh = o_lo + r;
+      g = gp[oh * OW + c];
+      const int code = ap[oh * OW + c];
+      if (code != 0xff) win = (2 * oh - 1 + (code >> 4)) * W + 2 * c - 1 + (code & 15);
+    }
+    gs[o] = g;
+    winner[o] = win;
+  }
+  __syncthreads();
+  const int w4 = W >> 2;
+  const int npatch = ((h_hi - h_lo) >> 1) * w4;
+  for (int t = threadIdx.x; t < npatch; t += kBlock) {
+    const int m = t / w4, q = t - m * w4;
+    const int* w0 = winner + m * wp + 2 * q;       // windows (m, 2q .. 2q+2)
+    const int* w1 = w0 + wp;                        // windows (m+1, ...)
+    const float* g0 = gs + m * wp + 2 * q;
+    const float* g1 = g0 + wp;
+    const int a0 = w0[0], a1 = w0[1], a2 = w0[2], b0 = w1[0], b1 = w1[1], b2 = w1[2];
+    const float ga0 = g0[0], ga1 = g0[1], ga2 = g0[2], gb0 = g1[0], gb1 = g1[1], gb2 = g1[2];
+    const int h = h_lo + 2 * m;
+    const int i0 = h * W + 4 * q, i1 = i0 + W;      // flat indices of the patch's two rows
+#define PICK(wv, gv, idx) ((wv) == (idx) ? (gv) : 0.0f)
+    float4 top, bot;
+    top.x = 0.0f + PICK(a0, ga0, i0);
+    top.y = (0.0f + PICK(a0, ga0, i0 + 1)) + PICK(a1, ga1, i0 + 1);
+    top.z = 0.0f + PICK(a1, ga1, i0 + 2);
+    top.w = (0.0f + PICK(a1, ga1, i0 + 3)) + PICK(a2, ga2, i0 + 3);
+    bot.x = (0.0f + PICK(a0, ga0, i1)) + PICK(b0, gb0, i1);
+    bot.y = (((0.0f + PICK(a0, ga0, i1 + 1)) + PICK(a1, ga1, i1 + 1)) + PICK(b0, gb0, i1 + 1)) +
+            PICK(b1, gb1, i1 + 1);
+    bot.z = (0.0f + PICK(a1, ga1, i1 + 2)) + PICK(b1, gb1, i1 + 2);
+    bot.w = (((0.0f + PICK(a1, ga1, i1 + 3)) + PICK(a2, ga2, i1 + 3)) + PICK(b1, gb1, i1 + 3)) +
+            PICK(b2, gb2, i1 + 3);
+#undef PICK
+    *reinterpret_cast<float4*>(dp + i0) = top;
+    *reinterpret_cast<float4*>(dp + i1) = bot;
+  }
+}
+
 // Band height: the largest power-of-two-ish row count whose staging fits
 // `budget` bytes of shared memory; 0 rows means even one row does not fit.
 BandPlan plan_bands(const PoolShape& p, size_t budget) {
@@ -548,6 +671,49 @@ int sgb_maxpool_backward_f32(const float* x, const float* y, const float* dy, fl
     maxpool_bwd_kernel<<<dim3(static_cast<unsigned>(planes), by), kBlock, 0, as_stream(stream)>>>(
         x, dy, dx, p);
   }
+  return launch_status();
+}
+
+int sgb_maxpool_forward_argmax_f32(const float* x, float* y, unsigned char* argmax, int N, int C, int H,
+                                   int W, int kh, int kw, int ph, int pw, int sh, int sw, void* stream) {
+  POOL_PROLOGUE(1)
+  if (!x || !y || !argmax) return SGB_ERR_NULL;
+  if (kh > 15 || kw > 15) return SGB_ERR_UNSUPPORTED;           // offsets are stored in nibbles; 15|15 is "none"
+  maxpool_fwd_argmax_kernel<<<blocks_for(out_total), kBlock, 0, as_stream(stream)>>>(x, y, argmax, p, out_total);
+  return launch_status();
+}
+
+int sgb_maxpool_backward_argmax_f32(const float* dy, const unsigned char* argmax, float* dx, int N, int C,
+                                    int H, int W, int kh, int kw, int ph, int pw, int sh, int sw,
+                                    void* stream) {
+  POOL_PROLOGUE(0)
+  if (!dy || !argmax || !dx) return SGB_ERR_NULL;
+  if (kh > 15 || kw > 15) return SGB_ERR_UNSUPPORTED;
+  const size_t planes = static_cast<size_t>(N) * C;
+  cudaStream_t s = as_stream(stream);
+  if (kh == 3 && kw == 3 && sh == 2 && sw == 2 && ph == 1 && pw == 1 && W % 4 == 0 && H % 2 == 0 && H >= 2 &&
+      aligned16(dx) && planes <= 0x7fffffffu && static_cast<long long>(H) * W <= 0x7fffffffLL) {
+    const int nb = (H + 31) / 32;
+    int rows = (H + nb - 1) / nb;
+    rows += rows & 1;
+    const int nbands = (H + rows - 1) / rows;
+    const size_t bytes = 2 * static_cast<size_t>((rows >> 1) + 2) * (p.OW + 1) * sizeof(float);
+    if (bytes <= 48 * 1024 && nbands <= 65535) {
+      const dim3 g(static_cast<unsigned>(planes), nbands);
+#define SGB_STEM_W(WW)                                                                                  \
+  if (W == WW && p.OW == WW / 2) {                                                                      \
+    maxpool_bwd_argmax_k3s2p1_kernel<WW><<<g, kBlock, bytes, s>>>(dy, argmax, dx, H, W, p.OH, p.OW, rows); \
+    return launch_status();                                                                             \
+  }
+      SGB_STEM_W(112)
+      SGB_STEM_W(56)
+      SGB_STEM_W(32)
+#undef SGB_STEM_W
+      maxpool_bwd_argmax_k3s2p1_kernel<0><<<g, kBlock, bytes, s>>>(dy, argmax, dx, H, W, p.OH, p.OW, rows);
+      return launch_status();
+    }
+  }
+  maxpool_bwd_argmax_kernel<<<blocks_for(in_total), kBlock, 0, s>>>(dy, argmax, dx, p, in_total);
   return launch_status();
 }
 

@@ -26,7 +26,7 @@ def _table(tensors):
 class HotPathGPU(object):
     def __init__(self, plan, communicator=None, world=1, seed=0, lr=0.1, momentum=0.9,
                  weight_decay=1e-5, threshold=2097152, dist_option="plain", spars=0.05,
-                 device=None, update_on_arrival=True):
+                 device=None, update_on_arrival=True, pool_argmax=False):
         self.plan, self.comm, self.world = plan, communicator, world
         self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
         self.threshold, self.dist_option, self.spars = threshold, dist_option, spars
@@ -36,6 +36,10 @@ class HotPathGPU(object):
         # results as updating everything after the final wait).
         self.update_on_arrival = bool(update_on_arrival) and communicator is not None \
             and dist_option in ("plain", "half")
+        # pool_argmax: max-pool backward consumes the arg-max record of the forward
+        # partner (produced once at set-up: the forward pass is outside this path)
+        # instead of recomputing the winners from x and y.  Same dx bit for bit.
+        self.pool_argmax = bool(pool_argmax)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.lib = _lib.lib()
         self.t = {}
@@ -166,6 +170,15 @@ class HotPathGPU(object):
                                    (p(a["x"]), p(a["dy_a"]), p(a["dy_b"]), p(a["relu_x"]), p(a["scale"]),
                                     p(a["mean"]), p(a["invstd"]), p(a["joined"]), p(a["dx"]), p(a["dscale"]),
                                     p(a["dbias"]), n, c, h * w, ws.data_ptr(), ws.numel(), S)))
+            elif k == "maxpool_bwd" and self.pool_argmax:
+                y_scratch = torch.empty_like(t[a["y"]])
+                record = torch.empty(t[a["y"]].shape, dtype=torch.uint8, device=self.device)
+                _lib.call("sgb_maxpool_forward_argmax_f32", p(a["x"]), y_scratch.data_ptr(), record.data_ptr(),
+                          *geom(a["x"], a["kernel"], a["stride"], a["pad"]), torch.cuda.current_stream().cuda_stream)
+                torch.cuda.synchronize()
+                t[a["dx"] + ".argmax"] = record
+                self.calls.append(("sgb_maxpool_backward_argmax_f32",
+                                   (p(a["dy"]), record.data_ptr(), p(a["dx"])) + geom(a["x"], a["kernel"], a["stride"], a["pad"]) + (S,)))
             elif k == "maxpool_bwd":
                 self.calls.append(("sgb_maxpool_backward_f32",
                                    (p(a["x"]), p(a["y"]), p(a["dy"]), p(a["dx"])) + geom(a["x"], a["kernel"], a["stride"], a["pad"]) + (S,)))

@@ -73,6 +73,7 @@ def main(argv=None):
     ap.add_argument("--relu", action="store_true", help="bn: fused ReLU mask")
     ap.add_argument("--join", action="store_true", help="bn: fused gradient join + ReLU mask")
     ap.add_argument("--mode", default="compat", help="topk key: compat | magnitude")
+    ap.add_argument("--argmax", action="store_true", help="maxpool: backward from the forward's arg-max record")
     ap.add_argument("--graph", action="store_true",
                     help="time a CUDA-graph replay of the calls (no host launch cost; same buffers every call)")
     ap.add_argument("--iters", type=int, default=20)
@@ -144,7 +145,12 @@ def main(argv=None):
             h = sw.CudnnPoolingHandle(x, (shape[2], shape[3]), (1, 1), (0, 0), False)
         y = sw.GpuPoolingForward(h, x)
         dy, dx = torch.randn_like(y), torch.empty_like(x)
-        if a.case == "maxpool":
+        if a.case == "maxpool" and a.argmax:
+            _, arg = sw.GpuPoolingForwardArgmax(h, x)
+            fn = lambda: _lib.call("sgb_maxpool_backward_argmax_f32", dy.data_ptr(), arg.data_ptr(), dx.data_ptr(),
+                                   *h._geom(), stream)
+            nbytes = 4 * (x.numel() + y.numel()) + y.numel()       # dy, record, dx
+        elif a.case == "maxpool":
             fn = lambda: _lib.call("sgb_maxpool_backward_f32", x.data_ptr(), y.data_ptr(), dy.data_ptr(),
                                    dx.data_ptr(), *h._geom(), stream)
             nbytes = 4 * (2 * x.numel() + 2 * y.numel())

@@ -336,7 +336,7 @@ def numel(shape):
     return n
 
 
-def algorithmic_bytes(plan, world=1):
+def algorithmic_bytes(plan, world=1, pool_argmax=False):
     """Bytes each op must move at minimum (fp32), by op family - the figures the
     roofline fraction is computed on.  BN backward counts 12 B/element (read x,
     read dy, write dx) + 20 B/channel whatever the implementation moves; the
@@ -364,6 +364,8 @@ def algorithmic_bytes(plan, world=1):
         elif op.kind == "bn_add_relu_bwd":
             s = T[a["x"]].shape                   # reads x, dy_a, dy_b, relu_x; writes joined, dx
             add("bn_add_relu_bwd", 24 * numel(s) + 20 * s[1])
+        elif op.kind == "maxpool_bwd" and pool_argmax:   # dy, one record byte per window, dx
+            add("maxpool_bwd", 4 * (numel(T[a["x"]].shape) + numel(T[a["y"]].shape)) + numel(T[a["y"]].shape))
         elif op.kind == "maxpool_bwd":
             add("maxpool_bwd", 4 * (2 * numel(T[a["x"]].shape) + 2 * numel(T[a["y"]].shape)))
         elif op.kind == "avgpool_bwd":

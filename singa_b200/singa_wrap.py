@@ -500,6 +500,27 @@ def GpuPoolingBackward(cph, dy, x, y):
     return dx
 
 
+def GpuPoolingForwardArgmax(cph, x):
+    """Max-pool forward that also returns the arg-max record (one uint8 per
+    window: where its first maximum sits) for GpuPoolingBackwardArgmax."""
+    _chk(x)
+    assert cph.is_max_pooling
+    shape = (cph.batchsize, cph.channels, cph.pooled_height, cph.pooled_width)
+    y = torch.empty(shape, dtype=_F32, device=x.device)
+    arg = torch.empty(shape, dtype=torch.uint8, device=x.device)
+    _lib.call("sgb_maxpool_forward_argmax_f32", _p(x), _p(y), _p(arg), *cph._geom(), _stream())
+    return y, arg
+
+
+def GpuPoolingBackwardArgmax(cph, dy, argmax):
+    """Max-pool backward from dy and the forward's arg-max record alone (no x,
+    no y); equals GpuPoolingBackward bit for bit."""
+    _chk(dy, argmax)
+    dx = torch.empty((cph.batchsize, cph.channels, cph.height, cph.width), dtype=_F32, device=dy.device)
+    _lib.call("sgb_maxpool_backward_argmax_f32", _p(dy), _p(argmax), _p(dx), *cph._geom(), _stream())
+    return dx
+
+
 # ------------------------------------------------------------- multi-tensor ops
 def _ptr_table(tensors):
     import ctypes as C

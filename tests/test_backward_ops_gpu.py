@@ -326,6 +326,24 @@ def test_pooling_forward_backward(sw, oracle, case, is_max):
     assert np.array_equal(dx.view(np.uint32), want.view(np.uint32)), "pool backward not bit-exact"
 
 
+@pytest.mark.parametrize("case", POOL_CASES + [((32, 64, 112, 112), (3, 3), (2, 2), (1, 1)),
+                                               ((2, 4, 56, 56), (3, 3), (2, 2), (1, 1)),
+                                               ((1, 2, 10, 20), (3, 3), (2, 2), (1, 1))])
+def test_maxpool_argmax_partner_equals_recomputing_backward(sw, case):
+    shape, k, s, p = case
+    g = torch.Generator(device="cuda").manual_seed(shape[2] * 11 + shape[3])
+    x = torch.relu(torch.randn(shape, device="cuda", generator=g))          # exact ties at 0
+    x[0, 0, 0, :] = -3.4028234663852886e38                                   # a row no window may credit
+    h = sw.CudnnPoolingHandle(x, k, s, p, is_max=True)
+    y = sw.GpuPoolingForward(h, x)
+    y2, arg = sw.GpuPoolingForwardArgmax(h, x)
+    assert torch.equal(y, y2) and arg.dtype == torch.uint8
+    dy = torch.randn(tuple(y.shape), device="cuda", generator=g)
+    want = sw.GpuPoolingBackward(h, dy, x, y)
+    got = sw.GpuPoolingBackwardArgmax(h, dy, arg)
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+
+
 def test_maxpool_backward_all_equal_window_goes_to_first(sw):
     x = np.zeros((1, 1, 4, 4), np.float32)
     h = sw.CudnnPoolingHandle(dev(x), (2, 2), (2, 2), (0, 0), True)

@@ -47,6 +47,21 @@ def test_small_resnet_step_matches_oracle(fused, graph):
     close(got["loss"], host["loss"], 1e-5, "loss")
 
 
+def test_pool_argmax_record_gives_the_same_step_bitwise():
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import build_plan
+    outs = []
+    for flag in (False, True):
+        plan = build_plan(batch=2, image=64, num_classes=10, fused=True, blocks=(1, 1, 1, 1))
+        gpu = HotPathGPU(plan, communicator=None, world=1, seed=3, pool_argmax=flag)
+        gpu.run_step()
+        torch.cuda.synchronize()
+        outs.append({p: gpu.t[p].clone() for p in plan["params"]})
+        outs[-1]["bn1.dx"] = gpu.t["bn1.dx"].clone()
+    for p in outs[0]:
+        assert torch.equal(outs[0][p], outs[1][p]), p
+
+
 def test_fused_and_unfused_plans_agree_bitwise():
     from singa_b200.hot_path import HotPathGPU
     from singa_b200.resnet50_path import build_plan
