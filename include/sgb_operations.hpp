@@ -114,6 +114,22 @@ inline void GpuPoolingBackward(const CudnnPoolingHandle& h, const float* dy, con
   check_op(st, "GpuPoolingBackward");
 }
 
+/* Forward partner with an arg-max record (one byte per window) and the backward
+ * that consumes only dy and that record; max pooling only.  No reference
+ * counterpart: an optional pair for a _Pooling2d that keeps the record. */
+inline void GpuPoolingForwardArgmax(const CudnnPoolingHandle& h, const float* x, float* y, unsigned char* argmax,
+                                    void* stream) {
+  check_op(sgb_maxpool_forward_argmax_f32(x, y, argmax, h.batchsize, h.channels, h.height, h.width, h.kernel_h,
+                                          h.kernel_w, h.pad_h, h.pad_w, h.stride_h, h.stride_w, stream),
+           "GpuPoolingForwardArgmax");
+}
+inline void GpuPoolingBackwardArgmax(const CudnnPoolingHandle& h, const float* dy, const unsigned char* argmax,
+                                     float* dx, void* stream) {
+  check_op(sgb_maxpool_backward_argmax_f32(dy, argmax, dx, h.batchsize, h.channels, h.height, h.width, h.kernel_h,
+                                           h.kernel_w, h.pad_h, h.pad_w, h.stride_h, h.stride_w, stream),
+           "GpuPoolingBackwardArgmax");
+}
+
 /* GpuConvBackwardb (convolution.cc:684-702): db[c] = sum over n, h, w of dy. */
 inline void GpuConvBackwardb(const float* dy, float* db, int batchsize, int channels, int out_h, int out_w, void* ws,
                              size_t ws_bytes, void* stream) {

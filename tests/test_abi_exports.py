@@ -86,6 +86,8 @@ int main(int argc, char**) {
                               bn.workspace_bytes(), nullptr);
     sgb::GpuPoolingForward(mp, nullptr, nullptr, nullptr);
     sgb::GpuPoolingBackward(mp, nullptr, nullptr, nullptr, nullptr, nullptr);
+    sgb::GpuPoolingForwardArgmax(mp, nullptr, nullptr, nullptr, nullptr);
+    sgb::GpuPoolingBackwardArgmax(mp, nullptr, nullptr, nullptr, nullptr);
     sgb::GpuConvBackwardb(nullptr, nullptr, 1, 1, 1, 1, nullptr, 0, nullptr);
     sgb::NcclIdHolder id;
     sgb::Communicator c(0, 1, id, 1024);
