@@ -272,7 +272,7 @@ def main():
     from singa_b200 import _lib
     from singa_b200.communicator import Communicator, NcclIdHolder
     from singa_b200.hot_path import HotPathGPU
-    from singa_b200.resnet50_path import algorithmic_bytes, build_plan, fuse_plan
+    from singa_b200.resnet50_path import add_wgrad_refresh, algorithmic_bytes, build_plan, fuse_plan
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback "
@@ -292,6 +292,7 @@ def main():
     plan = build_plan(batch=BATCH, fused=False)        # the reference's call sequence ...
     if fused:
         plan = fuse_plan(plan)                         # ... rewritten by the peephole pass
+    plan = add_wgrad_refresh(plan)                     # the contractions' weight gradients are rewritten every step
     path = HotPathGPU(plan, communicator=comm, world=world, seed=1000 + rank, dist_option=args.dist_option,
                       pool_argmax=args.pool_argmax)
     by_family, nparam = algorithmic_bytes(plan, world, pool_argmax=args.pool_argmax)

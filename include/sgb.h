@@ -485,7 +485,45 @@ int sgb_comm_destroy(sgb_comm *c);
 int sgb_comm_rank(const sgb_comm *c);
 int sgb_comm_world_size(const sgb_comm *c);
 size_t sgb_comm_staged_elems(const sgb_comm *c);
+/* The three side streams (Context::s, c1, c2 of src/core/device/cuda_gpu.cc:
+ * 76-80), for callers that profile or order against them: which = 0 (s, NCCL),
+ * 1 (c1, pre-processing), 2 (c2, post-processing). */
 void *sgb_comm_stream(const sgb_comm *c, int which);
+/* The side stream on which the result of the most recent synch / flush /
+ * sparsification call can be consumed (e.g. by an optimizer update enqueued
+ * right behind it) without waiting for the rest of the backward pass:
+ * c2 for in-place, fp16 and sparse results, c1 for an unpacked fp32 bucket.
+ * Work put there is joined to the compute stream by the next sgb_comm_wait. */
+void *sgb_comm_result_stream(const sgb_comm *c);
+/* The communicator's cross-stream ordering rules as a pure host function (no
+ * GPU needed): given the state {dirty_s, dirty_c1, dirty_c2, c2_reads_recv}
+ * and a call kind (0 synch, 1 flush in place, 2 flush packed, 3 flush half,
+ * 4 synch half, 5 sparsification, 6 stage copy, 7 wait) it updates the state
+ * and returns the edge masks recorded before the pre-processing kernel,
+ * before the collective, behind it, and behind the post-processing kernel
+ * (bits: 1 compute->c1, 2 compute->s, 4 c1->s, 8 c2(done)->s, 16 s->c1,
+ * 32 s->c2, 64 s->compute, 128 c1->compute, 256 c2->compute, 512 mark c2
+ * done).  The communicator emits exactly these edges; the reference records
+ * its compute-stream event before every stage and flush
+ * (src/io/communicator.cc:227-233, 255-271, 313-319). */
+int sgb_comm_order_plan(unsigned char *state4, int call, unsigned *edges4,
+                        int *result_stream);
+/* Per-phase device timing, the counterpart of the reference's time profiling
+ * that brackets a "Dist_s_*" / "Dist_c1_*" / "Dist_c2_*" operation with events
+ * on the stream its name selects (src/core/device/cuda_gpu.cc:128-169).
+ * begin: records the origin on the compute stream and switches timing on;
+ * every phase of every communicator call is then bracketed on its own side
+ * stream under the reference's operation name (also emitted as NVTX ranges,
+ * always).  range: brackets caller work on side stream `which` (begin != 0
+ * opens, 0 closes the range opened last).  end: synchronises the device,
+ * copies up to `capacity` rows (name, start and end in ms since the origin)
+ * and switches timing off; *count receives the number of recorded phases.
+ * Not usable while a stream is being captured (phases are then not timed). */
+int sgb_comm_profile_begin(sgb_comm *c, void *compute_stream);
+int sgb_comm_profile_range(sgb_comm *c, const char *name, int which, int begin);
+int sgb_comm_profile_end(sgb_comm *c, char *names, size_t name_stride,
+                         float *start_ms, float *end_ms, size_t capacity,
+                         size_t *count);
 /* 1 (default): top-K key as the reference's comparator computes it;
  * 0: key = |value|. */
 int sgb_comm_set_topk_mode(sgb_comm *c, int mode);

@@ -65,6 +65,12 @@ class OraclePath(object):
                 t[a["v"]][...] = cpu.sum_rows(t[a["M"]])
             elif k == "conv_bias_bwd":
                 t[a["db"]][...] = cpu.conv_bias_backward(t[a["dy"]])
+            elif k == "wgrad_refresh":
+                for p in a["params"]:
+                    t["d:" + p][...] = t["wsyn:" + p]
+            elif k == "fill":       # every parameter gradient := value (the GPU fills its gradient arena)
+                for p in self.plan["params"]:
+                    t["d:" + p][...] = np.float32(a["value"])
             elif k == "grad_ready":
                 pass     # one rank: the all-reduce of a single contribution is the identity
             elif k == "sync_and_update":
@@ -110,7 +116,7 @@ def make_tensors(plan, seed=0):
                 t[name] = np.zeros(spec.shape, np.float32)
             else:
                 t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(0.05)
-        elif k == "pgrad":
+        elif k in ("pgrad", "wsyn"):
             t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(1e-3)
         else:
             t[name] = np.zeros(spec.shape, np.float32)

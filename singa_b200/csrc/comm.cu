@@ -21,6 +21,11 @@
 #include <new>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
+#include <string>
+
+#include "comm_order.h"
 #include "common.cuh"
 #include "sparse.cuh"
 
@@ -70,12 +75,26 @@ struct sgb_comm {
   int topk_mode = 1;           // 1 = the reference comparator's key, 0 = |value|
   cudaStream_t s = nullptr, c1 = nullptr, c2 = nullptr;
   cudaEvent_t ev_compute = nullptr, ev_c1 = nullptr, ev_s = nullptr, ev_c2 = nullptr,
-              ev_host = nullptr;
+              ev_c2_done = nullptr, ev_host = nullptr;
   size_t send_off = 0;         // elements staged since the last flush
-  // side streams that received work since the last wait(): only those are
+  // Which side streams received work since the last wait() (only those are
   // joined, so a wait() issued while the compute stream is being captured
-  // never touches a stream outside the capture
-  bool dirty_s = false, dirty_c1 = false, dirty_c2 = false;
+  // never touches a stream outside the capture) and whether c2 still reads a
+  // receive buffer: the state of the edge planner in comm_order.h.
+  sgb::order::State order;
+  int result_stream = sgb::order::kStreamS;   // where the last call's result can be consumed
+  // Per-phase device timing (off by default; never during stream capture):
+  // one event pair per phase on the stream that runs it, named like the
+  // reference's operations ("Dist_s_fusedSynch_allreduce", ...), measured
+  // from an origin event on the compute stream.
+  bool profiling = false;
+  cudaEvent_t prof_origin = nullptr;
+  struct Range {
+    std::string name;
+    cudaEvent_t start, end;
+  };
+  std::vector<Range> ranges;
+  size_t open_range = 0;
   // Staging is deferred: a stage call only records the tensors; the bytes are
   // gathered by ONE multi-tensor pack launch when the bucket is flushed (the
   // tensors must stay alive until then anyway - the flush writes into them).
@@ -93,36 +112,81 @@ int edge(cudaEvent_t ev, cudaStream_t from, cudaStream_t to) {
   return SGB_OK;
 }
 
-// Ordering rules around every collective (stream s):
-//   before: s waits for the staging stream c1 and, if it carries work, for the
-//           post-processing stream c2 - so the send buffer is complete and the
-//           previous consumer of the receive buffer is done;
-//   after:  c1 (and c2 when it will post-process) wait for the collective - so
-//           nothing refills a send buffer that NCCL is still reading.
-int before_collective(sgb_comm* c, cudaStream_t compute) {
-  if (!c->dirty_c1)  // c1 idle since the last wait(): order it after the compute stream first
-    OK(edge(c->ev_compute, compute, c->c1));
-  c->dirty_c1 = true;
-  OK(edge(c->ev_c1, c->c1, c->s));
-  if (c->dirty_c2) OK(edge(c->ev_c2, c->c2, c->s));
-  c->dirty_s = true;
-  return SGB_OK;
+cudaStream_t side(const sgb_comm* c, int which) {
+  return which == sgb::order::kStreamS ? c->s : (which == sgb::order::kStreamC1 ? c->c1 : c->c2);
 }
 
-int after_collective(sgb_comm* c, bool c2_too) {
-  CU(cudaEventRecord(c->ev_s, c->s));
-  CU(cudaStreamWaitEvent(c->c1, c->ev_s, 0));
-  if (c2_too) {
-    CU(cudaStreamWaitEvent(c->c2, c->ev_s, 0));
-    c->dirty_c2 = true;
+// Emits the edges of one phase of a planned call (see comm_order.h), in a
+// fixed order.  Every edge re-records its event; a wait takes the state of the
+// event at the time of the wait, so an event can serve many edges in a row.
+int emit(sgb_comm* c, unsigned edges, cudaStream_t compute) {
+  using namespace sgb::order;
+  if (edges & kComputeToC1) OK(edge(c->ev_compute, compute, c->c1));
+  if (edges & kComputeToS) OK(edge(c->ev_compute, compute, c->s));
+  if (edges & kC1ToS) OK(edge(c->ev_c1, c->c1, c->s));
+  if (edges & kC2DoneToS) CU(cudaStreamWaitEvent(c->s, c->ev_c2_done, 0));
+  if (edges & (kSToC1 | kSToC2)) {
+    CU(cudaEventRecord(c->ev_s, c->s));
+    if (edges & kSToC1) CU(cudaStreamWaitEvent(c->c1, c->ev_s, 0));
+    if (edges & kSToC2) CU(cudaStreamWaitEvent(c->c2, c->ev_s, 0));
   }
+  if (edges & kMarkC2Done) CU(cudaEventRecord(c->ev_c2_done, c->c2));
+  if (edges & kSToCompute) OK(edge(c->ev_s, c->s, compute));
+  if (edges & kC1ToCompute) OK(edge(c->ev_c1, c->c1, compute));
+  if (edges & kC2ToCompute) OK(edge(c->ev_c2, c->c2, compute));
   return SGB_OK;
 }
 
-int pack_pending(sgb_comm* c, cudaStream_t compute) {
+sgb::order::Step plan_call(sgb_comm* c, int call) {
+  sgb::order::Step p = sgb::order::plan(c->order, call);
+  c->result_stream = p.result_stream;
+  return p;
+}
+
+// A named phase on one of the side streams: an NVTX range around the enqueue
+// and, while profiling is on, an event pair on that stream.
+struct Phase {
+  sgb_comm* c;
+  cudaStream_t stream;
+  bool timed = false;
+  size_t slot = 0;
+  Phase(sgb_comm* comm, const char* name, int which) : c(comm), stream(side(comm, which)) {
+    nvtxRangePushA(name);
+    if (!c->profiling) return;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return;
+    sgb_comm::Range r;
+    r.name = name;
+    if (cudaEventCreate(&r.start) != cudaSuccess) return;
+    if (cudaEventCreate(&r.end) != cudaSuccess) {
+      cudaEventDestroy(r.start);
+      return;
+    }
+    cudaEventRecord(r.start, stream);
+    slot = c->ranges.size();
+    c->ranges.push_back(r);
+    timed = true;
+  }
+  ~Phase() {
+    if (timed) cudaEventRecord(c->ranges[slot].end, stream);
+    nvtxRangePop();
+  }
+};
+
+void drop_ranges(sgb_comm* c) {
+  for (auto& r : c->ranges) {
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.end);
+  }
+  c->ranges.clear();
+}
+
+// Packs the deferred tensors into the staging buffer on c1.  The caller has
+// emitted compute -> c1 for this call already (every staged gradient was
+// produced before this point).
+int pack_pending(sgb_comm* c, const char* name) {
   if (c->pend_ptrs.empty()) return SGB_OK;
-  OK(edge(c->ev_compute, compute, c->c1));   // every staged gradient was produced before this point
-  c->dirty_c1 = true;
+  Phase ph(c, name, sgb::order::kStreamC1);
   if (c->pend_half)
     OK(sgb_pack_f32_to_f16(c->pend_ptrs.data(), c->pend_sizes.data(), c->pend_ptrs.size(), c->send_h,
                            c->pend_off, c->c1));
@@ -132,6 +196,13 @@ int pack_pending(sgb_comm* c, cudaStream_t compute) {
   c->pend_ptrs.clear();
   c->pend_sizes.clear();
   return SGB_OK;
+}
+
+// A bucket of the other precision is still pending: it is packed now, ordered
+// after the compute stream.
+int pack_other_kind(sgb_comm* c, cudaStream_t compute, const char* name) {
+  OK(emit(c, plan_call(c, sgb::order::kStageCopy).pre, compute));
+  return pack_pending(c, name);
 }
 
 void defer(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count, int half) {
@@ -220,7 +291,7 @@ int sgb_comm_create(sgb_comm** out, int rank, int world, const void* unique_id, 
   CU(cudaStreamCreateWithPriority(&c->s, cudaStreamNonBlocking, prio_hi));
   CU(cudaStreamCreateWithPriority(&c->c1, cudaStreamNonBlocking, prio_hi));
   CU(cudaStreamCreateWithPriority(&c->c2, cudaStreamNonBlocking, prio_hi));
-  cudaEvent_t* evs[] = {&c->ev_compute, &c->ev_c1, &c->ev_s, &c->ev_c2};
+  cudaEvent_t* evs[] = {&c->ev_compute, &c->ev_c1, &c->ev_s, &c->ev_c2, &c->ev_c2_done};
   for (cudaEvent_t* e : evs) CU(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
   CU(cudaEventCreateWithFlags(&c->ev_host, cudaEventDisableTiming | cudaEventBlockingSync));
   return SGB_OK;
@@ -237,7 +308,8 @@ int sgb_comm_destroy(sgb_comm* c) {
   for (void* b : bufs)
     if (b) cudaFree(b);
   if (c->nnz_host) cudaFreeHost(c->nnz_host);
-  cudaEvent_t evs[] = {c->ev_compute, c->ev_c1, c->ev_s, c->ev_c2, c->ev_host};
+  drop_ranges(c);
+  cudaEvent_t evs[] = {c->ev_compute, c->ev_c1, c->ev_s, c->ev_c2, c->ev_c2_done, c->ev_host, c->prof_origin};
   for (cudaEvent_t e : evs)
     if (e) cudaEventDestroy(e);
   cudaStream_t ss[] = {c->s, c->c1, c->c2};
@@ -267,11 +339,75 @@ void* sgb_comm_stream(const sgb_comm* c, int which) {
 
 int sgb_comm_wait(sgb_comm* c, void* compute_stream) {
   if (!c) return SGB_ERR_NULL;
-  cudaStream_t cs = sgb::as_stream(compute_stream);
-  if (c->dirty_s) OK(edge(c->ev_s, c->s, cs));
-  if (c->dirty_c1) OK(edge(c->ev_c1, c->c1, cs));
-  if (c->dirty_c2) OK(edge(c->ev_c2, c->c2, cs));
-  c->dirty_s = c->dirty_c1 = c->dirty_c2 = false;
+  return emit(c, plan_call(c, sgb::order::kWait).before, sgb::as_stream(compute_stream));
+}
+
+void* sgb_comm_result_stream(const sgb_comm* c) { return c ? side(c, c->result_stream) : nullptr; }
+
+int sgb_comm_order_plan(unsigned char* state, int call, unsigned* edges, int* result_stream) {
+  if (!state || !edges) return SGB_ERR_NULL;
+  if (call < sgb::order::kSynch || call > sgb::order::kWait) return SGB_ERR_UNSUPPORTED;
+  sgb::order::State st;
+  st.dirty_s = state[0];
+  st.dirty_c1 = state[1];
+  st.dirty_c2 = state[2];
+  st.c2_reads_recv = state[3];
+  const sgb::order::Step p = sgb::order::plan(st, call);
+  state[0] = st.dirty_s;
+  state[1] = st.dirty_c1;
+  state[2] = st.dirty_c2;
+  state[3] = st.c2_reads_recv;
+  edges[0] = p.pre;
+  edges[1] = p.before;
+  edges[2] = p.after;
+  edges[3] = p.post;
+  if (result_stream) *result_stream = p.result_stream;
+  return SGB_OK;
+}
+
+int sgb_comm_profile_begin(sgb_comm* c, void* compute_stream) {
+  if (!c) return SGB_ERR_NULL;
+  drop_ranges(c);
+  if (!c->prof_origin) CU(cudaEventCreate(&c->prof_origin));
+  CU(cudaEventRecord(c->prof_origin, sgb::as_stream(compute_stream)));
+  c->profiling = true;
+  return SGB_OK;
+}
+
+int sgb_comm_profile_range(sgb_comm* c, const char* name, int which, int begin) {
+  if (!c || !name) return SGB_ERR_NULL;
+  if (which < 0 || which > 2) return SGB_ERR_UNSUPPORTED;
+  if (!c->profiling) return SGB_OK;
+  if (begin) {
+    sgb_comm::Range r;
+    r.name = name;
+    CU(cudaEventCreate(&r.start));
+    CU(cudaEventCreate(&r.end));
+    CU(cudaEventRecord(r.start, side(c, which)));
+    c->open_range = c->ranges.size();
+    c->ranges.push_back(r);
+  } else if (c->open_range < c->ranges.size()) {
+    CU(cudaEventRecord(c->ranges[c->open_range].end, side(c, which)));
+  }
+  return SGB_OK;
+}
+
+int sgb_comm_profile_end(sgb_comm* c, char* names, size_t name_stride, float* start_ms, float* end_ms,
+                         size_t capacity, size_t* count) {
+  if (!c || !count) return SGB_ERR_NULL;
+  c->profiling = false;
+  CU(cudaDeviceSynchronize());
+  *count = c->ranges.size();
+  for (size_t i = 0; i < c->ranges.size() && i < capacity; ++i) {
+    const sgb_comm::Range& r = c->ranges[i];
+    if (names && name_stride) {
+      std::strncpy(names + i * name_stride, r.name.c_str(), name_stride - 1);
+      names[i * name_stride + name_stride - 1] = 0;
+    }
+    if (start_ms) CU(cudaEventElapsedTime(start_ms + i, c->prof_origin, r.start));
+    if (end_ms) CU(cudaEventElapsedTime(end_ms + i, c->prof_origin, r.end));
+  }
+  drop_ranges(c);
   return SGB_OK;
 }
 
@@ -280,26 +416,31 @@ int sgb_comm_synch(sgb_comm* c, void* data, size_t n, int is_half, void* compute
   if (n == 0) return SGB_OK;
   if (!data) return SGB_ERR_NULL;
   if (n > 0x7fffffffu) return SGB_ERR_SIZE;
-  c->dirty_s = true;
-  OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->s));
-  NC(ncclAllReduce(data, data, n, is_half ? ncclHalf : ncclFloat, ncclSum, c->nccl, c->s));
-  return SGB_OK;
+  const sgb::order::Step p = plan_call(c, sgb::order::kSynch);
+  OK(emit(c, p.before, sgb::as_stream(compute_stream)));
+  {
+    Phase ph(c, "Dist_s_synch_allreduce", sgb::order::kStreamS);
+    NC(ncclAllReduce(data, data, n, is_half ? ncclHalf : ncclFloat, ncclSum, c->nccl, c->s));
+  }
+  return emit(c, p.after, nullptr);
 }
 
 int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
                          int is_half, int send, void* compute_stream) {
   if (!c) return SGB_ERR_NULL;
   OK(check_list(tensors, sizes, count));
+  cudaStream_t compute = sgb::as_stream(compute_stream);
   const size_t esz = is_half ? sizeof(__half) : sizeof(float);
   if (!send) {
     const size_t total = total_of(sizes, count);
     if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
     if (!is_half) {
-      if (!c->pend_ptrs.empty() && c->pend_half) OK(pack_pending(c, sgb::as_stream(compute_stream)));
+      if (!c->pend_ptrs.empty() && c->pend_half)
+        OK(pack_other_kind(c, compute, "Dist_c1_fusedSynchHalf_filling"));
       defer(c, tensors, sizes, count, 0);
     } else {
-      c->dirty_c1 = true;
-      OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
+      OK(emit(c, plan_call(c, sgb::order::kStageCopy).pre, compute));
+      Phase ph(c, "Dist_c1_fusedSynch_filling", sgb::order::kStreamC1);
       size_t off = c->send_off;
       for (size_t i = 0; i < count; ++i) {
         CU(cudaMemcpyAsync(reinterpret_cast<char*>(c->send) + off * esz, tensors[i],
@@ -314,7 +455,8 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
   const size_t total = total_of(sizes, count);
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
   // Gradients that already sit back to back in memory (a gradient arena) need
-  // neither the pack nor the unpack pass: the bucket is reduced in place.
+  // neither the pack nor the unpack pass: the bucket is reduced in place, on s,
+  // ordered directly after the compute stream that produced it.
   if (!is_half && !c->pend_half && c->pend_off == 0 && c->pend_ptrs.size() == count &&
       c->send_off == total) {
     bool in_place = true;
@@ -327,19 +469,27 @@ int sgb_comm_fused_synch(sgb_comm* c, void* const* tensors, const size_t* sizes,
       c->pend_ptrs.clear();
       c->pend_sizes.clear();
       c->send_off = 0;
-      OK(before_collective(c, sgb::as_stream(compute_stream)));
-      NC(ncclAllReduce(tensors[0], tensors[0], total, ncclFloat, ncclSum, c->nccl, c->s));
-      OK(after_collective(c, false));
-      return SGB_OK;
+      const sgb::order::Step p = plan_call(c, sgb::order::kFlushInPlace);
+      OK(emit(c, p.before, compute));
+      {
+        Phase ph(c, "Dist_s_fusedSynch_allreduce", sgb::order::kStreamS);
+        NC(ncclAllReduce(tensors[0], tensors[0], total, ncclFloat, ncclSum, c->nccl, c->s));
+      }
+      return emit(c, p.after, nullptr);
     }
   }
-  OK(pack_pending(c, sgb::as_stream(compute_stream)));
-  OK(before_collective(c, sgb::as_stream(compute_stream)));
-  if (c->send_off)
+  const sgb::order::Step p = plan_call(c, sgb::order::kFlushPacked);
+  OK(emit(c, p.pre, compute));
+  OK(pack_pending(c, "Dist_c1_fusedSynch_filling"));
+  OK(emit(c, p.before, compute));
+  if (c->send_off) {
+    Phase ph(c, "Dist_s_fusedSynch_allreduce", sgb::order::kStreamS);
     NC(ncclAllReduce(c->send, c->recv, c->send_off, is_half ? ncclHalf : ncclFloat, ncclSum,
                      c->nccl, c->s));
+  }
   c->send_off = 0;
-  OK(after_collective(c, false));
+  OK(emit(c, p.after, nullptr));
+  Phase ph(c, "Dist_c1_fusedSynch_copyBackToTensor", sgb::order::kStreamC1);
   if (!is_half) {
     OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c1));
   } else {
@@ -359,14 +509,24 @@ int sgb_comm_synch_half(sgb_comm* c, float* data, size_t n, void* compute_stream
   if (!data) return SGB_ERR_NULL;
   if (n > c->max_elems) return SGB_ERR_CAPACITY;
   OK(half_init(c));
-  OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
-  c->dirty_c1 = true;
-  OK(sgb_cast_f32_f16(data, c->dsend_h, n, c->c1));
-  OK(before_collective(c, sgb::as_stream(compute_stream)));
-  NC(ncclAllReduce(c->dsend_h, c->drecv_h, n, ncclHalf, ncclSum, c->nccl, c->s));
-  OK(after_collective(c, true));
-  OK(sgb_cast_f16_f32(c->drecv_h, data, n, c->c2));
-  return SGB_OK;
+  cudaStream_t compute = sgb::as_stream(compute_stream);
+  const sgb::order::Step p = plan_call(c, sgb::order::kSynchHalf);
+  OK(emit(c, p.pre, compute));
+  {
+    Phase ph(c, "Dist_c1_synchHalf_float2half", sgb::order::kStreamC1);
+    OK(sgb_cast_f32_f16(data, c->dsend_h, n, c->c1));
+  }
+  OK(emit(c, p.before, compute));
+  {
+    Phase ph(c, "Dist_s_synchHalf_allreduce", sgb::order::kStreamS);
+    NC(ncclAllReduce(c->dsend_h, c->drecv_h, n, ncclHalf, ncclSum, c->nccl, c->s));
+  }
+  OK(emit(c, p.after, nullptr));
+  {
+    Phase ph(c, "Dist_c2_synchHalf_half2float", sgb::order::kStreamC2);
+    OK(sgb_cast_f16_f32(c->drecv_h, data, n, c->c2));
+  }
+  return emit(c, p.post, nullptr);
 }
 
 int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* sizes,
@@ -374,24 +534,33 @@ int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* s
   if (!c) return SGB_ERR_NULL;
   OK(check_list(tensors, sizes, count));
   OK(half_init(c));
+  cudaStream_t compute = sgb::as_stream(compute_stream);
   const size_t total = total_of(sizes, count);
   if (!send) {
     if (c->send_off + total > c->max_elems) return SGB_ERR_CAPACITY;
     // copy + float2half of the reference collapse into one pack-and-cast pass at flush time
-    if (!c->pend_ptrs.empty() && !c->pend_half) OK(pack_pending(c, sgb::as_stream(compute_stream)));
+    if (!c->pend_ptrs.empty() && !c->pend_half)
+      OK(pack_other_kind(c, compute, "Dist_c1_fusedSynch_filling"));
     defer(c, tensors, sizes, count, 1);
     c->send_off += total;
     return SGB_OK;
   }
   if (total > c->max_elems) return SGB_ERR_CAPACITY;
-  OK(pack_pending(c, sgb::as_stream(compute_stream)));
-  OK(before_collective(c, sgb::as_stream(compute_stream)));
-  if (c->send_off)
+  const sgb::order::Step p = plan_call(c, sgb::order::kFlushHalf);
+  OK(emit(c, p.pre, compute));
+  OK(pack_pending(c, "Dist_c1_fusedSynchHalf_float2half"));
+  OK(emit(c, p.before, compute));
+  if (c->send_off) {
+    Phase ph(c, "Dist_s_fusedSynchHalf_allreduce", sgb::order::kStreamS);
     NC(ncclAllReduce(c->send_h, c->recv_h, c->send_off, ncclHalf, ncclSum, c->nccl, c->s));
+  }
   c->send_off = 0;
-  OK(after_collective(c, true));
-  OK(sgb_unpack_f16_to_f32(c->recv_h, 0, tensors, sizes, count, 1.0f, c->c2));
-  return SGB_OK;
+  OK(emit(c, p.after, nullptr));
+  {
+    Phase ph(c, "Dist_c2_fusedSynchHalf_half2floatcopy", sgb::order::kStreamC2);
+    OK(sgb_unpack_f16_to_f32(c->recv_h, 0, tensors, sizes, count, 1.0f, c->c2));
+  }
+  return emit(c, p.post, nullptr);
 }
 
 int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
@@ -403,8 +572,9 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   if (n == 0) return SGB_OK;
   OK(sparse_init(c));
   const int W = c->world;
-  OK(edge(c->ev_compute, sgb::as_stream(compute_stream), c->c1));
-  c->dirty_c1 = true;
+  const char* op_name = count > 1 ? "Dist_c1c2_fusedSparsification" : "Dist_c1c2_sparsification";
+  const sgb::order::Step p = plan_call(c, sgb::order::kSparse);
+  OK(emit(c, p.pre, sgb::as_stream(compute_stream)));
   // One tensor, or tensors that lie back to back in memory (a gradient arena),
   // are selected from and scattered into IN PLACE: no copy into the send
   // buffer and none back (16 B/element saved).  The selection has finished
@@ -414,9 +584,11 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
     in_place = static_cast<const float*>(tensors[i]) == static_cast<const float*>(tensors[i - 1]) + sizes[i - 1];
   float* grad = in_place ? static_cast<float*>(tensors[0]) : c->send;
   float* dense = in_place ? static_cast<float*>(tensors[0]) : c->recv;
-  if (!in_place) OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
 
   size_t nnz_max = 0;
+  auto select = [&]() -> int {
+  Phase ph(c, op_name, sgb::order::kStreamC1);
+  if (!in_place) OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
   if (!topk) {
     OK(sgb::sparse_threshold_count(grad, accumulation, n, spars, c->nnz_dev, c->ws,
                                    c->ws_bytes, c->c1));
@@ -438,11 +610,18 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
                              reinterpret_cast<float*>(c->pay_send) + nnz_max, c->ws, c->ws_bytes,
                              c->c1));
   }
+  return SGB_OK;
+  };
+  OK(select());
 
-  OK(before_collective(c, sgb::as_stream(compute_stream)));
-  if (nnz_max)
+  OK(emit(c, p.before, sgb::as_stream(compute_stream)));
+  if (nnz_max) {
+    Phase ph(c, "Dist_s_sparsification_allgather", sgb::order::kStreamS);
     NC(ncclAllGather(c->pay_send, c->pay_recv, 2 * nnz_max, ncclFloat, c->nccl, c->s));
-  OK(after_collective(c, true));
+  }
+  OK(emit(c, p.after, nullptr));
+  auto scatter = [&]() -> int {
+  Phase ph(c, op_name, sgb::order::kStreamC2);
   CU(cudaMemsetAsync(dense, 0, n * sizeof(float), c->c2));
   for (int r = 0; r < W && nnz_max; ++r) {  // ranks in ascending order, as the reference
     const int* seg = c->pay_recv + static_cast<size_t>(r) * 2 * nnz_max;
@@ -452,6 +631,9 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   }
   if (!in_place) OK(sgb_unpack_f32(c->recv, 0, tensors, sizes, count, 1.0f, c->c2));
   return SGB_OK;
+  };
+  OK(scatter());
+  return emit(c, p.post, nullptr);
 }
 
 }  // extern "C"

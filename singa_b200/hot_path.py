@@ -70,8 +70,22 @@ class HotPathGPU(object):
             cnt = numel(T["d:" + n].shape)
             arena_view["d:" + n] = self.grad_arena[off:off + cnt].view(T["d:" + n].shape)
             off += cnt
+        self.t["grad_arena"] = self.grad_arena
+        # pristine stand-ins of the contractions' weight gradients, back to back in
+        # refresh order (one flat buffer: a refresh is one multi-tensor copy)
+        wsyn = [n for n, spec in T.items() if spec.kind == "wsyn"]
+        self.wsyn_flat = torch.empty(sum(numel(T[n].shape) for n in wsyn), device=dev)
+        self.wsyn_off, off = {}, 0
+        for n in wsyn:
+            cnt = numel(T[n].shape)
+            self.wsyn_off[n] = off
+            self.t[n] = self.wsyn_flat[off:off + cnt].view(T[n].shape)
+            self.t[n].copy_(randn(T[n].shape, 1e-3))
+            off += cnt
         for name, spec in T.items():
             k = spec.kind
+            if k == "wsyn":
+                continue
             if k == "pgrad" and name in arena_view:
                 self.t[name] = arena_view[name]
                 self.t[name].copy_(randn(spec.shape, 1e-3))
@@ -122,7 +136,7 @@ class HotPathGPU(object):
 
     def host_copy(self):
         """numpy copies of every tensor + moments (inputs for the CPU checker)."""
-        out = {k: v.detach().cpu().numpy().copy() for k, v in self.t.items()}
+        out = {k: v.detach().cpu().numpy().copy() for k, v in self.t.items() if k != "grad_arena"}
         out.update({"m:" + k: v.detach().cpu().numpy().copy() for k, v in self.moments.items()})
         return out
 
@@ -216,6 +230,18 @@ class HotPathGPU(object):
                 assert L.sgb_conv_bias_backward_workspace_bytes(n, c, hw) <= ws.numel()
                 self.calls.append(("sgb_conv_bias_backward_f32",
                                    (p(a["dy"]), p(a["db"]), n, c, hw, ws.data_ptr(), ws.numel(), S)))
+            elif k == "wgrad_refresh":
+                # consecutive stand-ins are one run of the flat buffer
+                names = ["wsyn:" + q for q in a["params"]]
+                for i in range(1, len(names)):
+                    assert self.wsyn_off[names[i]] == self.wsyn_off[names[i - 1]] + t[names[i - 1]].numel()
+                ptrs, sizes, n = _table([t["d:" + q] for q in a["params"]])
+                self._keep = getattr(self, "_keep", []) + [ptrs, sizes]
+                self.calls.append(("sgb_unpack_f32", (self.wsyn_flat.data_ptr(), self.wsyn_off[names[0]], ptrs, sizes,
+                                                      n, 1.0, S)))
+            elif k == "fill":
+                x = t[a["x"]]
+                self.calls.append(("sgb_set_f32", (float(a["value"]), x.data_ptr(), x.numel(), S)))
             elif k == "grad_ready":
                 self.calls.append(("grad_ready", a["param"]))
             elif k == "sync_and_update":
@@ -266,10 +292,9 @@ class HotPathGPU(object):
                 g = self.grads[idx]
                 if half:
                     self._check("synch_half", L.sgb_comm_synch_half(c._h, g.data_ptr(), g.numel(), stream))
-                    self._sgd_bucket(idx, 2)          # result lands on c2
                 else:
                     self._check("synch", L.sgb_comm_synch(c._h, g.data_ptr(), g.numel(), 0, stream))
-                    self._sgd_bucket(idx, 0)          # in place on the NCCL stream
+                self._sgd_bucket(idx)
                 return 1
             ptrs, sizes, n = self.single_tables[idx]
             if half:
@@ -281,10 +306,9 @@ class HotPathGPU(object):
                 ptrs, sizes, n = self.fused_tables[idx]
                 if half:
                     self._check("flush_half", L.sgb_comm_fused_synch_half(c._h, ptrs, sizes, n, 1, stream))
-                    self._sgd_bucket(idx, 2)
                 else:
                     self._check("flush", L.sgb_comm_fused_synch(c._h, ptrs, sizes, n, 0, 1, stream))
-                    self._sgd_bucket(idx, 1)          # unpacked on c1
+                self._sgd_bucket(idx)
                 n_calls += 2
             return n_calls
         # sparse options: nothing is staged, the whole bucket is handed over at flush time
@@ -296,15 +320,21 @@ class HotPathGPU(object):
             c._h, ptrs, sizes, n, self.residuals[idx].data_ptr(), float(self.spars), int(topk), stream))
         return 1
 
-    def _sgd_bucket(self, idx, which_stream):
+    def _sgd_bucket(self, idx):
+        """The bucket's parameters are updated on the side stream on which its
+        reduced gradients land (never on the NCCL stream: the next bucket's
+        all-reduce does not wait for this update)."""
         if not self.update_on_arrival:
             return
-        L = self.lib
-        side = L.sgb_comm_stream(self.comm._h, which_stream)
+        L, h = self.lib, self.comm._h
+        side = L.sgb_comm_result_stream(h)
+        which = [L.sgb_comm_stream(h, w) for w in (0, 1, 2)].index(side)
         pp, gp, mp, sizes, n = self.bucket_sgd[idx]
         scale = float(np.float32(1.0) / np.float32(self.world))
+        L.sgb_comm_profile_range(h, b"sgd_update_bucket", which, 1)
         self._check("sgd", L.sgb_sgd_update_multi_f32(pp, gp, mp, sizes, n, self.lr, self.momentum, 0.0,
                                                        self.weight_decay, 0, scale, side))
+        L.sgb_comm_profile_range(h, b"sgd_update_bucket", which, 0)
 
     def run_step(self):
         """Enqueues one full step on the current stream (+ the communicator's

@@ -266,17 +266,19 @@ def fuse_plan(plan, join_bn=False):
     producer = {}
     for i, op in enumerate(ops):
         k, a = op.kind, op.args
-        if k == "relu_bwd" and a["dy"] in producer and ops[producer[a["dy"]]].kind == "add_out" \
-                and readers.get(a["dy"]) == [i]:
+        if k == "relu_bwd" and a["dy"] in producer and out[producer[a["dy"]]].kind == "add_out" \
+                and producer[a["dy"]] not in dead and readers.get(a["dy"]) == [i]:
             j = producer[a["dy"]]
-            src = ops[j].args
+            src = out[j].args
             dead.add(j)
             T.pop(a["dy"], None)
             op = Op("add_relu_bwd", dict(dy_a=src["a"], dy_b=src["b"], x=a["x"], dx=a["dx"]))
-        elif k == "bn_bwd" and a["dy"] in producer and ops[producer[a["dy"]]].kind == "relu_bwd" \
-                and readers.get(a["dy"]) == [i]:
+        elif k == "bn_bwd" and a["dy"] in producer and out[producer[a["dy"]]].kind == "relu_bwd" \
+                and producer[a["dy"]] not in dead and readers.get(a["dy"]) == [i]:
+            # keyed on the op as already rewritten: a relu_bwd that absorbed a join is an
+            # add_relu_bwd by now and is left alone here (join_bn handles that pair)
             j = producer[a["dy"]]
-            src = ops[j].args
+            src = out[j].args
             dead.add(j)
             T.pop(a["dy"], None)
             op = Op("bn_relu_bwd", dict(a, dy=src["dy"], relu_x=src["x"]))
@@ -288,9 +290,10 @@ def fuse_plan(plan, join_bn=False):
             rest = {key: v for key, v in a.items() if key != "dy"}
             op = Op("bn_add_relu_bwd", dict(rest, dy_a=src["dy_a"], dy_b=src["dy_b"], relu_x=src["x"],
                                             joined=a["dy"]))
-        elif k == "scale" and a["x"] in producer and ops[producer[a["x"]]].kind == "ce_bwd":
+        elif k == "scale" and a["x"] in producer and out[producer[a["x"]]].kind == "ce_bwd" \
+                and producer[a["x"]] not in dead:
             j = producer[a["x"]]
-            src = ops[j].args
+            src = out[j].args
             dead.add(j)
             op = Op("ce_grad", dict(p=src["p"], t=src["t"], scale=a["c"], grad=a["x"]))
         out.append(op)
@@ -327,6 +330,43 @@ def _fuse_loss_head(ops):
                                       scale=ops[grd].args["scale"]))
         return ops[:i] + [fused] + [o for j, o in enumerate(ops[i + 1:], i + 1) if j not in (fwd, grd)]
     return ops
+
+
+WRITES = {
+    "relu_bwd": ("dx",), "add_relu_bwd": ("dx",), "add_out": ("out",),
+    "bn_bwd": ("dx", "dscale", "dbias"), "bn_relu_bwd": ("dx", "dscale", "dbias"),
+    "bn_add_relu_bwd": ("joined", "dx", "dscale", "dbias"), "maxpool_bwd": ("dx",), "avgpool_bwd": ("dx",),
+    "softmax": ("y",), "ce_fwd": ("loss",), "sum_all": ("out",), "ce_bwd": ("grad",), "ce_grad": ("grad",),
+    "scale": ("x",), "sum_rows": ("v",), "conv_bias_bwd": ("db",), "softmax_ce": ("y", "loss", "grad"),
+}
+
+
+def add_wgrad_refresh(plan, where="start"):
+    """Rewrites, every step, the parameter gradients that no op of the path
+    produces (the weight gradients of the Conv/Linear contractions) from
+    pristine stand-in copies "wsyn:<param>".  This stands for the write the
+    contraction's backward-filter call performs in the reference; without it a
+    stand-in gradient that is all-reduced in place would be multiplied by the
+    world size on every step.  where="start": one multi-tensor copy at the
+    beginning of the step; where="each": one copy right before each such
+    gradient is reported ready (the position of the contraction)."""
+    written = set()
+    for op in plan["ops"]:
+        for key in WRITES.get(op.kind, ()):
+            written.add(op.args[key])
+    stand = [p for p in plan["grad_order"] if "d:" + p not in written]
+    T = dict(plan["tensors"])
+    for p in stand:
+        T["wsyn:" + p] = Tensor("wsyn:" + p, T["d:" + p].shape, "wsyn")
+    if where == "start":
+        ops = [Op("wgrad_refresh", dict(params=tuple(stand)))] + list(plan["ops"])
+    else:
+        ops, todo = [], set(stand)
+        for op in plan["ops"]:
+            if op.kind == "grad_ready" and op.args["param"] in todo:
+                ops.append(Op("wgrad_refresh", dict(params=(op.args["param"],))))
+            ops.append(op)
+    return dict(plan, ops=ops, tensors=T)
 
 
 def numel(shape):
@@ -380,6 +420,8 @@ def algorithmic_bytes(plan, world=1, pool_argmax=False):
             add("softmax_ce", 8 * numel(T[a["x"]].shape))
         elif op.kind == "sum_rows":
             add("bias_grad", 4 * numel(T[a["M"]].shape))
+        elif op.kind == "wgrad_refresh":                         # read the stand-in, write the gradient
+            add("wgrad_standin", 8 * sum(numel(T["d:" + p].shape) for p in a["params"]))
     nparam = sum(numel(T[p].shape) for p in plan["params"])
     add("sgd", 20 * nparam)
     return out, nparam

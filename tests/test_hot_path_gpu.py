@@ -136,3 +136,98 @@ def test_step_with_communicator_graph_and_update_on_arrival(dist_option):
         gc.collect()
         torch.cuda.synchronize()
         comm.close()
+
+
+@pytest.mark.parametrize("dist_option", ["plain", "half"])
+def test_buckets_wait_for_the_kernels_that_produce_their_gradients(dist_option):
+    """Every bucket's collective (and the update enqueued behind it on a side
+    stream) must be ordered after the compute-stream kernels that wrote that
+    bucket's gradients IN THIS STEP - for every bucket, not only the first.
+    The step is built so that a missing edge cannot go unnoticed: the whole
+    gradient arena is overwritten with a huge sentinel by the first kernel of
+    the step, a slow elementwise kernel sits in front of every batch-norm
+    backward call, and each stand-in weight gradient is written right before
+    it is reported ready.  A collective or update that ran early would consume
+    the sentinel.  Captured once, replayed with fresh labels each time;
+    parameters must equal the oracle executor's after every replay."""
+    from oracle.path import OraclePath
+    from singa_b200.communicator import Communicator, NcclIdHolder
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import Op, Tensor, add_wgrad_refresh, build_plan, fuse_plan
+    plan = fuse_plan(build_plan(batch=2, image=64, num_classes=10, blocks=(1, 1, 1, 1)))
+    plan = add_wgrad_refresh(plan, where="each")
+    T = dict(plan["tensors"])
+    big = (64 * 1024 * 1024,)                                    # 256 MB per operand: ~0.1 ms per delay kernel
+    for n in ("delay.a", "delay.b", "delay.out"):
+        T[n] = Tensor(n, big, "grad")
+    ops = [Op("fill", dict(x="grad_arena", value=3.0e30))]
+    for op in plan["ops"]:
+        if op.kind in ("bn_bwd", "bn_relu_bwd"):
+            ops.append(Op("add_out", dict(a="delay.a", b="delay.b", out="delay.out")))
+        ops.append(op)
+    plan = dict(plan, ops=ops, tensors=T)
+    comm = Communicator(torch.cuda.current_device(), 1, NcclIdHolder(), buffSize=4194304)
+    try:
+        gpu = HotPathGPU(plan, communicator=comm, world=1, seed=11, dist_option=dist_option, threshold=2000)
+        assert gpu.update_on_arrival
+        assert sum(1 for k, _ in gpu.events if k == "fused") >= 4 and len(gpu.events) >= 20
+        host = gpu.host_copy()
+        for n in ("delay.a", "delay.b", "delay.out"):
+            host.pop(n)                                          # the checker has no use for the delay operands
+        ref_plan = dict(plan, ops=[o for o in plan["ops"] if not (o.kind == "add_out" and o.args["a"] == "delay.a")])
+        ref = OraclePath(ref_plan, host, dist_option=dist_option)
+        tol = 2e-3 if dist_option == "half" else 1e-6
+        rng = np.random.default_rng(5)
+
+        def new_labels():
+            lab = rng.integers(0, 10, host["labels"].shape).astype(np.int32)
+            host["labels"][...] = lab
+            gpu.t["labels"].copy_(torch.from_numpy(lab))
+
+        def check(what):
+            torch.cuda.synchronize()
+            got = gpu.host_copy()
+            for p in plan["params"]:
+                assert np.isfinite(got[p]).all(), "%s: %s consumed the sentinel" % (what, p)
+                close(got[p], host[p], tol, "%s: param %s" % (what, p))
+
+        ref.run_step()
+        gpu.run_step()
+        check("eager step")
+        g = gpu.capture()
+        for k in range(3):
+            new_labels()
+            ref.run_step()
+            g.replay()
+            check("replay %d" % k)
+        gpu.release_graph()
+        del g
+    finally:
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        comm.close()
+
+
+def test_refreshed_stand_in_gradients_do_not_compound():
+    """The weight gradients of the contractions are rewritten from pristine
+    copies every step, so repeated steps update with the same finite values
+    (an in-place all-reduce would otherwise scale a never-rewritten gradient
+    by the world size on every step)."""
+    from oracle.path import OraclePath
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import add_wgrad_refresh, build_plan, fuse_plan
+    plan = add_wgrad_refresh(fuse_plan(build_plan(batch=2, image=64, num_classes=10, blocks=(1, 1, 1, 1))))
+    assert plan["ops"][0].kind == "wgrad_refresh" and len(plan["ops"][0].args["params"]) > 10
+    gpu = HotPathGPU(plan, communicator=None, world=1, seed=2)
+    host = gpu.host_copy()
+    ref = OraclePath(plan, host)
+    gpu.t["d:conv1.W"].fill_(7.0)                 # whatever the last step left is overwritten
+    for _ in range(2):
+        ref.run_step()
+        gpu.run_step()
+    torch.cuda.synchronize()
+    got = gpu.host_copy()
+    assert np.array_equal(got["d:conv1.W"], got["wsyn:conv1.W"])
+    for p in plan["params"]:
+        close(got[p], host[p], 1e-6, "param " + p)

@@ -103,3 +103,88 @@ def test_loss_head_is_not_fused_across_a_use_of_the_gradient():
     fused = fuse_plan(dict(plan, ops=ops[:i + 1] + [blocker] + ops[i + 1:]))
     kinds = [o.kind for o in fused["ops"]]
     assert "softmax_ce" not in kinds and "softmax" in kinds and "ce_grad" in kinds
+
+
+def test_join_relu_bn_chain_without_a_second_reader_keeps_every_read_produced():
+    """add_out(a, b -> t) ; relu_bwd(t, r -> m) ; bn_bwd(m): `m` has one reader,
+    so the first rule rewrites the ReLU into add_relu_bwd; the batch-norm rule
+    must then see the REWRITTEN producer and leave the pair alone (or fold it
+    through the join rule) - never read a tensor nothing produces."""
+    from singa_b200.resnet50_path import READS, WRITES, Op, Tensor
+    shape = (2, 8, 4, 4)
+    T = {n: Tensor(n, shape, "syn") for n in ("a", "b")}
+    T.update({n: Tensor(n, shape, "act") for n in ("r", "x")})
+    T.update({n: Tensor(n, shape, "grad") for n in ("t", "m", "dx")})
+    for n in ("scale", "mean", "invstd", "ds", "db"):
+        T[n] = Tensor(n, (8,), "stat")
+    ops = [Op("add_out", dict(a="a", b="b", out="t")),
+           Op("relu_bwd", dict(dy="t", x="r", dx="m")),
+           Op("bn_bwd", dict(dy="m", x="x", scale="scale", mean="mean", invstd="invstd", dx="dx",
+                             dscale="ds", dbias="db"))]
+    base = dict(tensors=T, ops=ops, params=[], grad_order=[], batch=2)
+    for join_bn in (False, True):
+        plan = fuse_plan(base, join_bn=join_bn)
+        produced = set()
+        for op in plan["ops"]:
+            for key in READS[op.kind]:
+                name = op.args[key]
+                assert name in plan["tensors"], (join_bn, op.kind, name)
+                assert name in produced or plan["tensors"][name].kind in ("syn", "act", "stat"), (op.kind, name)
+            produced.update(op.args[k] for k in WRITES[op.kind])
+        kinds = [o.kind for o in plan["ops"]]
+        assert kinds == (["bn_add_relu_bwd"] if join_bn else ["add_relu_bwd", "bn_bwd"]), kinds
+        assert "dx" in produced
+
+
+def test_every_collective_of_a_step_is_ordered_after_the_compute_stream():
+    """Replays the bucket events of the ResNet-50 step through the
+    communicator's edge planner (the same function the GPU code emits its
+    events from) for each synchronisation option: every collective must be
+    ordered after the compute stream AT ITS OWN CALL (directly, or through the
+    pre-processing stream), the next bucket's collective must not wait for
+    the stream that carries the previous bucket's update, and wait() must join
+    exactly the streams that received work."""
+    import ctypes as C
+
+    from singa_b200 import _lib
+    lib = _lib.lib()
+    plan = build_plan()
+    sizes = [numel(plan["tensors"]["d:" + n].shape) for n in plan["grad_order"]]
+    events = plan_buckets(sizes)
+    assert len(events) == 11
+    E = dict(compute_c1=1, compute_s=2, c1_s=4, c2done_s=8, s_c1=16, s_c2=32, s_compute=64, c1_compute=128,
+             c2_compute=256, mark_c2=512)
+
+    def call(state, kind):
+        edges, res = (C.c_uint * 4)(), C.c_int()
+        assert lib.sgb_comm_order_plan(state, kind, edges, C.byref(res)) == 0
+        return list(edges), res.value
+
+    for option, kinds in (("plain/arena", {"direct": 0, "fused": 1}), ("plain/packed", {"direct": 0, "fused": 2}),
+                          ("half", {"direct": 4, "fused": 3})):
+        state = (C.c_ubyte * 4)()
+        n_compute_edges = 0
+        for ev_kind, _ in events:
+            (pre, before, after, post), result = call(state, kinds[ev_kind])
+            direct = bool(before & E["compute_s"])
+            via_c1 = bool(pre & E["compute_c1"]) and bool(before & E["c1_s"])
+            assert direct or via_c1, (option, ev_kind)
+            n_compute_edges += 1
+            if option == "plain/arena":
+                assert before == E["compute_s"], "in-place buckets wait for the compute stream only"
+                assert result == 2 and after & E["s_c2"]
+            if option == "half":
+                assert result == 2 and after & E["s_c2"] and post & E["mark_c2"]
+        assert n_compute_edges == len(events)
+        (_, join, _, _), _ = call(state, 7)
+        want = E["s_compute"] | (E["c1_compute"] if option != "plain/arena" else 0) | \
+            (E["c2_compute"] if option != "plain/packed" else 0)
+        if option == "plain/packed":
+            want |= E["c2_compute"]       # the direct tensors' results are consumed on c2
+        assert join == want, (option, join, want)
+        assert list(state) == [0, 0, 0, 0]
+        (_, join, _, _), _ = call(state, 7)
+        assert join == 0                  # nothing to join after a wait
+    assert lib.sgb_comm_order_plan(None, 0, None, None) == -1
+    state, edges = (C.c_ubyte * 4)(), (C.c_uint * 4)()
+    assert lib.sgb_comm_order_plan(state, 8, edges, None) != 0
