@@ -91,14 +91,17 @@ class ClockSampler(object):
         return out
 
 
-def cpu_arm(steps, warmup, batch=CPU_SAMPLE_BATCH):
+def cpu_arm(steps, warmup, batch=CPU_SAMPLE_BATCH, threads=None):
     """The CPU statement of the hot path on a bounded sample: ResNet-50 at a
-    reduced batch, all host threads.  Returns (images/s, ms/step, cores)."""
+    reduced batch, on `threads` host threads (default: every core of the box,
+    whatever OMP_NUM_THREADS the launcher exported).  Returns (images/s,
+    ms/step, threads used)."""
     from oracle import build, cpu
     from oracle.path import OraclePath, make_tensors
-    from singa_b200.resnet50_path import build_plan
+    from singa_b200.resnet50_path import add_wgrad_refresh, build_plan
     build.build_oracle()
-    plan = build_plan(batch=batch, fused=False)
+    cpu.set_num_threads(threads or os.cpu_count() or 1)
+    plan = add_wgrad_refresh(build_plan(batch=batch, fused=False))
     tensors = make_tensors(plan, seed=0)
     ref = OraclePath(plan, tensors)
     for _ in range(warmup):
@@ -110,9 +113,21 @@ def cpu_arm(steps, warmup, batch=CPU_SAMPLE_BATCH):
     return batch / dt, dt * 1e3, cpu.num_threads()
 
 
+def workload_config(world, dist_option, fused, use_graph, pool_argmax, relu_mask=False):
+    """The `config` object shared by both arms (same keys, same values)."""
+    return {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
+            "global_batch": BATCH * world, "dist_option": dist_option,
+            "fusion": "bn+relu, join+relu, softmax+ce+grad" if fused else "none (one kernel per reference call)",
+            "cuda_graph": use_graph, "pool_argmax_record": bool(pool_argmax), "relu_bit_mask": bool(relu_mask),
+            "bucket_elems": 4194304, "threshold_elems": 2097152,
+            "excluded": "cuDNN/cuBLAS contractions (conv, linear): stand-in gradients, rewritten every step"}
+
+
 def reference_main(args, rank, world):
-    """The reference arm: the CPU statement of the path on the host cores.  Runs
-    exactly --steps steps after --warmup warm-up steps; the per-step sample (the
+    """The reference arm: the CPU statement of the path on the host cores of
+    ONE box (rank 0 alone runs; the value is that of one host and is not
+    multiplied by the number of GPUs).  Runs exactly --steps steps after
+    --warmup warm-up steps on every core of the box; the per-step sample (the
     batch fed to the CPU) is halved from 8 until the whole run fits in about
     three minutes, and the sample actually used is reported."""
     if rank != 0:
@@ -124,13 +139,15 @@ def reference_main(args, rank, world):
         batch //= 2
     v, ms, cores = cpu_arm(steps, warmup, batch)
     sample = "ResNet-50 hot path at batch %d (of %d) per step, fp32, %d OpenMP threads" % (batch, BATCH, cores)
+    config = workload_config(world, args.dist_option, not args.call_pattern, not args.no_graph, args.pool_argmax,
+                             args.relu_mask)
+    config.update({"sample_batch": batch, "device": "host CPU, one box (value not scaled by n_gpus)",
+                   "note": "CPU restatement (oracle port) of the reference path; the reference's own lang::Cpp "
+                           "backend has no BatchNorm/Pooling without DNNL"})
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": "images/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "resnet50_b32_224_backward_sync_update", "device": "host CPU",
-                   "note": "CPU restatement (oracle port) of the reference path; the reference's own lang::Cpp "
-                           "backend has no BatchNorm/Pooling without DNNL"},
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "cpu_baseline": {"value": v, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -138,33 +155,24 @@ def reference_main(args, rank, world):
     print(json.dumps(line))
 
 
-def sparse_main(args, rank, world, local):
-    """Sparse gradient exchange: every step each rank selects from a fresh flat
-    gradient (plus its residual), all ranks exchange [index | value] payloads
-    and every rank scatter-adds all payloads into the dense result.  One JSON
-    line: steps/s of the whole job, per-step time (max over ranks), payload."""
-    import faulthandler
-    faulthandler.dump_traceback_later(int(os.environ.get("SGB_BENCH_WATCHDOG_S", "900")), exit=True)
-    import torch
-    import torch.distributed as dist
-    from singa_b200 import _lib
-    from singa_b200.communicator import Communicator, NcclIdHolder
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
-    _lib.lib()
-    torch.cuda.set_device(local)
+def percentiles(xs):
+    xs = sorted(xs)
+
+    def q(f):
+        return xs[min(len(xs) - 1, int(round(f * (len(xs) - 1))))]
+    return {"p10": round(q(0.1), 4), "p50": round(q(0.5), 4), "p90": round(q(0.9), 4), "max": round(xs[-1], 4)}
+
+
+def sparse_leg(torch, dist, comm, rank, world, workload, n, K, W, sampler=None):
+    """Sparse gradient exchange (benchmark configuration 5): every step each
+    rank selects from a fresh flat gradient (plus its residual), all ranks
+    exchange [index | value] payloads and every rank scatter-adds all payloads
+    into the dense result.  Returns a dict (ms per exchange step = max over
+    ranks, elements/s of the whole job, roofline of the step)."""
     multi = world > 1
-    if multi:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
-    box = [NcclIdHolder().id if rank == 0 else None]
-    if multi:
-        dist.broadcast_object_list(box, src=0)
-    n = args.elements
-    comm = Communicator(local, world, NcclIdHolder(box[0]), buffSize=n)
-    topk = args.workload == "sparse_topk"
+    topk = workload == "sparse_topk"
     spars = 0.01 if topk else 2e-3
-    K, W = max(args.steps, 1), max(args.warmup, 3)
-    fresh = min(K, 20)                       # distinct gradients held on the device (0.4 GB each)
+    fresh = min(K, 20)                       # distinct gradients held on the device (0.4 GB each at 1e8)
     gen = torch.Generator(device="cuda")
     grads = []
     for step in range(fresh):
@@ -186,10 +194,9 @@ def sparse_main(args, rank, world, local):
     for k in range(W):
         step(k)
     acc.zero_()
-    sampler = ClockSampler(local)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    if rank == 0:
+    if sampler is not None:
         sampler.start()
     e0.record()
     for k in range(K):
@@ -201,7 +208,7 @@ def sparse_main(args, rank, world, local):
         t = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if sampler is not None else None
     nnz = int((work != 0).sum().item())       # non-zeros of the last dense result
     # the copy of the fresh gradient is part of the loop but not of the exchange: time it alone
     c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -214,25 +221,155 @@ def sparse_main(args, rank, world, local):
     peak, peak_kind = measured_peak()
     alg = 16.0 * n                            # read g, read acc, write acc, write dense result
     ex_ms = ms - copy_ms
-    if rank == 0:
-        print(json.dumps({
-            "metric": "sparse_gradient_exchange_elements_per_sec", "value": n * world / (ex_ms / 1e3),
-            "unit": "elements/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ex_ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "elements_per_gpu": n, "spars": spars, "residual": True,
-                       "topk_mode": "compat" if topk else None, "fresh_gradients": fresh,
-                       "loop_ms_incl_gradient_copy": ms, "dense_nonzeros_after_last_step": nnz,
-                       "l2": "inputs larger than L2: 0.4 GB per operand"},
-            "clocks": clocks,
+    del grads, work, acc
+    torch.cuda.empty_cache()
+    return {"workload": workload, "elements_per_gpu": n, "spars": spars, "residual": True,
+            "topk_mode": "compat" if topk else None, "steps": K, "warmup": W, "fresh_gradients": fresh,
+            "ms_per_step": ex_ms, "elements_per_sec": n * world / (ex_ms / 1e3),
+            "loop_ms_incl_gradient_copy": ms, "dense_nonzeros_after_last_step": nnz, "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": round(alg / ex_ms / 1e6, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(alg / ex_ms / 1e6 / peak, 4), "peak_kind": peak_kind, "traffic": None,
-                         "algorithmic_bytes_per_step": alg},
+                         "algorithmic_bytes_per_step": alg}}
+
+
+def sparse_main(args, rank, world, local):
+    """`--workload sparse_topk|sparse_threshold`: the sparse exchange alone, one JSON line."""
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("SGB_BENCH_WATCHDOG_S", "900")), exit=True)
+    import torch
+    import torch.distributed as dist
+    from singa_b200 import _lib
+    from singa_b200.communicator import Communicator, NcclIdHolder
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+    _lib.lib()
+    torch.cuda.set_device(local)
+    multi = world > 1
+    if multi:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    box = [NcclIdHolder().id if rank == 0 else None]
+    if multi:
+        dist.broadcast_object_list(box, src=0)
+    n = args.elements
+    comm = Communicator(local, world, NcclIdHolder(box[0]), buffSize=n)
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    r = sparse_leg(torch, dist, comm, rank, world, args.workload, n, K, W,
+                   sampler=ClockSampler(local) if rank == 0 else None)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "sparse_gradient_exchange_elements_per_sec", "value": r["elements_per_sec"],
+            "unit": "elements/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {k: r[k] for k in ("workload", "elements_per_gpu", "spars", "residual", "topk_mode",
+                                         "fresh_gradients", "loop_ms_incl_gradient_copy",
+                                         "dense_nonzeros_after_last_step")},
+            "clocks": r["clocks"], "roofline": r["roofline"],
         }), flush=True)
     torch.cuda.synchronize()
     comm.close()
     if multi:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def sync_check(torch, np, comm, rank, world):
+    """Cross-rank value check of every dense synchronisation entry point on
+    seeded per-rank buffers: every rank regenerates all ranks' inputs, so the
+    expected sums are known locally.  fp32 sums within 1e-5, fp16 within 1e-3
+    (relative to the largest expected magnitude)."""
+    sizes = [1000003, 4096, 77, 250000, 1]            # odd sizes, a 1-element tensor, 1.25 M in total
+
+    def inputs(r, tag):
+        rng = np.random.default_rng(1000 * tag + r)
+        return [rng.standard_normal(s).astype(np.float32) * np.float32(1e-2) for s in sizes]
+
+    worst = {}
+
+    def rel(got, want):
+        want = np.asarray(want, np.float64)
+        return float(np.abs(np.asarray(got, np.float64) - want).max() / max(np.abs(want).max(), 1e-30))
+
+    def expect(tag, half=False):
+        per_rank = [inputs(r, tag) for r in range(world)]
+        if half:
+            per_rank = [[a.astype(np.float16).astype(np.float64) for a in rr] for rr in per_rank]
+        return [sum(per_rank[r][i].astype(np.float64) for r in range(world)) for i in range(len(sizes))]
+
+    def dev(arrs, contiguous):
+        if contiguous:
+            flat = torch.from_numpy(np.concatenate(arrs)).cuda()
+            out, off = [], 0
+            for a in arrs:
+                out.append(flat[off:off + a.size])
+                off += a.size
+            return out
+        return [torch.from_numpy(np.concatenate([a, np.zeros(3, np.float32)])).cuda()[:a.size] for a in arrs]
+
+    # synch: one tensor in place
+    ts = dev(inputs(rank, 1), False)
+    for t in ts:
+        comm.synch(t)
+    comm.wait()
+    torch.cuda.synchronize()
+    worst["synch"] = max(rel(t.cpu().numpy(), w) for t, w in zip(ts, expect(1)))
+    # fusedSynch: contiguous list (reduced in place) and scattered list (packed)
+    for name, contiguous, tag in (("fusedSynch_contiguous", True, 2), ("fusedSynch_scattered", False, 3)):
+        ts = dev(inputs(rank, tag), contiguous)
+        for t in ts:
+            comm.fusedSynch([t], send=False)
+        comm.fusedSynch(ts, send=True)
+        comm.wait()
+        torch.cuda.synchronize()
+        worst[name] = max(rel(t.cpu().numpy(), w) for t, w in zip(ts, expect(tag)))
+    # fp16 transport
+    ts = dev(inputs(rank, 4), False)
+    for t in ts:
+        comm.fusedSynchHalf([t], send=False)
+    comm.fusedSynchHalf(ts, send=True)
+    comm.wait()
+    torch.cuda.synchronize()
+    worst["fusedSynchHalf"] = max(rel(t.cpu().numpy(), w) for t, w in zip(ts, expect(4, half=True)))
+    ts = dev(inputs(rank, 5), False)
+    comm.synchHalf(ts[0])
+    comm.wait()
+    torch.cuda.synchronize()
+    worst["synchHalf"] = rel(ts[0].cpu().numpy(), expect(5, half=True)[0])
+    tol = {"synch": 1e-5, "fusedSynch_contiguous": 1e-5, "fusedSynch_scattered": 1e-5,
+           "fusedSynchHalf": 1e-3 * max(world, 2), "synchHalf": 1e-3 * max(world, 2)}
+    ok = all(worst[k] <= tol[k] for k in worst)
+    return worst, ok
+
+
+def timeline(torch, path, comm):
+    """One eager (uncaptured) step with every communicator phase and every
+    per-bucket update bracketed by timing events on its own stream.  Returns
+    rows per bucket: ms since the start of the step at which the bucket's last
+    gradient was ready on the compute stream, its collective started / ended,
+    its update ended; plus the end of the step."""
+    path.profile = True
+    for _ in range(2):                      # the first profiled step warms the event pools
+        torch.cuda.synchronize()
+        comm.profile_begin()
+        path.run_step()
+        comm.profile_mark("step_end")
+        rows = comm.profile_end()
+    path.profile = False
+    buckets, cur = [], None
+    step_end = None
+    for name, t0, t1 in rows:
+        if name == "bucket_ready":
+            cur = {"ready": round(t0, 4)}
+            buckets.append(cur)
+        elif name == "step_end":
+            step_end = round(t0, 4)
+        elif cur is not None and name.startswith("Dist_s_"):
+            cur["collective"] = name
+            cur["start"], cur["end"] = round(t0, 4), round(t1, 4)
+        elif cur is not None and name == "sgd_update_bucket":
+            cur["update_end"] = round(t1, 4)
+    coll_ms = sum(b["end"] - b["start"] for b in buckets if "end" in b)
+    return {"mode": "eager, one step", "step_end_ms": step_end, "collective_ms_sum": round(coll_ms, 4),
+            "buckets": buckets}
 
 
 def main():
@@ -251,8 +388,15 @@ def main():
     ap.add_argument("--pool-argmax", action="store_true",
                     help="max-pool backward from the forward partner's arg-max record instead of (x, y): changes "
                          "what the backward consumes, so it is not the default")
+    ap.add_argument("--relu-mask", action="store_true",
+                    help="ReLU backward (alone or fused) from the forward partner's one-bit-per-element record "
+                         "instead of the stored ReLU input: changes what the backward consumes, not the default")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-legs", action="store_true",
+                    help="skip the fp16-sync and sparse-exchange legs that ride in the same JSON line")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0, help="cap on the CTAs NCCL's kernels use (0 = default)")
+    ap.add_argument("--no-register", action="store_true", help="do not register the gradient arena with NCCL")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -282,19 +426,32 @@ def main():
     multi = world > 1
     if multi:
         dist.init_process_group("gloo", rank=rank, world_size=world)
-    box = [NcclIdHolder().id if rank == 0 else None]
-    if multi:
-        dist.broadcast_object_list(box, src=0)
-    comm = Communicator(local, world, NcclIdHolder(box[0]), buffSize=4194304)
+
+    def new_comm(buff):
+        box = [NcclIdHolder().id if rank == 0 else None]
+        if multi:
+            dist.broadcast_object_list(box, src=0)
+        return Communicator(local, world, NcclIdHolder(box[0]), buffSize=buff, max_ctas=args.nccl_max_ctas)
+
+    comm = new_comm(4194304)
 
     K, W = max(args.steps, 1), max(args.warmup, 3)
+    WARM_REPLAYS = 10            # untimed graph replays (NCCL included) before the timed region, whatever W is
     fused = not args.call_pattern
-    plan = build_plan(batch=BATCH, fused=False)        # the reference's call sequence ...
-    if fused:
-        plan = fuse_plan(plan)                         # ... rewritten by the peephole pass
-    plan = add_wgrad_refresh(plan)                     # the contractions' weight gradients are rewritten every step
-    path = HotPathGPU(plan, communicator=comm, world=world, seed=1000 + rank, dist_option=args.dist_option,
-                      pool_argmax=args.pool_argmax)
+    use_graph = not args.no_graph
+
+    def make_path(dist_option, communicator):
+        plan = build_plan(batch=BATCH, fused=False)        # the reference's call sequence ...
+        if fused:
+            plan = fuse_plan(plan)                         # ... rewritten by the peephole pass
+        plan = add_wgrad_refresh(plan)                     # the contractions' weight gradients are rewritten every step
+        hp = HotPathGPU(plan, communicator=communicator, world=world, seed=1000 + rank, dist_option=dist_option,
+                        pool_argmax=args.pool_argmax)
+        if multi and not args.no_register:
+            communicator.register(hp.grad_arena)
+        return plan, hp
+
+    plan, path = make_path(args.dist_option, comm)
     by_family, nparam = algorithmic_bytes(plan, world, pool_argmax=args.pool_argmax)
 
     def barrier():
@@ -309,38 +466,46 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- warm-up (eager), graph capture, warm replays
-    launches = 0
-    for _ in range(W):
-        launches = path.run_step()
-    torch.cuda.synchronize()
-    use_graph = not args.no_graph
-    if use_graph:
-        path.capture()
-        path.graph.replay()
+    def timed_steps(hp, k_steps):
+        """W eager warm-up steps, capture, warm replays, then exactly k_steps
+        timed steps (own event pair each).  Returns (ms per step = max over
+        ranks of the whole region / k_steps, per-step list of this rank, launches)."""
+        launches = 0
+        for _ in range(W):
+            launches = hp.run_step()
         torch.cuda.synchronize()
-
-    def one_step():
         if use_graph:
-            path.graph.replay()
-        else:
-            path.run_step()
+            hp.capture()
+            for _ in range(WARM_REPLAYS):
+                hp.graph.replay()
+            torch.cuda.synchronize()
 
-    # ---- device-resident timing
+        def one():
+            if use_graph:
+                hp.graph.replay()
+            else:
+                hp.run_step()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(k_steps + 1)]
+        barrier()
+        torch.cuda.profiler.start()     # lets `ncu --profile-from-start off` see exactly the timed steps
+        marks[0].record()
+        for i in range(k_steps):
+            one()
+            marks[i + 1].record()
+        barrier()
+        torch.cuda.profiler.stop()
+        total = max_over_ranks(marks[0].elapsed_time(marks[-1])) / k_steps
+        per = [marks[i].elapsed_time(marks[i + 1]) for i in range(k_steps)]
+        return total, per, one, launches
+
+    # ---- device-resident timing (clocks sampled from the warm replays to the end of the e2e region)
     sampler = ClockSampler(local)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
     if rank == 0:
         sampler.start()
-    torch.cuda.profiler.start()     # lets `ncu --profile-from-start off` see exactly the timed steps
-    e0.record()
-    for _ in range(K):
-        one_step()
-    e1.record()
-    barrier()
-    torch.cuda.profiler.stop()
-    ms = max_over_ranks(e0.elapsed_time(e1)) / K
+    ms, per_step, one_step, _ = timed_steps(path, K)
     value = BATCH * world / (ms / 1e3)
+    step_ms = percentiles(per_step)
+    step_ms["max"] = round(max_over_ranks(step_ms["max"]), 4)
 
     # ---- end to end: pinned host batch + labels in, loss out, every step.
     # The next batch is prefetched on a copy stream while the current step runs
@@ -390,24 +555,86 @@ def main():
     fam_ms = profile_families(path, torch)
     peak, peak_kind = measured_peak()
     fam = {}
-    alias = {"relu_bwd": "relu_bwd", "add_relu_bwd": "add_relu_bwd", "add_out": "join", "bn_bwd": "bn_bwd",
-             "bn_relu_bwd": "bn_relu_bwd", "bn_add_relu_bwd": "bn_add_relu_bwd", "maxpool_bwd": "maxpool_bwd", "avgpool_bwd": "avgpool_bwd", "sgd": "sgd"}
+    alias = {"relu_bwd": "relu_bwd", "relu_mask_bwd": "relu_mask_bwd", "add_relu_bwd": "add_relu_bwd",
+             "add_relu_mask_bwd": "add_relu_mask_bwd", "add_out": "join", "bn_bwd": "bn_bwd",
+             "bn_relu_bwd": "bn_relu_bwd", "bn_relu_mask_bwd": "bn_relu_mask_bwd",
+             "bn_add_relu_bwd": "bn_add_relu_bwd", "maxpool_bwd": "maxpool_bwd",
+             "avgpool_bwd": "avgpool_bwd", "wgrad_refresh": "wgrad_standin", "sgd": "sgd"}
     for k, name in alias.items():
         if k in fam_ms and name in by_family and fam_ms[k] > 0:
             gbs = by_family[name] / fam_ms[k] / 1e6
             fam[name] = {"ms": round(fam_ms[k], 4), "GBps": round(gbs, 1), "frac": round(gbs / peak, 3)}
-    bn_keys = [k for k in ("bn_bwd", "bn_relu_bwd", "bn_add_relu_bwd") if k in fam_ms]
+    bn_keys = [k for k in ("bn_bwd", "bn_relu_bwd", "bn_relu_mask_bwd", "bn_add_relu_bwd") if k in fam_ms]
     bn_bytes = sum(by_family[k] for k in bn_keys)
     bn_ms = sum(fam_ms[k] for k in bn_keys)
     bn_launches = sum(1 for o in plan["ops"] if o.kind in bn_keys)
     achieved = bn_bytes / bn_ms / 1e6
+    captured_plan = fused and not args.relu_mask
     roofline = {"bound": "hbm", "kernel": "batch-norm backward (reduce + apply)", "achieved": round(achieved, 1),
                 "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                "traffic": NCU_BN_TRAFFIC_PER_CALL[fused],
+                "traffic": NCU_BN_TRAFFIC_PER_CALL[fused] if (captured_plan or not fused) else None,
+                "traffic_source": "ncu capture summarised in profiles/bench_resnet50_launch_list.md (a constant, "
+                                  "not measured in this run)",
                 "peak_kind": peak_kind, "launches_per_step": bn_launches,
                 "algorithmic_bytes_per_launch": bn_bytes / max(bn_launches, 1),
                 "avg_launch_ms": bn_ms / max(bn_launches, 1)}
     total_alg = sum(by_family.values())
+
+    # ---- cross-rank value check and the eager per-bucket timeline (every rank runs them, rank 0 reports)
+    worst, ok = sync_check(torch, np, comm, rank, world)
+    ok = bool(max_over_ranks(0.0 if ok else 1.0) == 0.0)
+    check = {"max_rel_err": {k: float("%.3e" % max_over_ranks(v)) for k, v in worst.items()}, "ok": ok,
+             "tolerance": "1e-5 fp32, 1e-3 x world fp16, relative to the largest expected sum"}
+    tl = timeline(torch, path, comm)
+    launches_per_step = kernel_launches(path)
+
+    nvlink = None
+    if multi:
+        wire = 2.0 * (world - 1) / world * 4.0 * nparam * (0.5 if args.dist_option == "half" else 1.0)
+        lower = wire / 900e9 * 1e3
+        coll = tl["collective_ms_sum"]
+        nvlink = {"bytes_per_step": wire, "formula": "2 (W-1)/W x gradient bytes, per GPU and direction",
+                  "peak_GBps": 900.0, "peak_measured_GBps": 770.0, "lower_bound_ms": round(lower, 4),
+                  "lower_bound_share_of_step": round(lower / ms, 4),
+                  "collective_ms_sum": coll, "achieved_GBps": round(wire / coll / 1e6, 1) if coll else None,
+                  "frac": round(wire / coll / 1e6 / 900.0, 4) if coll else None,
+                  "frac_of_measured": round(wire / coll / 1e6 / 770.0, 4) if coll else None,
+                  "note": "collective times from the eager timeline (they overlap the backward kernels)"}
+
+    path.release_graph()          # graphs that captured NCCL work must go before the communicator
+    import gc
+    del one_step
+    gc.collect()
+    torch.cuda.synchronize()
+
+    # ---- configurations 4 and 5 with the same code, in the same line
+    extra = {}
+    if not args.no_extra_legs and not args.call_pattern:
+        other = "half" if args.dist_option == "plain" else "plain"
+        K2 = min(K, 50)
+        _, path2 = make_path(other, comm)
+        ms2, per2, one2, _ = timed_steps(path2, K2)
+        extra["config4_fp16_sync" if other == "half" else "config3_plain_sync"] = {
+            "dist_option": other, "steps": K2, "ms_per_step": ms2, "images_per_sec": BATCH * world / (ms2 / 1e3),
+            "step_ms": percentiles(per2)}
+        path2.release_graph()
+        del one2, path2
+        gc.collect()
+        torch.cuda.synchronize()
+        del path
+        gc.collect()
+        torch.cuda.empty_cache()
+        comm.close()
+        comm = new_comm(args.elements)
+        legs = {}
+        for wl in ("sparse_topk", "sparse_threshold"):
+            r = sparse_leg(torch, dist, comm, rank, world, wl, args.elements, 20, 3)
+            legs[wl] = {k: r[k] for k in ("spars", "topk_mode", "steps", "ms_per_step", "elements_per_sec",
+                                          "dense_nonzeros_after_last_step", "roofline")}
+            if multi and wl == "sparse_topk":      # all-gather: every GPU receives the (W-1) payloads of its peers
+                pay = 8.0 * _lib.lib().sgb_topk_count(r["spars"], args.elements)
+                legs[wl]["nvlink_lower_bound_ms"] = round((world - 1) * pay / 900e9 * 1e3, 5)
+        extra["config5_sparse_exchange"] = dict(legs, elements_per_gpu=args.elements, fresh_gradients=20)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -418,25 +645,22 @@ def main():
                         "ms_per_step": cms}
 
     if rank == 0:
+        config = workload_config(world, args.dist_option, fused, use_graph, args.pool_argmax, args.relu_mask)
+        config.update({"l2": "inputs larger than L2: %.1f GB touched per step vs 126 MB" % (total_alg / 1e9),
+                       "algorithmic_GB_per_step": round(total_alg / 1e9, 3),
+                       "hot_path_GBps": round(total_alg / ms / 1e6, 1),
+                       "warm_graph_replays": WARM_REPLAYS if use_graph else 0,
+                       "nccl_max_ctas": args.nccl_max_ctas, "arena_registered": bool(multi and not args.no_register)})
         line = {
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
-                       "global_batch": BATCH * world, "dist_option": args.dist_option,
-                       "fusion": "bn+relu, join+relu, softmax+ce+grad" if fused else "none (one kernel per reference call)",
-                       "cuda_graph": use_graph, "pool_argmax_record": bool(args.pool_argmax), "bucket_elems": 4194304, "threshold_elems": 2097152,
-                       "l2": "inputs larger than L2: %.1f GB touched per step vs 126 MB" % (total_alg / 1e9),
-                       "excluded": "cuDNN/cuBLAS contractions (conv, linear): stand-in gradients",
-                       "algorithmic_GB_per_step": round(total_alg / 1e9, 3),
-                       "hot_path_GBps": round(total_alg / ms / 1e6, 1)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": kernel_launches(path) * K,
-            "roofline": roofline, "roofline_by_family": fam, "cpu_baseline": cpu_baseline,
+            "ms_per_step": ms, "step_ms": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * K,
+            "roofline": roofline, "roofline_by_family": fam, "sync_check": check, "nvlink": nvlink,
+            "timeline": tl, "cpu_baseline": cpu_baseline,
         }
+        line.update(extra)
         print(json.dumps(line), flush=True)
-    path.release_graph()          # graphs that captured NCCL work must go before the communicator
-    import gc
-    gc.collect()
     torch.cuda.synchronize()
     comm.close()
     if multi:
@@ -455,12 +679,14 @@ def kernel_launches(path):
            "sgb_avgpool_backward_f32": 1, "sgb_softmax_rows_f32": 1, "sgb_cross_entropy_f32": 1,
            "sgb_sum_all_f32": 1, "sgb_softmax_cross_entropy_bwd_f32": 1,
            "sgb_softmax_cross_entropy_grad_f32": 1, "sgb_softmax_cross_entropy_fused_f32": 1,
-           "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1}
+           "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1, "sgb_set_f32": 1}
     n = 0
     for name, args in path.calls:
         if name in ("sgb_bn_backward_f32", "sgb_bn_relu_backward_f32", "sgb_bn_add_relu_backward_f32"):
             N, _, HW = args[-6:-3]          # (..., N, C, HW, workspace, workspace bytes, stream)
             n += 2 if N * HW * 8 > 8 * 100 * 1024 else 1
+        elif name == "sgb_unpack_f32":       # stand-in weight gradients: one launch per 72 tensors
+            n += (args[4] + 71) // 72
         else:
             n += per.get(name, 0)
     if path.comm is not None:

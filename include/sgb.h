@@ -481,6 +481,17 @@ int sgb_comm_unique_id_bytes(void);
 int sgb_comm_get_unique_id(void *id_out);
 int sgb_comm_create(sgb_comm **out, int rank, int world, const void *unique_id,
                     size_t max_elems);
+/* As sgb_comm_create, with NCCL's per-communicator limits on the number of
+ * CTAs its kernels may use (ncclConfig_t minCTAs / maxCTAs; 0 = NCCL's
+ * default): the collectives share the SMs with the backward kernels. */
+int sgb_comm_create_ex(sgb_comm **out, int rank, int world,
+                       const void *unique_id, size_t max_elems, int min_ctas,
+                       int max_ctas);
+/* Registers a caller-owned device buffer that will be reduced in place (a
+ * gradient arena) with NCCL (ncclCommRegister), so that collectives on it can
+ * use the registered-buffer protocols.  Deregistered by sgb_comm_destroy; the
+ * buffer must outlive the communicator. */
+int sgb_comm_register(sgb_comm *c, void *buffer, size_t bytes);
 int sgb_comm_destroy(sgb_comm *c);
 int sgb_comm_rank(const sgb_comm *c);
 int sgb_comm_world_size(const sgb_comm *c);
@@ -521,6 +532,8 @@ int sgb_comm_order_plan(unsigned char *state4, int call, unsigned *edges4,
  * Not usable while a stream is being captured (phases are then not timed). */
 int sgb_comm_profile_begin(sgb_comm *c, void *compute_stream);
 int sgb_comm_profile_range(sgb_comm *c, const char *name, int which, int begin);
+/* A named point in time on any stream (start == end in the rows). */
+int sgb_comm_profile_mark(sgb_comm *c, const char *name, void *stream);
 int sgb_comm_profile_end(sgb_comm *c, char *names, size_t name_stride,
                          float *start_ms, float *end_ms, size_t capacity,
                          size_t *count);

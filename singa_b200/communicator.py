@@ -43,7 +43,7 @@ class Communicator(object):
     current (compute) stream wait for the communicator's side streams.
     """
 
-    def __init__(self, local_rank, world_size, holder, buffSize=4194304):
+    def __init__(self, local_rank, world_size, holder, buffSize=4194304, min_ctas=0, max_ctas=0):
         if not torch.cuda.is_available():
             raise RuntimeError("singa_b200.Communicator needs a CUDA device; there is no CPU path")
         self.local_rank = int(local_rank)
@@ -55,8 +55,8 @@ class Communicator(object):
         idbuf = C.create_string_buffer(holder.id, len(holder.id))
         self._h = None
         try:
-            _lib.call("sgb_comm_create", C.byref(handle), self.global_rank, self.world_size,
-                      C.cast(idbuf, C.c_void_p), int(buffSize))
+            _lib.call("sgb_comm_create_ex", C.byref(handle), self.global_rank, self.world_size,
+                      C.cast(idbuf, C.c_void_p), int(buffSize), int(min_ctas), int(max_ctas))
         except _lib.SgbError:
             if handle:
                 _lib.lib().sgb_comm_destroy(handle)
@@ -77,6 +77,29 @@ class Communicator(object):
     def set_topk_mode(self, mode):
         """"compat" (default): the reference comparator's key; "magnitude": |g|."""
         _lib.call("sgb_comm_set_topk_mode", self._h, {"magnitude": 0, "compat": 1}[mode])
+
+    def register(self, t):
+        """Registers a tensor that is reduced in place (a gradient arena) with NCCL."""
+        _lib.call("sgb_comm_register", self._h, t.data_ptr(), t.numel() * t.element_size())
+
+    # -- per-phase device timing (the reference's per-operation time profiling)
+    def profile_begin(self):
+        _lib.call("sgb_comm_profile_begin", self._h, _stream())
+
+    def profile_mark(self, name):
+        _lib.call("sgb_comm_profile_mark", self._h, name.encode(), _stream())
+
+    def profile_end(self, capacity=4096):
+        """[(phase name, start ms, end ms)] since profile_begin, in issue order."""
+        stride = 64
+        names = C.create_string_buffer(stride * capacity)
+        t0, t1 = (C.c_float * capacity)(), (C.c_float * capacity)()
+        count = C.c_size_t()
+        _lib.call("sgb_comm_profile_end", self._h, C.cast(names, C.c_void_p), stride, t0, t1, capacity,
+                  C.byref(count))
+        n = min(count.value, capacity)
+        return [(names.raw[i * stride:(i + 1) * stride].split(b"\0", 1)[0].decode(), float(t0[i]), float(t1[i]))
+                for i in range(n)]
 
     # -- reference API -------------------------------------------------------
     def synch(self, t):

@@ -95,6 +95,7 @@ struct sgb_comm {
   };
   std::vector<Range> ranges;
   size_t open_range = 0;
+  std::vector<void*> registered;   // ncclCommRegister handles (user buffers reduced in place)
   // Staging is deferred: a stage call only records the tensors; the bytes are
   // gathered by ONE multi-tensor pack launch when the bucket is flushed (the
   // tensors must stay alive until then anyway - the flush writes into them).
@@ -176,7 +177,7 @@ struct Phase {
 void drop_ranges(sgb_comm* c) {
   for (auto& r : c->ranges) {
     cudaEventDestroy(r.start);
-    cudaEventDestroy(r.end);
+    if (r.end) cudaEventDestroy(r.end);
   }
   c->ranges.clear();
 }
@@ -268,6 +269,20 @@ int sgb_comm_get_unique_id(void* id_out) {
 }
 
 int sgb_comm_create(sgb_comm** out, int rank, int world, const void* unique_id, size_t max_elems) {
+  return sgb_comm_create_ex(out, rank, world, unique_id, max_elems, 0, 0);
+}
+
+int sgb_comm_register(sgb_comm* c, void* buffer, size_t bytes) {
+  if (!c || !buffer) return SGB_ERR_NULL;
+  if (bytes == 0) return SGB_ERR_SIZE;
+  void* handle = nullptr;
+  NC(ncclCommRegister(c->nccl, buffer, bytes, &handle));
+  c->registered.push_back(handle);
+  return SGB_OK;
+}
+
+int sgb_comm_create_ex(sgb_comm** out, int rank, int world, const void* unique_id, size_t max_elems,
+                       int min_ctas, int max_ctas) {
   if (!out || !unique_id) return SGB_ERR_NULL;
   if (world < 1 || rank < 0 || rank >= world || max_elems == 0) return SGB_ERR_SIZE;
   if (max_elems > 0x7fffffffu) return SGB_ERR_SIZE;  // collective counts and 1-based indices are int32
@@ -280,7 +295,14 @@ int sgb_comm_create(sgb_comm** out, int rank, int world, const void* unique_id, 
   CU(cudaGetDevice(&c->device));
   ncclUniqueId id;
   std::memcpy(&id, unique_id, sizeof(id));
-  NC(ncclCommInitRank(&c->nccl, world, id, rank));
+  if (min_ctas > 0 || max_ctas > 0) {
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    if (min_ctas > 0) cfg.minCTAs = min_ctas;
+    if (max_ctas > 0) cfg.maxCTAs = max_ctas;
+    NC(ncclCommInitRankConfig(&c->nccl, world, id, rank, &cfg));
+  } else {
+    NC(ncclCommInitRank(&c->nccl, world, id, rank));
+  }
   CU(cudaMalloc(&c->send, max_elems * sizeof(float)));
   CU(cudaMalloc(&c->recv, max_elems * sizeof(float)));
   // Highest priority: the collectives and their small pack / unpack kernels
@@ -302,7 +324,10 @@ int sgb_comm_destroy(sgb_comm* c) {
   if (c->s) cudaStreamSynchronize(c->s);
   if (c->c1) cudaStreamSynchronize(c->c1);
   if (c->c2) cudaStreamSynchronize(c->c2);
-  if (c->nccl) ncclCommDestroy(c->nccl);
+  if (c->nccl) {
+    for (void* h : c->registered) ncclCommDeregister(c->nccl, h);
+    ncclCommDestroy(c->nccl);
+  }
   void* bufs[] = {c->send, c->recv, c->send_h, c->recv_h, c->dsend_h, c->drecv_h, c->sum, c->pay_send,
                   c->pay_recv, c->ws, c->nnz_dev};
   for (void* b : bufs)
@@ -392,6 +417,18 @@ int sgb_comm_profile_range(sgb_comm* c, const char* name, int which, int begin) 
   return SGB_OK;
 }
 
+int sgb_comm_profile_mark(sgb_comm* c, const char* name, void* stream) {
+  if (!c || !name) return SGB_ERR_NULL;
+  if (!c->profiling) return SGB_OK;
+  sgb_comm::Range r;
+  r.name = name;
+  CU(cudaEventCreate(&r.start));
+  CU(cudaEventRecord(r.start, sgb::as_stream(stream)));
+  r.end = nullptr;   // a mark has no extent
+  c->ranges.push_back(r);
+  return SGB_OK;
+}
+
 int sgb_comm_profile_end(sgb_comm* c, char* names, size_t name_stride, float* start_ms, float* end_ms,
                          size_t capacity, size_t* count) {
   if (!c || !count) return SGB_ERR_NULL;
@@ -405,7 +442,7 @@ int sgb_comm_profile_end(sgb_comm* c, char* names, size_t name_stride, float* st
       names[i * name_stride + name_stride - 1] = 0;
     }
     if (start_ms) CU(cudaEventElapsedTime(start_ms + i, c->prof_origin, r.start));
-    if (end_ms) CU(cudaEventElapsedTime(end_ms + i, c->prof_origin, r.end));
+    if (end_ms) CU(cudaEventElapsedTime(end_ms + i, c->prof_origin, r.end ? r.end : r.start));
   }
   drop_ranges(c);
   return SGB_OK;

@@ -47,6 +47,7 @@ class HotPathGPU(object):
         self._bind()
         self.graph = None
         self.launches_per_step = None
+        self.profile = False      # True: mark "bucket_ready" on the compute stream (communicator timing on)
 
     # ------------------------------------------------------------------ tensors
     def _alloc(self, seed):
@@ -286,6 +287,8 @@ class HotPathGPU(object):
         ev = self.flush_after.get(idx)
         opt = self.dist_option
         is_direct = ev is not None and ev[0] == "direct"
+        if self.profile and ev is not None:
+            L.sgb_comm_profile_mark(c._h, b"bucket_ready", stream)
         if opt in ("plain", "half"):
             half = opt == "half"
             if is_direct:
