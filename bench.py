@@ -113,6 +113,65 @@ def cpu_arm(steps, warmup, batch=CPU_SAMPLE_BATCH, threads=None):
     return batch / dt, dt * 1e3, cpu.num_threads()
 
 
+def config1_leg(torch, steps=50):
+    """Benchmark configuration 1 (MLP 784-4096-4096-10, batch 256, SGD lr 0.05
+    momentum 0.9), backward + update hot path without the contractions: the GPU
+    executor (CUDA-graph replay, CUDA events) beside the reference's own
+    lang::Cpp code - its tensor.cc / tensor_math_cpp.h compiled unmodified into
+    oracle/_ref/libref_core.so - walking the same ops on the host cores."""
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import build_mlp_plan, fuse_plan
+    plan = fuse_plan(build_mlp_plan())
+    hp = HotPathGPU(plan, communicator=None, world=1, seed=0, lr=0.05, momentum=0.9, weight_decay=0.0)
+    for _ in range(3):
+        hp.run_step()
+    torch.cuda.synchronize()
+    g = hp.capture()
+    for _ in range(10):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    gpu_ms = e0.elapsed_time(e1) / steps
+    hp.release_graph()
+    out = {"workload": "mlp_784_4096_4096_10_b256_backward_update", "steps": steps, "gpu_ms_per_step": gpu_ms,
+           "gpu_images_per_sec": 256 / (gpu_ms / 1e3), "cpu_reference": None}
+    try:
+        from oracle import ref_core
+        from oracle.path import make_tensors
+        if not ref_core.available():
+            raise ImportError("oracle/_ref/libref_core.so not built")
+        raw = build_mlp_plan()
+        t = make_tensors(raw, seed=0)
+        dims = (784, 4096, 4096, 10)
+        mlp = ref_core.MLP(256, dims, lr=0.05, momentum=0.9)
+        for i in range(3):
+            mlp.set(i, 0, t["fc%d.W" % i])
+            mlp.set(i, 1, t["fc%d.b" % i])
+        relu_x = [t["relu%d.x" % i] for i in range(2)]
+        dgrad = [None] + [t["fc%d.dgrad" % i] for i in (1, 2)]
+        wgrad = [t["d:fc%d.W" % i] for i in range(3)]
+        ref_core.mlp_hot_path_step(mlp, t["logits"], t["labels"], relu_x, dgrad, wgrad)      # warm-up
+        n = 5
+        t0 = time.perf_counter()
+        for _ in range(n):
+            ref_core.mlp_hot_path_step(mlp, t["logits"], t["labels"], relu_x, dgrad, wgrad)
+        ms = (time.perf_counter() - t0) / n * 1e3
+        mlp.close()
+        out["cpu_reference"] = {
+            "kind": "reference", "ms_per_step": ms, "images_per_sec": 256 / (ms / 1e3), "cores": os.cpu_count(),
+            "sample": "the full configuration-1 step, %d timed steps after 1 warm-up; the reference's elementwise "
+                      "loops are serial (one core), only its BLAS-1 calls use OpenMP; includes the host copies "
+                      "into singa::Tensor objects" % n}
+    except Exception as e:      # the comparator is optional on a box without the prebuilt library
+        out["cpu_reference_unavailable"] = str(e)[:200]
+    return out
+
+
 def workload_config(world, dist_option, fused, use_graph, pool_argmax, relu_mask=False):
     """The `config` object shared by both arms (same keys, same values)."""
     return {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
@@ -643,6 +702,9 @@ def main():
                         "sample": "ResNet-50 hot path at batch %d (of %d), 3 timed steps after 1 warm-up, "
                                   "oracle C port, %d OpenMP threads" % (CPU_SAMPLE_BATCH, BATCH, cores),
                         "ms_per_step": cms}
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.no_extra_legs:
+        extra["config1_mlp"] = config1_leg(torch)
 
     if rank == 0:
         config = workload_config(world, args.dist_option, fused, use_graph, args.pool_argmax, args.relu_mask)

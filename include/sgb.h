@@ -43,6 +43,17 @@ extern "C" {
 const char *sgb_status_string(int status);
 int sgb_last_cuda_error(void); /* last cudaError_t recorded by this library */
 int sgb_version(void);
+/* Library-wide switches, read at launch time (set them before capturing a
+ * CUDA graph; a captured launch keeps the setting it was captured with).
+ * SGB_OPT_OVERLAP_LAUNCHES (default 1): the batch-norm and elementwise
+ * kernels are launched with programmatic stream serialisation, so that a
+ * kernel's CTAs are scheduled while the previous kernel of the same stream
+ * drains; each such kernel waits for its predecessors' completion before its
+ * first access to global memory, so results and stream-order semantics are
+ * unchanged.  0 restores plain launches. */
+enum sgb_option { SGB_OPT_OVERLAP_LAUNCHES = 1, SGB_OPT_COUNT_ = 2 };
+int sgb_set_option(int option, int value);
+int sgb_get_option(int option);
 
 /* --------------------------------------------------------------- ReLU path */
 /* y = x > 0 ? x : 0.  Replaces singa::cuda::relu

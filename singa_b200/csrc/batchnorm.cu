@@ -79,6 +79,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                      float2* __restrict__ partial, BnShape sh, int per_slice) {
   __shared__ float sm[32];
   const int c = blockIdx.y, slice = blockIdx.x;
+  dependency_wait();
   const float mu = mean[c];
   float s_dy = 0.f, s_dyx = 0.f;
   if (VEC) {
@@ -111,6 +112,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       s_dyx += g * (x[off] - mu);
     }
   }
+  release_dependents();
   s_dy = block_sum(s_dy, sm);
   s_dyx = block_sum(s_dyx, sm);
   if (threadIdx.x == 0)
@@ -141,6 +143,7 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   size_t off[kApplyUnits];
   Vec4f vx[kApplyUnits], vg[kApplyUnits], vm[kApplyUnits];
   UnitWalk w(min(unit0, total - 1), kBlock, hwu);
+  dependency_wait();
 #pragma unroll
   for (int j = 0; j < kApplyUnits; ++j) {
     vx[j].f[0] = vg[j].f[0] = vm[j].f[0] = 0.f;
@@ -184,6 +187,7 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     }
   }
   __syncthreads();
+  release_dependents();
   const float k = coef[0], a = coef[1], b = coef[2], mu = coef[3];
 #pragma unroll
   for (int j = 0; j < kApplyUnits; ++j) {
@@ -247,9 +251,10 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const int first = u0 + threadIdx.x;
   float* sx = stage;
   float* sg = stage + static_cast<size_t>(per_cta) * kW;
-  const float mu = mean[c];
   const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
   const size_t chan_off = static_cast<size_t>(c) * sh.HW;
+  dependency_wait();                                  // first access to global memory follows
+  const float mu = mean[c];
 
   // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
   if (VEC && ADD) {
@@ -404,7 +409,9 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     dbias[c] = a;
   }
 
-  // phase 3: dx from the staged copy
+  // phase 3: dx from the staged copy.  From here on this CTA only drains: the
+  // next kernel of the stream may take the SM slots that free up.
+  release_dependents();
   {
     UnitWalk w(first, T, hwu);
     for (int u = first; u < u1; u += T, w.next()) {
@@ -452,6 +459,7 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const size_t sample_stride = static_cast<size_t>(sh.C) * sh.HW;
   const size_t base = static_cast<size_t>(c0) * sh.HW;
   UnitWalk wl(threadIdx.x, kBlock, run4);
+  dependency_wait();
   if (MASK) {
     // x by asynchronous copy; dy and the ReLU input through registers, four
     // units (eight independent 16-byte loads) per round
@@ -540,6 +548,7 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     }
   }
   __syncthreads();
+  release_dependents();
   {
     UnitWalk w(threadIdx.x, kBlock, run4);
     for (int u = threadIdx.x; u < units; u += kBlock, w.next()) {
@@ -563,8 +572,8 @@ int launch_group(const float* x, const float* dy, const float* relu_in, const fl
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_set[dev] = true;
   }
-  kernel<<<sh.C / G, kBlock, smem, s>>>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh);
-  return launch_status();
+  return launch_ex(kernel, dim3(sh.C / G), dim3(kBlock), smem, s, 0, true, x, dy, relu_in, scale, mean, invstd,
+                   dx, dscale, dbias, sh);
 }
 
 // Cluster size (1, 2, 4 or 8) and per-CTA share for the single-pass kernel;
@@ -622,22 +631,8 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
     if (e != cudaSuccess) return note_cuda_error(e);
     attr_set[dev] = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(sh.C) * cs);
-  cfg.blockDim = dim3(T);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cs;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, dy, relu_in, scale, mean, invstd, dx, dscale,
-                                     dbias, sh, per_cta, dy_b, joined);
-  if (e != cudaSuccess) return note_cuda_error(e);
-  return launch_status();
+  return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
+                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined);
 }
 
 template <bool VEC, bool MASK>
@@ -732,16 +727,21 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
   const int total = static_cast<int>(vec ? per_channel / 4 : per_channel);
   const int per_slice = static_cast<int>(ceil_div(total, slices));
   const dim3 g1(slices, C), g2(static_cast<unsigned>(ceil_div(total, kBlock * kApplyUnits)), C);
+  int st;
   if (vec) {
-    bn_bwd_reduce_kernel<true, MASK><<<g1, kBlock, 0, s>>>(x, dy, relu_in, mean, partial, sh, per_slice);
-    bn_bwd_apply_kernel<true, MASK><<<g2, kBlock, 0, s>>>(x, dy, relu_in, scale, mean, invstd,
-                                                          partial, slices, dx, dscale, dbias, sh);
+    st = launch_ex(bn_bwd_reduce_kernel<true, MASK>, g1, dim3(kBlock), 0, s, 0, true, x, dy, relu_in, mean, partial,
+                   sh, per_slice);
+    if (st != SGB_OK) return st;
+    st = launch_ex(bn_bwd_apply_kernel<true, MASK>, g2, dim3(kBlock), 0, s, 0, true, x, dy, relu_in, scale, mean,
+                   invstd, partial, slices, dx, dscale, dbias, sh);
   } else {
-    bn_bwd_reduce_kernel<false, MASK><<<g1, kBlock, 0, s>>>(x, dy, relu_in, mean, partial, sh, per_slice);
-    bn_bwd_apply_kernel<false, MASK><<<g2, kBlock, 0, s>>>(x, dy, relu_in, scale, mean, invstd,
-                                                           partial, slices, dx, dscale, dbias, sh);
+    st = launch_ex(bn_bwd_reduce_kernel<false, MASK>, g1, dim3(kBlock), 0, s, 0, true, x, dy, relu_in, mean,
+                   partial, sh, per_slice);
+    if (st != SGB_OK) return st;
+    st = launch_ex(bn_bwd_apply_kernel<false, MASK>, g2, dim3(kBlock), 0, s, 0, true, x, dy, relu_in, scale, mean,
+                   invstd, partial, slices, dx, dscale, dbias, sh);
   }
-  return launch_status();
+  return st;
 }
 
 int bn_add_relu_backward(const float* x, const float* dy_a, const float* dy_b, const float* relu_in,

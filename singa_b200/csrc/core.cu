@@ -8,7 +8,15 @@ namespace {
 std::atomic<int> g_last_cuda_error{0};
 constexpr int kMaxDevices = 64;
 std::atomic<int> g_sm_count[kMaxDevices];
+std::atomic<int> g_options[SGB_OPT_COUNT_];
+struct OptionDefaults {
+  OptionDefaults() { g_options[SGB_OPT_OVERLAP_LAUNCHES].store(1); }
+} g_option_defaults;
 }  // namespace
+
+int option(int which) {
+  return which > 0 && which < SGB_OPT_COUNT_ ? g_options[which].load(std::memory_order_relaxed) : 0;
+}
 
 int note_cuda_error(cudaError_t e) {
   g_last_cuda_error.store(static_cast<int>(e));
@@ -47,6 +55,14 @@ const char* sgb_status_string(int status) {
 
 int sgb_last_cuda_error(void) { return sgb::g_last_cuda_error.load(); }
 
-int sgb_version(void) { return 100; }
+int sgb_version(void) { return 110; }
+
+int sgb_set_option(int option, int value) {
+  if (option <= 0 || option >= SGB_OPT_COUNT_) return SGB_ERR_UNSUPPORTED;
+  sgb::g_options[option].store(value);
+  return SGB_OK;
+}
+
+int sgb_get_option(int option) { return sgb::option(option); }
 
 }  // extern "C"

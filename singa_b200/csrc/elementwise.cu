@@ -35,6 +35,7 @@ ew_vec_kernel(F f, const uint4* __restrict__ a, const uint4* __restrict__ b,
               const uint4* __restrict__ c, uint4* __restrict__ out, size_t nvec,
               int lanes) {
   const size_t tile = static_cast<size_t>(kBlock) * kUnroll;
+  dependency_wait();
   for (size_t base = blockIdx.x * tile; base < nvec; base += gridDim.x * tile) {
     uint4 va[kUnroll], vb[kUnroll], vc[kUnroll];
 #pragma unroll
@@ -46,6 +47,7 @@ ew_vec_kernel(F f, const uint4* __restrict__ a, const uint4* __restrict__ b,
         if (IN >= 3) vc[u] = ld128(c + i);
       }
     }
+    if (base + gridDim.x * tile >= nvec) release_dependents();   // last tile of this CTA: only stores remain
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const size_t i = base + u * kBlock + threadIdx.x;
@@ -90,9 +92,10 @@ int run(F f, const TA* a, const TB* b, const TC* c, TO* out, size_t n,
   if (vec_ok && n >= static_cast<size_t>(lanes)) {
     const size_t nvec = n / lanes;
     unsigned grid = oneshot_grid(nvec);
-    ew_vec_kernel<IN, F><<<grid, kBlock, 0, s>>>(
-        f, reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b),
-        reinterpret_cast<const uint4*>(c), reinterpret_cast<uint4*>(out), nvec, lanes);
+    const int st = launch_ex(ew_vec_kernel<IN, F>, dim3(grid), dim3(kBlock), 0, s, 0, true, f,
+                             reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b),
+                             reinterpret_cast<const uint4*>(c), reinterpret_cast<uint4*>(out), nvec, lanes);
+    if (st != SGB_OK) return st;
     done = nvec * lanes;
   }
   if (done < n) {
