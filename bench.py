@@ -475,7 +475,7 @@ def main():
     from singa_b200 import _lib
     from singa_b200.communicator import Communicator, NcclIdHolder
     from singa_b200.hot_path import HotPathGPU
-    from singa_b200.resnet50_path import add_wgrad_refresh, algorithmic_bytes, build_plan, fuse_plan
+    from singa_b200.resnet50_path import add_wgrad_refresh, algorithmic_bytes, build_plan, fuse_plan, mask_plan
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback "
@@ -503,6 +503,8 @@ def main():
         plan = build_plan(batch=BATCH, fused=False)        # the reference's call sequence ...
         if fused:
             plan = fuse_plan(plan)                         # ... rewritten by the peephole pass
+        if args.relu_mask:
+            plan = mask_plan(plan)                         # ReLU decisions from the forward partner's bit record
         plan = add_wgrad_refresh(plan)                     # the contractions' weight gradients are rewritten every step
         hp = HotPathGPU(plan, communicator=communicator, world=world, seed=1000 + rank, dist_option=dist_option,
                         pool_argmax=args.pool_argmax)
@@ -737,6 +739,7 @@ def kernel_launches(path):
     samples) exceeds what a cluster of eight CTAs can stage (8 x 100 KB): then
     it is the reduce + apply pair."""
     per = {"sgb_relu_backward_f32": 1, "sgb_add_relu_backward_f32": 1, "sgb_binary_f32": 1,
+           "sgb_relu_backward_mask_f32": 1, "sgb_add_relu_backward_mask_f32": 1,
            "sgb_maxpool_backward_f32": 1, "sgb_maxpool_backward_argmax_f32": 1,
            "sgb_avgpool_backward_f32": 1, "sgb_softmax_rows_f32": 1, "sgb_cross_entropy_f32": 1,
            "sgb_sum_all_f32": 1, "sgb_softmax_cross_entropy_bwd_f32": 1,
@@ -744,7 +747,8 @@ def kernel_launches(path):
            "sgb_scalar_f32": 1, "sgb_sum_rows_f32": 1, "sgb_set_f32": 1}
     n = 0
     for name, args in path.calls:
-        if name in ("sgb_bn_backward_f32", "sgb_bn_relu_backward_f32", "sgb_bn_add_relu_backward_f32"):
+        if name in ("sgb_bn_backward_f32", "sgb_bn_relu_backward_f32", "sgb_bn_relu_backward_mask_f32",
+                    "sgb_bn_add_relu_backward_f32"):
             N, _, HW = args[-6:-3]          # (..., N, C, HW, workspace, workspace bytes, stream)
             n += 2 if N * HW * 8 > 8 * 100 * 1024 else 1
         elif name == "sgb_unpack_f32":       # stand-in weight gradients: one launch per 72 tensors

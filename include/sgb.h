@@ -50,8 +50,22 @@ int sgb_version(void);
  * kernel's CTAs are scheduled while the previous kernel of the same stream
  * drains; each such kernel waits for its predecessors' completion before its
  * first access to global memory, so results and stream-order semantics are
- * unchanged.  0 restores plain launches. */
-enum sgb_option { SGB_OPT_OVERLAP_LAUNCHES = 1, SGB_OPT_COUNT_ = 2 };
+ * unchanged.  0 restores plain launches.
+ * SGB_OPT_STABLE_FORWARD_INPUTS (default 0): a promise by the caller about the
+ * batch-norm backward entry points: x, the ReLU input, scale, mean and the
+ * inverse standard deviation were written before the PREVIOUS kernel of the
+ * stream started (they are tensors the forward pass saved - true of every call
+ * an autograd backward pass makes).  With launch overlap on, the kernels then
+ * read those tensors while the previous kernel drains and wait only before
+ * they read dy.  Leave it 0 when a forward-side input may have been produced
+ * by the kernel just before.
+ * SGB_OPT_BN_CLUSTER_SIZE (default 0 = chosen per shape): forces the number of
+ * CTAs that share one channel in the single-pass batch-norm kernels (1..16,
+ * used when a channel fits that many CTAs' shared memory); for tuning. */
+enum sgb_option {
+  SGB_OPT_OVERLAP_LAUNCHES = 1, SGB_OPT_STABLE_FORWARD_INPUTS = 2,
+  SGB_OPT_BN_CLUSTER_SIZE = 3, SGB_OPT_COUNT_ = 4
+};
 int sgb_set_option(int option, int value);
 int sgb_get_option(int option);
 
@@ -77,6 +91,25 @@ int sgb_relu_backward_f16(const void *dy, const void *x, void *dx, size_t n,
 int sgb_add_relu_backward_f32(const float *dy_a, const float *dy_b,
                               const float *x, float *dx, size_t n,
                               void *stream);
+
+/* ReLU with a one-bit-per-element record - a forward partner (it changes what
+ * the backward pass consumes, so it is opt-in): y = max(x, 0) and bit i & 31
+ * of 32-bit word i >> 5 of `mask` = (x[i] > 0), the rule of cuda::relubackward
+ * (math_kernel.cu:253-259).  `mask` holds sgb_relu_mask_bytes(n) bytes, 4-byte
+ * aligned.  The three backward forms read the record instead of the stored
+ * input (1/32 of its bytes) and give bit-identical results:
+ *   relu_backward_mask      dx = bit ? dy : 0
+ *   add_relu_backward_mask  dx = bit ? dy_a + dy_b : 0      (join + ReLU)
+ *   bn_relu_backward_mask   batch-norm backward of dy masked by the record
+ *                           (declared with the batch-norm functions). */
+size_t sgb_relu_mask_bytes(size_t n);
+int sgb_relu_forward_mask_f32(const float *x, float *y, void *mask, size_t n,
+                              void *stream);
+int sgb_relu_backward_mask_f32(const float *dy, const void *mask, float *dx,
+                               size_t n, void *stream);
+int sgb_add_relu_backward_mask_f32(const float *dy_a, const float *dy_b,
+                                   const void *mask, float *dx, size_t n,
+                                   void *stream);
 
 /* ----------------------------------------------------- elementwise families */
 /* out = a (op) b, tensor (op) tensor.  Replaces singa::cuda::add/sub/mult/
@@ -353,6 +386,14 @@ int sgb_bn_backward_noalloc_f32(const float *x, const float *dy,
 /* Same with the backward of the ReLU that follows the BN layer folded in:
  * dy is first masked by relu_in > 0 (relu_in = the tensor ReLU stored, i.e.
  * the BN output).  Equals ReLUBackward + GpuBatchNormBackward bit for bit. */
+/* As sgb_bn_relu_backward_f32 with the ReLU decisions taken from the bit
+ * record of sgb_relu_forward_mask_f32 (element order of the NCHW tensor). */
+int sgb_bn_relu_backward_mask_f32(const float *x, const float *dy,
+                                  const void *relu_mask, const float *scale,
+                                  const float *mean, const float *invstd,
+                                  float *dx, float *dscale, float *dbias, int N,
+                                  int C, int HW, void *ws, size_t ws_bytes,
+                                  void *stream);
 int sgb_bn_relu_backward_f32(const float *x, const float *dy,
                              const float *relu_in, const float *scale,
                              const float *mean, const float *invstd, float *dx,
@@ -503,6 +544,13 @@ int sgb_comm_create_ex(sgb_comm **out, int rank, int world,
  * use the registered-buffer protocols.  Deregistered by sgb_comm_destroy; the
  * buffer must outlive the communicator. */
 int sgb_comm_register(sgb_comm *c, void *buffer, size_t bytes);
+/* Makes the communicator issue its work on three CALLER-OWNED streams instead
+ * of the ones it created: the reference's communicator takes s, c1 and c2 from
+ * the device Context (src/core/device/cuda_gpu.cc:76-80), and its per-operation
+ * time profiling records events on exactly those streams.  The three streams
+ * must be distinct and must outlive the communicator; SGB_ERR_STATE while work
+ * staged or enqueued since the last sgb_comm_wait is pending. */
+int sgb_comm_use_streams(sgb_comm *c, void *s, void *c1, void *c2);
 int sgb_comm_destroy(sgb_comm *c);
 int sgb_comm_rank(const sgb_comm *c);
 int sgb_comm_world_size(const sgb_comm *c);

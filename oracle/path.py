@@ -25,11 +25,15 @@ class OraclePath(object):
             a, k = op.args, op.kind
             if k == "relu_bwd":
                 t[a["dx"]][...] = cpu.relu_backward(t[a["dy"]], t[a["x"]])
+            elif k == "relu_mask_bwd":        # the bit record encodes x > 0: recompute it from the input
+                t[a["dx"]][...] = cpu.relu_backward(t[a["dy"]], t[a["x_ref"]])
             elif k == "add_relu_bwd":
                 t[a["dx"]][...] = cpu.relu_backward(t[a["dy_a"]] + t[a["dy_b"]], t[a["x"]])
+            elif k == "add_relu_mask_bwd":
+                t[a["dx"]][...] = cpu.relu_backward(t[a["dy_a"]] + t[a["dy_b"]], t[a["x_ref"]])
             elif k == "add_out":
                 t[a["out"]][...] = t[a["a"]] + t[a["b"]]
-            elif k in ("bn_bwd", "bn_relu_bwd", "bn_add_relu_bwd"):
+            elif k in ("bn_bwd", "bn_relu_bwd", "bn_relu_mask_bwd", "bn_add_relu_bwd"):
                 if k == "bn_add_relu_bwd":
                     t[a["joined"]][...] = cpu.relu_backward(t[a["dy_a"]] + t[a["dy_b"]], t[a["relu_x"]])
                     dy = t[a["joined"]]
@@ -37,6 +41,8 @@ class OraclePath(object):
                     dy = t[a["dy"]]
                 if k == "bn_relu_bwd":
                     dy = cpu.relu_backward(dy, t[a["relu_x"]])
+                if k == "bn_relu_mask_bwd":
+                    dy = cpu.relu_backward(dy, t[a["x_ref"]])
                 dx, ds, db = cpu.bn_backward(dy, t[a["x"]], t[a["scale"]], t[a["mean"]], t[a["invstd"]])
                 t[a["dx"]][...] = dx
                 t[a["dscale"]][...] = ds
@@ -118,6 +124,8 @@ def make_tensors(plan, seed=0):
                 t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(0.05)
         elif k in ("pgrad", "wsyn"):
             t[name] = rng.standard_normal(spec.shape, dtype=np.float32) * np.float32(1e-3)
+        elif k == "mask":
+            continue                              # the CPU checker recomputes the decisions from the input
         else:
             t[name] = np.zeros(spec.shape, np.float32)
     for name in list(T):

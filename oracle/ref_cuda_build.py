@@ -63,7 +63,7 @@ def _includes():
 
 def _cxx(src, obj, extra=()):
     cmd = ["g++", "-std=c++14", "-O2", "-fopenmp", "-fPIC", "-w", "-include", "cstring", "-include", "cstdint",
-           "-include", os.path.join(SHIMS_CUDA, "saxpyi_compat.h")] + _includes() + list(extra) + ["-c", src, "-o", obj]
+           "-include", os.path.join(SHIMS_CUDA, "saxpyi_compat.h")] + list(extra) + _includes() + ["-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("g++ failed for %s:\n%s" % (src, r.stderr[-4000:]))
@@ -92,7 +92,8 @@ def build_variant(variant, force=False):
     mine = []
     if variant == "sgb":
         mine = [os.path.join(ADAPTER, f) for f in ("tensor_math_cuda.h", "tensor_with_sgb_backend.cc",
-                                                   "operations.cc", "communicator.cc", "communicator.h")]
+                                                   "operations.cc", "communicator.cc",
+                                                   os.path.join("singa", "io", "communicator.h"))]
         mine += [os.path.join(PKG, "libsgb.so"), os.path.join(PKG, "libsgb_singa.so")]
     deps = [ref(s) for s in CORE] + [ref("src/core/tensor/tensor.cc"), doors] + shim_files + mine
     if not force and not _stale(lib, deps):
@@ -111,7 +112,7 @@ def build_variant(variant, force=False):
     jobs.append((_cxx, ref("src/model/operation/batchnorm.cc"), obj("batchnorm"),
                  ("-DGpuBatchNormBackward=GpuBatchNormBackward_reference",) if variant == "sgb" else ()))
     jobs.append((_cxx, doors, obj("doors"),
-                 ("-I", ADAPTER, "-DSGB_ADAPTER_COMMUNICATOR") if variant == "sgb" else ()))
+                 ("-I", ADAPTER, "-DSGB_VARIANT") if variant == "sgb" else ()))
     if variant == "reference":
         jobs.append((_cxx, ref("src/core/tensor/tensor.cc"), obj("tensor"), ()))
         jobs.append((_cxx, ref("src/io/communicator.cc"), obj("communicator"), ()))

@@ -21,6 +21,9 @@
 #include "singa/io/communicator.h"
 #include "model/operation/batchnorm.h"
 #include "model/operation/pooling.h"
+#ifdef SGB_VARIANT
+#include "model/operation/convolution.h"
+#endif
 
 using singa::Shape;
 using singa::Tensor;
@@ -157,6 +160,21 @@ void* rs_pool_forward(void* h, void* x) {
 void* rs_pool_backward(void* h, void* dy, void* x, void* y) {
   return own(singa::GpuPoolingBackward(*static_cast<singa::CudnnPoolingHandle*>(h), T(dy), T(x), T(y)));
 }
+
+#ifdef SGB_VARIANT
+// Bias gradient of a convolution.  Only in the build with this repository's
+// back end: the reference's convolution.cc does not compile against cuDNN 9,
+// so no handle can be constructed; the replacement never reads the handle, and
+// a zeroed stand-in object is passed by reference.
+void* rs_conv_bias_backward(void* dy, void* b) {
+  alignas(16) static unsigned char storage[sizeof(singa::CudnnConvHandle)] = {};
+  const singa::CudnnConvHandle& fake = *reinterpret_cast<const singa::CudnnConvHandle*>(storage);
+  return own(singa::GpuConvBackwardb(T(dy), T(b), fake));
+}
+int rs_variant() { return 1; }
+#else
+int rs_variant() { return 0; }
+#endif
 
 // ------------------------------------------------------------- communicator
 int rs_nccl_id_bytes() { return static_cast<int>(sizeof(ncclUniqueId)); }

@@ -64,6 +64,30 @@ struct UnitWalk {
   }
 };
 
+// How the fused ReLU backward learns which gradients to keep.  MASK 0: no ReLU.
+// MASK 1: from the ReLU's stored input (keep where it is > 0).  MASK 2: from the
+// forward partner's record, one bit per element in element order (bit i & 7 of
+// byte i >> 3; 1 = the input was > 0), passed through the same pointer.
+// `off` is the element offset; for the 4-wide forms it is a multiple of 4.
+template <int MASK>
+__device__ __forceinline__ unsigned keep4(const float* relu_in, size_t off) {
+  if (MASK == 2) {
+    const unsigned char b = reinterpret_cast<const unsigned char*>(relu_in)[off >> 3];
+    return (b >> (off & 4)) & 15u;
+  }
+  Vec4f v;
+  v.u = ld128(relu_in + off);
+  unsigned bits = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) bits |= (v.f[k] > 0 ? 1u : 0u) << k;
+  return bits;
+}
+template <int MASK>
+__device__ __forceinline__ bool keep1(const float* relu_in, size_t off) {
+  if (MASK == 2) return (reinterpret_cast<const unsigned char*>(relu_in)[off >> 3] >> (off & 7)) & 1u;
+  return relu_in[off] > 0;
+}
+
 __host__ __device__ inline int bn_slices_for(long long per_channel, int C, int sms) {
   long long s = (static_cast<long long>(sms) * 16 + C - 1) / C;
   const long long max_s = (per_channel + 2047) / 2048;  // >= 2048 elements per slice
@@ -72,7 +96,7 @@ __host__ __device__ inline int bn_slices_for(long long per_channel, int C, int s
   return static_cast<int>(s < 1 ? 1 : s);
 }
 
-template <bool VEC, bool MASK>
+template <bool VEC, int MASK>
 __global__ void __launch_bounds__(kBlock)
 bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                      const float* __restrict__ relu_in, const float* __restrict__ mean,
@@ -88,14 +112,15 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     UnitWalk w(i0 + threadIdx.x, kBlock, hw4);
     for (int i = i0 + threadIdx.x; i < i1; i += kBlock, w.next()) {
       const size_t off = (static_cast<size_t>(w.n) * sh.C + c) * sh.HW + 4 * w.q;
-      Vec4f vx, vg, vm;
+      Vec4f vx, vg;
       vx.u = ld128(x + off);
       vg.u = ld128(dy + off);
-      if (MASK) vm.u = ld128(relu_in + off);
+      unsigned bits = 15u;
+      if (MASK) bits = keep4<MASK>(relu_in, off);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float g = vg.f[k];
-        if (MASK) g = vm.f[k] > 0 ? g : 0.0f;
+        if (MASK) g = (bits >> k) & 1u ? g : 0.0f;
         s_dy += g;
         s_dyx += g * (vx.f[k] - mu);
       }
@@ -107,7 +132,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       const int n = i / sh.HW, q = i - n * sh.HW;
       const size_t off = (static_cast<size_t>(n) * sh.C + c) * sh.HW + q;
       float g = dy[off];
-      if (MASK) g = relu_in[off] > 0 ? g : 0.0f;
+      if (MASK) g = keep1<MASK>(relu_in, off) ? g : 0.0f;
       s_dy += g;
       s_dyx += g * (x[off] - mu);
     }
@@ -124,7 +149,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
 // per CTA make them cheaper per byte.
 constexpr int kApplyUnits = 4;
 
-template <bool VEC, bool MASK>
+template <bool VEC, int MASK>
 __global__ void __launch_bounds__(kBlock)
 bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                     const float* __restrict__ relu_in, const float* __restrict__ scale,
@@ -153,11 +178,11 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       if (VEC) {
         vx[j].u = ld128(x + off[j]);
         vg[j].u = ld128(dy + off[j]);
-        if (MASK) vm[j].u = ld128(relu_in + off[j]);
+        if (MASK) vm[j].i[0] = static_cast<int>(keep4<MASK>(relu_in, off[j]));
       } else {
         vx[j].f[0] = x[off[j]];
         vg[j].f[0] = dy[off[j]];
-        if (MASK) vm[j].f[0] = relu_in[off[j]];
+        if (MASK) vm[j].i[0] = keep1<MASK>(relu_in, off[j]) ? 1 : 0;
       }
       w.next();
     }
@@ -197,13 +222,13 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float g = vg[j].f[i];
-        if (MASK) g = vm[j].f[i] > 0 ? g : 0.0f;
+        if (MASK) g = (vm[j].i[0] >> i) & 1 ? g : 0.0f;
         o.f[i] = k * (g - a - (vx[j].f[i] - mu) * b);
       }
       st128(dx + off[j], o.u);
     } else {
       float g = vg[j].f[0];
-      if (MASK) g = vm[j].f[0] > 0 ? g : 0.0f;
+      if (MASK) g = vm[j].i[0] & 1 ? g : 0.0f;
       dx[off[j]] = k * (g - a - (vx[j].f[0] - mu) * b);
     }
   }
@@ -228,14 +253,15 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // the ReLU input; it is formed while staging, kept in shared memory for the
 // two later phases and ALSO written to `joined` for the other consumers of the
 // join (the shortcut branch), which replaces a separate join+ReLU kernel.
-template <bool VEC, bool MASK, int T, bool ADD = false>
+template <bool VEC, int MASK, int T, bool ADD = false>
 __global__ void __launch_bounds__(T)
 bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ relu_in, const float* __restrict__ scale,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       float* __restrict__ dx, float* __restrict__ dscale,
                       float* __restrict__ dbias, BnShape sh, int per_cta,
-                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
+                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr,
+                      int early = 0) {
   extern __shared__ __align__(16) float stage[];
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
@@ -253,7 +279,12 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   float* sg = stage + static_cast<size_t>(per_cta) * kW;
   const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
   const size_t chan_off = static_cast<size_t>(c) * sh.HW;
-  dependency_wait();                                  // first access to global memory follows
+  // `early`: the caller vouches that x, the ReLU input and the per-channel
+  // statistics were written before the previous kernel of the stream started
+  // (they are tensors saved by the forward pass), so they may be read while
+  // that kernel drains; only dy waits for it.
+  const bool prefetch = VEC && !ADD && early != 0;
+  if (!prefetch) dependency_wait();                   // first access to global memory follows
   const float mu = mean[c];
 
   // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
@@ -290,6 +321,10 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         }
       }
     }
+  } else if (prefetch) {
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1; u += T, w.next())
+      cp_async16(sx + (u - u0) * 4, x + (w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4));
   } else {
     UnitWalk w(first, T, hwu);
     for (int u = first; u < u1; u += T, w.next()) {
@@ -300,16 +335,30 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         cp_async16(sg + l, dy + off);
       } else {
         float g = dy[off];
-        if (MASK) g = relu_in[off] > 0 ? g : 0.0f;
+        if (MASK) g = keep1<MASK>(relu_in, off) ? g : 0.0f;
         sx[l] = x[off];
         sg[l] = g;
       }
     }
   }
+  if (prefetch) {
+    dependency_wait();                                // the gradient is the previous kernel's output
+    UnitWalk w(first, T, hwu);
+    for (int u = first; u < u1; u += T, w.next())
+      cp_async16(sg + (u - u0) * 4, dy + (w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4));
+  }
   // fused ReLU: while the copies fly, read the ReLU input and keep only the
   // sign decisions, 4 bits per unit (a share is at most 16 units per thread)
   unsigned long long keep = 0;
-  if (VEC && MASK && !ADD) {
+  if (VEC && MASK == 2 && !ADD) {
+    // bit record: one byte holds the decisions of two units
+    UnitWalk w(first, T, hwu);
+    int slot = 0;
+    for (int u = first; u < u1; u += T, w.next(), slot += 4) {
+      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4;
+      keep |= static_cast<unsigned long long>(keep4<2>(relu_in, off)) << slot;
+    }
+  } else if (VEC && MASK && !ADD) {
     UnitWalk w(first, T, hwu);
     int slot = 0;
     for (int u = first; u < u1;) {
@@ -439,7 +488,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
 // bytes of shared memory) with 16-byte copies, reduces every channel with a
 // sub-group of its threads from shared memory, overwrites the staged dy with
 // dx in place and streams it back with 16-byte stores.
-template <bool MASK, int G>
+template <int MASK, int G>
 __global__ void __launch_bounds__(kBlock)
 bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                     const float* __restrict__ relu_in, const float* __restrict__ scale,
@@ -464,7 +513,8 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     // x by asynchronous copy; dy and the ReLU input through registers, four
     // units (eight independent 16-byte loads) per round
     for (int u = threadIdx.x; u < units;) {
-      Vec4f vg[4], vm[4];
+      Vec4f vg[4];
+      unsigned bits[4];
       int us[4], cnt = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -472,7 +522,7 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
           const size_t off = wl.n * sample_stride + base + 4 * static_cast<size_t>(wl.q);
           cp_async16(sx + 4 * u, x + off);
           vg[j].u = ld128(dy + off);
-          vm[j].u = ld128(relu_in + off);
+          bits[j] = keep4<MASK>(relu_in, off);
           us[j] = u;
           u += kBlock;
           wl.next();
@@ -483,7 +533,7 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       for (int j = 0; j < 4; ++j) {
         if (j < cnt) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) vg[j].f[k] = vm[j].f[k] > 0 ? vg[j].f[k] : 0.0f;
+          for (int k = 0; k < 4; ++k) vg[j].f[k] = (bits[j] >> k) & 1u ? vg[j].f[k] : 0.0f;
           *reinterpret_cast<uint4*>(sg + 4 * us[j]) = vg[j].u;
         }
       }
@@ -558,7 +608,7 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   }
 }
 
-template <bool MASK, int G>
+template <int MASK, int G>
 int launch_group(const float* x, const float* dy, const float* relu_in, const float* scale,
                  const float* mean, const float* invstd, float* dx, float* dscale, float* dbias,
                  BnShape sh, cudaStream_t s) {
@@ -578,16 +628,19 @@ int launch_group(const float* x, const float* dy, const float* relu_in, const fl
 
 // Cluster size (1, 2, 4 or 8) and per-CTA share for the single-pass kernel;
 // returns 0 when a channel does not fit 8 CTAs' shared memory.
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : dflt;
-}
-
 int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int channels) {
-  static const int share_kb = env_int("SGB_BN_SHARE_KB", 50);     // preferred staging per CTA
-  static const int max_cs = env_int("SGB_BN_MAX_CLUSTER", 8);     // 16 = non-portable cluster size
-  static const int fill = env_int("SGB_BN_FILL_CTAS_PER_SM", 0);  // >0: split small channels further (measured slower on B200)
+  constexpr int share_kb = 50;   // preferred staging per CTA
+  constexpr int max_cs = 8;      // portable cluster size
+  constexpr int fill = 0;        // >0 would split small channels further (measured slower on B200)
   const long long kPreferred = share_kb * 1024LL, kLimit = 100 * 1024;
+  const int forced = option(SGB_OPT_BN_CLUSTER_SIZE);
+  if (forced > 0 && forced <= 16) {
+    const long long share = (units_per_channel + forced - 1) / forced;
+    if (share * unit_bytes * 2 <= kLimit && share <= 8192) {
+      *per_cta = static_cast<int>(share);
+      return forced;
+    }
+  }
   for (int pass = 0; pass < 2; ++pass) {
     const long long cap = pass == 0 ? kPreferred : kLimit;
     for (int cs = 1; cs <= max_cs; cs *= 2) {
@@ -610,7 +663,7 @@ int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int 
   return 0;
 }
 
-template <bool VEC, bool MASK, int T, bool ADD = false>
+template <bool VEC, int MASK, int T, bool ADD = false>
 int launch_cluster_t(const float* x, const float* dy, const float* relu_in, const float* scale,
                      const float* mean, const float* invstd, float* dx, float* dscale,
                      float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s,
@@ -632,10 +685,11 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
     attr_set[dev] = true;
   }
   return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
-                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined);
+                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined,
+                   option(SGB_OPT_STABLE_FORWARD_INPUTS) && option(SGB_OPT_OVERLAP_LAUNCHES) ? 1 : 0);
 }
 
-template <bool VEC, bool MASK>
+template <bool VEC, int MASK>
 int launch_cluster(const float* x, const float* dy, const float* relu_in, const float* scale,
                    const float* mean, const float* invstd, float* dx, float* dscale,
                    float* dbias, BnShape sh, int cs, int per_cta, cudaStream_t s) {
@@ -681,7 +735,7 @@ int bn_add_relu_backward(const float* x, const float* dy_a, const float* dy_b, c
                          float* dx, float* dscale, float* dbias, int N, int C, int HW, void* ws,
                          size_t ws_bytes, void* stream);
 
-template <bool MASK>
+template <int MASK>
 int bn_backward(const float* x, const float* dy, const float* relu_in, const float* scale,
                 const float* mean, const float* invstd, float* dx, float* dscale,
                 float* dbias, int N, int C, int HW, void* ws, size_t ws_bytes, void* stream) {
@@ -699,9 +753,9 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
     return launch_status();
   }
   const bool vec = (HW % 4 == 0) && aligned16(x) && aligned16(dy) && aligned16(dx) &&
-                   (!MASK || aligned16(relu_in));
+                   (MASK != 1 || aligned16(relu_in));
   const BnShape sh{N, C, HW};
-  if (!vec && HW > 1 && aligned16(x) && aligned16(dy) && aligned16(dx) && (!MASK || aligned16(relu_in))) {
+  if (!vec && HW > 1 && aligned16(x) && aligned16(dy) && aligned16(dx) && (MASK != 1 || aligned16(relu_in))) {
     // odd planes: groups of adjacent channels make 16-byte runs (7x7 layers)
     const int G = (HW % 2) ? 4 : 2;
     if ((HW * G) % 4 == 0 && C % G == 0 && static_cast<long long>(G) * per_channel * 8 <= 100 * 1024) {
@@ -772,8 +826,8 @@ int bn_add_relu_backward(const float* x, const float* dy_a, const float* dy_b, c
   }
   int st = sgb_add_relu_backward_f32(dy_a, dy_b, relu_in, joined, static_cast<size_t>(N) * C * HW, stream);
   if (st != SGB_OK) return st;
-  return bn_backward<false>(x, joined, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW, ws,
-                            ws_bytes, stream);
+  return bn_backward<0>(x, joined, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW, ws,
+                        ws_bytes, stream);
 }
 
 // ------------------------------------------------------------ forward (training)
@@ -1089,8 +1143,8 @@ size_t sgb_bn_backward_workspace_bytes(int N, int C, int HW) {
 int sgb_bn_backward_f32(const float* x, const float* dy, const float* scale, const float* mean,
                         const float* invstd, float* dx, float* dscale, float* dbias, int N,
                         int C, int HW, void* ws, size_t ws_bytes, void* stream) {
-  return bn_backward<false>(x, dy, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
-                            ws, ws_bytes, stream);
+  return bn_backward<0>(x, dy, nullptr, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
+                        ws, ws_bytes, stream);
 }
 
 int sgb_bn_add_relu_backward_f32(const float* x, const float* dy_a, const float* dy_b,
@@ -1116,12 +1170,20 @@ int sgb_bn_backward_noalloc_f32(const float* x, const float* dy, const float* sc
   return bn_backward_static(x, dy, scale, mean, invstd, dx, dscale, dbias, N, C, HW, stream);
 }
 
+int sgb_bn_relu_backward_mask_f32(const float* x, const float* dy, const void* relu_mask,
+                                  const float* scale, const float* mean, const float* invstd,
+                                  float* dx, float* dscale, float* dbias, int N, int C, int HW,
+                                  void* ws, size_t ws_bytes, void* stream) {
+  return bn_backward<2>(x, dy, static_cast<const float*>(relu_mask), scale, mean, invstd, dx, dscale, dbias, N, C,
+                        HW, ws, ws_bytes, stream);
+}
+
 int sgb_bn_relu_backward_f32(const float* x, const float* dy, const float* relu_in,
                              const float* scale, const float* mean, const float* invstd,
                              float* dx, float* dscale, float* dbias, int N, int C, int HW,
                              void* ws, size_t ws_bytes, void* stream) {
-  return bn_backward<true>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
-                           ws, ws_bytes, stream);
+  return bn_backward<1>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, N, C, HW,
+                        ws, ws_bytes, stream);
 }
 
 }  // extern "C"

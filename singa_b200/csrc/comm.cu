@@ -74,6 +74,7 @@ struct sgb_comm {
   int* nnz_host = nullptr;     // pinned, world entries
   int topk_mode = 1;           // 1 = the reference comparator's key, 0 = |value|
   cudaStream_t s = nullptr, c1 = nullptr, c2 = nullptr;
+  bool own_streams = true;     // false after sgb_comm_use_streams: the caller's streams are not destroyed
   cudaEvent_t ev_compute = nullptr, ev_c1 = nullptr, ev_s = nullptr, ev_c2 = nullptr,
               ev_c2_done = nullptr, ev_host = nullptr;
   size_t send_off = 0;         // elements staged since the last flush
@@ -339,8 +340,27 @@ int sgb_comm_destroy(sgb_comm* c) {
     if (e) cudaEventDestroy(e);
   cudaStream_t ss[] = {c->s, c->c1, c->c2};
   for (cudaStream_t st : ss)
-    if (st) cudaStreamDestroy(st);
+    if (st && c->own_streams) cudaStreamDestroy(st);
   delete c;
+  return SGB_OK;
+}
+
+int sgb_comm_use_streams(sgb_comm* c, void* s, void* c1, void* c2) {
+  if (!c || !s || !c1 || !c2) return SGB_ERR_NULL;
+  if (s == c1 || s == c2 || c1 == c2) return SGB_ERR_UNSUPPORTED;
+  if (c->order.dirty_s || c->order.dirty_c1 || c->order.dirty_c2 || !c->pend_ptrs.empty()) return SGB_ERR_STATE;
+  if (c->own_streams) {
+    cudaStream_t ss[] = {c->s, c->c1, c->c2};
+    for (cudaStream_t st : ss)
+      if (st) {
+        CU(cudaStreamSynchronize(st));
+        CU(cudaStreamDestroy(st));
+      }
+  }
+  c->s = sgb::as_stream(s);
+  c->c1 = sgb::as_stream(c1);
+  c->c2 = sgb::as_stream(c2);
+  c->own_streams = false;
   return SGB_OK;
 }
 

@@ -491,6 +491,143 @@ int sgb_add_relu_backward_f32(const float* dy_a, const float* dy_b, const float*
       F32<EAddReluBwd>{EAddReluBwd{0.f, 0.f}}, dy_a, dy_b, x, dx, n, stream);
 }
 
+}  // extern "C"
+
+namespace sgb {
+namespace {
+// ---------------------------------------------- ReLU with a one-bit record
+// Forward partner of the ReLU backward kernels: besides y = max(x, 0) it
+// leaves one bit per element (1 = x > 0) in element order - bit i & 31 of
+// 32-bit word i >> 5 - so that the backward pass reads 1/32 of the bytes the
+// stored input would cost.  A thread turns its four comparisons into a
+// nibble; the eight lanes that own one word combine theirs with three
+// shuffles and one of them stores the word.
+__global__ void __launch_bounds__(kBlock)
+relu_fwd_mask_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, uint32_t* __restrict__ mask,
+                     size_t nvec) {
+  const size_t tile = static_cast<size_t>(kBlock) * kUnroll;
+  const size_t base = blockIdx.x * tile;
+  dependency_wait();
+  Vec4f v[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const size_t i = base + u * kBlock + threadIdx.x;
+    v[u].u = make_uint4(0, 0, 0, 0);
+    if (i < nvec) v[u].u = ld128(x + i);
+  }
+  release_dependents();
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const size_t i = base + u * kBlock + threadIdx.x;      // i & 7 == lane & 7: tiles are multiples of 8
+    unsigned nib = 0;
+    Vec4f o;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool keep = v[u].f[k] > 0;
+      nib |= (keep ? 1u : 0u) << k;
+      o.f[k] = keep ? v[u].f[k] : 0.0f;
+    }
+    unsigned word = nib << (4 * (threadIdx.x & 7));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    word |= __shfl_xor_sync(0xffffffffu, word, 4);
+    if (i < nvec) {
+      st128(y + i, o.u);
+      if ((threadIdx.x & 7) == 0) mask[i >> 3] = word;
+    }
+  }
+}
+
+// Elements [first, n): one thread per mask word (used for unaligned buffers and
+// for the last n % 4 elements, whose word the vector kernel has already
+// written with zeros in those positions).
+__global__ void relu_fwd_mask_tail_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                          uint32_t* __restrict__ mask, size_t first, size_t n) {
+  const size_t w = (first >> 5) + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  const size_t lo = w << 5;
+  if (lo >= n) return;
+  unsigned word = lo < first ? mask[w] : 0u;
+  for (size_t i = lo < first ? first : lo; i < n && i < lo + 32; ++i) {
+    const float v = x[i];
+    const bool keep = v > 0;
+    y[i] = keep ? v : 0.0f;
+    word |= (keep ? 1u : 0u) << (i & 31);
+  }
+  mask[w] = word;
+}
+
+// dx = bit ? dy : 0 and dx = bit ? dy_a + dy_b : 0 from the record above.
+struct FReluBwdMask {
+  const unsigned char* m;
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4, uint4, size_t i0) const {
+    const unsigned nib = (m[i0 >> 3] >> (i0 & 4)) & 15u;
+    Vec4f x, o;
+    x.u = a;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.f[k] = (nib >> k) & 1u ? x.f[k] : 0.0f;
+    return o.u;
+  }
+  __device__ __forceinline__ float one(float a, float, float, size_t i) const {
+    return (m[i >> 3] >> (i & 7)) & 1u ? a : 0.0f;
+  }
+};
+struct FAddReluBwdMask {
+  const unsigned char* m;
+  __device__ __forceinline__ uint4 vec(uint4 a, uint4 b, uint4, size_t i0) const {
+    const unsigned nib = (m[i0 >> 3] >> (i0 & 4)) & 15u;
+    Vec4f x, y, o;
+    x.u = a;
+    y.u = b;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.f[k] = (nib >> k) & 1u ? (x.f[k] + y.f[k]) : 0.0f;
+    return o.u;
+  }
+  __device__ __forceinline__ float one(float a, float b, float, size_t i) const {
+    return (m[i >> 3] >> (i & 7)) & 1u ? (a + b) : 0.0f;
+  }
+};
+}  // namespace
+}  // namespace sgb
+
+extern "C" {
+using namespace sgb;
+
+size_t sgb_relu_mask_bytes(size_t n) { return 4 * ((n + 31) / 32); }
+
+int sgb_relu_forward_mask_f32(const float* x, float* y, void* mask, size_t n, void* stream) {
+  if (n == 0) return SGB_OK;
+  if (!x || !y || !mask) return SGB_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(mask) & 3u) return SGB_ERR_UNSUPPORTED;
+  cudaStream_t s = as_stream(stream);
+  uint32_t* m = static_cast<uint32_t*>(mask);
+  size_t done = 0;
+  if (aligned16(x) && aligned16(y) && n >= 4) {
+    const size_t nvec = n / 4;
+    const int st = launch_ex(relu_fwd_mask_kernel, dim3(oneshot_grid(nvec)), dim3(kBlock), 0, s, 0, true,
+                             reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(y), m, nvec);
+    if (st != SGB_OK) return st;
+    done = nvec * 4;
+  }
+  if (done < n) {
+    const size_t words = ((n + 31) >> 5) - (done >> 5);
+    relu_fwd_mask_tail_kernel<<<static_cast<unsigned>(ceil_div(words, 128)), 128, 0, s>>>(x, y, m, done, n);
+  }
+  return launch_status();
+}
+
+int sgb_relu_backward_mask_f32(const float* dy, const void* mask, float* dx, size_t n, void* stream) {
+  if (n && !mask) return SGB_ERR_NULL;
+  return run<1, FReluBwdMask, float, float, float, float>(FReluBwdMask{static_cast<const unsigned char*>(mask)}, dy,
+                                                          nullptr, nullptr, dx, n, stream);
+}
+
+int sgb_add_relu_backward_mask_f32(const float* dy_a, const float* dy_b, const void* mask, float* dx, size_t n,
+                                   void* stream) {
+  if (n && !mask) return SGB_ERR_NULL;
+  return run<2, FAddReluBwdMask, float, float, float, float>(FAddReluBwdMask{static_cast<const unsigned char*>(mask)},
+                                                             dy_a, dy_b, nullptr, dx, n, stream);
+}
+
 #define H(p) static_cast<const __half*>(p)
 #define HO(p) static_cast<__half*>(p)
 #define RUN16_1(E, P0, IN, OUT)                                                \

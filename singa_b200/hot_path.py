@@ -85,7 +85,7 @@ class HotPathGPU(object):
             off += cnt
         for name, spec in T.items():
             k = spec.kind
-            if k == "wsyn":
+            if k in ("wsyn", "mask"):
                 continue
             if k == "pgrad" and name in arena_view:
                 self.t[name] = arena_view[name]
@@ -131,6 +131,18 @@ class HotPathGPU(object):
                 a = op.args
                 self.t[a["x"]].copy_(torch.relu(self.t[a["x"]]))
                 self.t[a["y"]].copy_(torch.nn.functional.max_pool2d(self.t[a["x"]], a["kernel"], a["stride"], a["pad"]))
+        # bit records of the ReLU forward partner (produced once at set-up: the
+        # forward pass is outside this path), from the stored ReLU inputs
+        for name, spec in T.items():
+            if spec.kind != "mask":
+                continue
+            src = self.t[name[len("mask:"):]]
+            n = src.numel()
+            rec = torch.zeros(self.lib.sgb_relu_mask_bytes(n), dtype=torch.uint8, device=dev)
+            y = torch.empty_like(src)
+            _lib.call("sgb_relu_forward_mask_f32", src.data_ptr(), y.data_ptr(), rec.data_ptr(), n,
+                      torch.cuda.current_stream().cuda_stream)
+            self.t[name] = rec
         self.moments = {p: torch.zeros_like(self.t[p]) for p in self.plan["params"]}
         self.ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
         torch.cuda.synchronize()
@@ -160,12 +172,17 @@ class HotPathGPU(object):
             a, k = op.args, op.kind
             if k == "relu_bwd":
                 self.calls.append(("sgb_relu_backward_f32", (p(a["dy"]), p(a["x"]), p(a["dx"]), t[a["x"]].numel(), S)))
+            elif k == "relu_mask_bwd":
+                self.calls.append(("sgb_relu_backward_mask_f32", (p(a["dy"]), p(a["x"]), p(a["dx"]), t[a["dx"]].numel(), S)))
+            elif k == "add_relu_mask_bwd":
+                self.calls.append(("sgb_add_relu_backward_mask_f32",
+                                   (p(a["dy_a"]), p(a["dy_b"]), p(a["x"]), p(a["dx"]), t[a["dx"]].numel(), S)))
             elif k == "add_relu_bwd":
                 self.calls.append(("sgb_add_relu_backward_f32",
                                    (p(a["dy_a"]), p(a["dy_b"]), p(a["x"]), p(a["dx"]), t[a["x"]].numel(), S)))
             elif k == "add_out":
                 self.calls.append(("sgb_binary_f32", (0, p(a["a"]), p(a["b"]), p(a["out"]), t[a["out"]].numel(), S)))
-            elif k in ("bn_bwd", "bn_relu_bwd"):
+            elif k in ("bn_bwd", "bn_relu_bwd", "bn_relu_mask_bwd"):
                 n, c, h, w = t[a["x"]].shape
                 need = L.sgb_bn_backward_workspace_bytes(n, c, h * w)
                 assert need <= ws.numel()
@@ -174,7 +191,7 @@ class HotPathGPU(object):
                                        (p(a["x"]), p(a["dy"]), p(a["scale"]), p(a["mean"]), p(a["invstd"]), p(a["dx"]),
                                         p(a["dscale"]), p(a["dbias"]), n, c, h * w, ws.data_ptr(), ws.numel(), S)))
                 else:
-                    self.calls.append(("sgb_bn_relu_backward_f32",
+                    self.calls.append(("sgb_bn_relu_backward_mask_f32" if k == "bn_relu_mask_bwd" else "sgb_bn_relu_backward_f32",
                                        (p(a["x"]), p(a["dy"]), p(a["relu_x"]), p(a["scale"]), p(a["mean"]),
                                         p(a["invstd"]), p(a["dx"]), p(a["dscale"]), p(a["dbias"]), n, c, h * w,
                                         ws.data_ptr(), ws.numel(), S)))

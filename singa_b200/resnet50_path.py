@@ -226,6 +226,8 @@ def build_plan(batch=32, image=224, num_classes=1000, fused=False, blocks=(3, 4,
 
 READS = {
     "relu_bwd": ("dy", "x"), "add_relu_bwd": ("dy_a", "dy_b", "x"), "add_out": ("a", "b"),
+    "relu_mask_bwd": ("dy", "x"), "add_relu_mask_bwd": ("dy_a", "dy_b", "x"),
+    "bn_relu_mask_bwd": ("dy", "relu_x", "x", "scale", "mean", "invstd"),
     "bn_bwd": ("dy", "x", "scale", "mean", "invstd"),
     "bn_relu_bwd": ("dy", "relu_x", "x", "scale", "mean", "invstd"),
     "bn_add_relu_bwd": ("dy_a", "dy_b", "relu_x", "x", "scale", "mean", "invstd"),
@@ -334,6 +336,7 @@ def _fuse_loss_head(ops):
 
 WRITES = {
     "relu_bwd": ("dx",), "add_relu_bwd": ("dx",), "add_out": ("out",),
+    "relu_mask_bwd": ("dx",), "add_relu_mask_bwd": ("dx",), "bn_relu_mask_bwd": ("dx", "dscale", "dbias"),
     "bn_bwd": ("dx", "dscale", "dbias"), "bn_relu_bwd": ("dx", "dscale", "dbias"),
     "bn_add_relu_bwd": ("joined", "dx", "dscale", "dbias"), "maxpool_bwd": ("dx",), "avgpool_bwd": ("dx",),
     "softmax": ("y",), "ce_fwd": ("loss",), "sum_all": ("out",), "ce_bwd": ("grad",), "ce_grad": ("grad",),
@@ -369,6 +372,31 @@ def add_wgrad_refresh(plan, where="start"):
     return dict(plan, ops=ops, tensors=T)
 
 
+def mask_plan(plan):
+    """Rewrites every ReLU backward (alone, joined, or folded into a batch-norm
+    backward) to consume the forward partner's one-bit-per-element record
+    "mask:<relu input>" instead of the stored ReLU input.  Opt-in: it changes
+    what the backward pass consumes.  The ops keep the name of the original
+    input under "x_ref" so that a checker can recompute the decisions."""
+    T = dict(plan["tensors"])
+    rename = {"relu_bwd": ("relu_mask_bwd", "x"), "add_relu_bwd": ("add_relu_mask_bwd", "x"),
+              "bn_relu_bwd": ("bn_relu_mask_bwd", "relu_x")}
+    ops = []
+    for op in plan["ops"]:
+        if op.kind in rename:
+            kind, key = rename[op.kind]
+            src = op.args[key]
+            mname = "mask:" + src
+            if mname not in T:
+                T[mname] = Tensor(mname, T[src].shape, "mask")
+            args = dict(op.args)
+            args[key] = mname
+            args["x_ref"] = src
+            op = Op(kind, args)
+        ops.append(op)
+    return dict(plan, ops=ops, tensors=T)
+
+
 def numel(shape):
     n = 1
     for s in shape:
@@ -393,6 +421,13 @@ def algorithmic_bytes(plan, world=1, pool_argmax=False):
             add("relu_bwd", 12 * numel(T[a["x"]].shape))
         elif op.kind == "add_relu_bwd":
             add("add_relu_bwd", 16 * numel(T[a["x"]].shape))
+        elif op.kind == "relu_mask_bwd":                 # dy, dx and one bit per element
+            add("relu_mask_bwd", 8 * numel(T[a["dx"]].shape) + numel(T[a["dx"]].shape) // 8)
+        elif op.kind == "add_relu_mask_bwd":
+            add("add_relu_mask_bwd", 12 * numel(T[a["dx"]].shape) + numel(T[a["dx"]].shape) // 8)
+        elif op.kind == "bn_relu_mask_bwd":
+            s = T[a["x"]].shape
+            add("bn_relu_mask_bwd", 12 * numel(s) + numel(s) // 8 + 20 * s[1])
         elif op.kind == "add_out":
             add("join", 12 * numel(T[a["out"]].shape))
         elif op.kind == "bn_bwd":

@@ -231,3 +231,60 @@ def test_refreshed_stand_in_gradients_do_not_compound():
     assert np.array_equal(got["d:conv1.W"], got["wsyn:conv1.W"])
     for p in plan["params"]:
         close(got[p], host[p], 1e-6, "param " + p)
+
+
+def test_relu_bit_record_gives_the_same_step_bitwise():
+    """The ReLU forward partner's one-bit-per-element record instead of the
+    stored ReLU input, in all three consumers (ReLU backward alone, joined,
+    folded into batch-norm backward): same parameters bit for bit, and the
+    step still equals the oracle executor's."""
+    from oracle.path import OraclePath
+    from singa_b200.hot_path import HotPathGPU
+    from singa_b200.resnet50_path import build_plan, fuse_plan, mask_plan
+    outs = []
+    for masked in (False, True):
+        plan = fuse_plan(build_plan(batch=2, image=64, num_classes=10, blocks=(2, 1, 1, 1)))
+        if masked:
+            plan = mask_plan(plan)
+            kinds = [o.kind for o in plan["ops"]]
+            assert "bn_relu_mask_bwd" in kinds and "add_relu_mask_bwd" in kinds and "relu_mask_bwd" in kinds
+            assert not any(k in kinds for k in ("bn_relu_bwd", "add_relu_bwd", "relu_bwd"))
+        gpu = HotPathGPU(plan, communicator=None, world=1, seed=3)
+        if masked:
+            host = gpu.host_copy()
+            OraclePath(plan, host).run_step()
+        gpu.run_step()
+        torch.cuda.synchronize()
+        outs.append({p: gpu.t[p].clone() for p in plan["params"]})
+        outs[-1]["bn1.dx"] = gpu.t["bn1.dx"].clone()
+    for p in outs[0]:
+        assert torch.equal(outs[0][p], outs[1][p]), p
+    got = gpu.host_copy()
+    for p in plan["params"]:
+        close(got[p], host[p], 1e-6, "param " + p)
+
+
+@pytest.mark.parametrize("n", [1, 3, 31, 32, 33, 4096, 100003])
+def test_relu_forward_record_layout(n):
+    """y = max(x, 0); bit i of the record = x[i] > 0 in plain element order,
+    for aligned and misaligned buffers and every tail length."""
+    from singa_b200 import _lib
+    L = _lib.lib()
+    for shift in (0, 1):
+        buf = torch.randn(n + 8, device="cuda")
+        buf[::3] = 0.0
+        x = buf[shift:shift + n]
+        ybuf = torch.empty(n + 8, device="cuda")
+        y = ybuf[shift:shift + n]
+        rec = torch.full((L.sgb_relu_mask_bytes(n),), 0xFF, dtype=torch.uint8, device="cuda")
+        _lib.call("sgb_relu_forward_mask_f32", x.data_ptr(), y.data_ptr(), rec.data_ptr(), n,
+                  torch.cuda.current_stream().cuda_stream)
+        dy = torch.randn(n + 8, device="cuda")[shift:shift + n]
+        dx = torch.empty(n + 8, device="cuda")[shift:shift + n]
+        _lib.call("sgb_relu_backward_mask_f32", dy.data_ptr(), rec.data_ptr(), dx.data_ptr(), n,
+                  torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert torch.equal(y, torch.relu(x))
+        bits = np.unpackbits(rec.cpu().numpy(), bitorder="little")[:n]
+        assert np.array_equal(bits.astype(bool), (x > 0).cpu().numpy())
+        assert torch.equal(dx, torch.where(x > 0, dy, torch.zeros_like(dy)))
