@@ -10,7 +10,8 @@
  *     TensorRef{t.block()->mutable_data(), t.Size(), t.data_type() == kFloat16}
  * and the stream the caller's kernels run on (the reference's ctx->stream).
  * A maintainer's adapter inside libsinga is therefore three lines per method
- * (build the refs, call, done); see INTEGRATION.md. */
+ * (build the refs, call, done); singa_b200/adapter/communicator.cc is that
+ * adapter, written on singa::Tensor and Device::Exec. */
 #ifndef SGB_COMMUNICATOR_HPP_
 #define SGB_COMMUNICATOR_HPP_
 

@@ -1,9 +1,9 @@
 """Per-kernel micro-benchmark of the backward-path kernels.
 
-    python -m singa_b200.microbench bn --shape 32,256,56,56 [--relu] [--iters 20]
-    python -m singa_b200.microbench relu --n 67108864
-    python -m singa_b200.microbench maxpool --shape 32,64,112,112
-    python -m singa_b200.microbench sgd | join | topk --n 100000000 | threshold --n ...
+    python microbench.py bn --shape 32,256,56,56 [--relu] [--iters 20]
+    python microbench.py relu --n 67108864
+    python microbench.py maxpool --shape 32,64,112,112
+    python microbench.py sgd | join | topk --n 100000000 | threshold --n ...
 
 Each case allocates seeded inputs larger than L2 where the real workload's
 are, launches the kernel through the C ABI and times it with CUDA events on
@@ -18,8 +18,8 @@ import sys
 
 import torch
 
-from . import _lib
-from . import singa_wrap as sw
+from singa_b200 import _lib
+from singa_b200 import singa_wrap as sw
 
 
 def timed(fn, iters, warmup):

@@ -92,4 +92,22 @@ int refcudnn_pooling(int backward, int is_max, int N, int C, int H, int W, int O
   cudnnDestroyTensorDescriptor(yd);
   return 0;
 }
+
+// The bias gradient of a convolution as the reference computes it
+// (apache/singa src/model/operation/convolution.cc:684-702):
+// cudnnConvolutionBackwardBias on the NCHW output gradient with a 1 x C x 1 x 1
+// bias descriptor, alpha = 1, beta = 0.
+int refcudnn_conv_bias_backward(int N, int C, int H, int W, const float* dy, float* db, void* stream) {
+  cudnnSetStream(handle(), static_cast<cudaStream_t>(stream));
+  cudnnTensorDescriptor_t yd, bd;
+  CK(cudnnCreateTensorDescriptor(&yd));
+  CK(cudnnCreateTensorDescriptor(&bd));
+  CK(cudnnSetTensor4dDescriptor(yd, CUDNN_TENSOR_NCHW, CUDNN_DATA_FLOAT, N, C, H, W));
+  CK(cudnnSetTensor4dDescriptor(bd, CUDNN_TENSOR_NCHW, CUDNN_DATA_FLOAT, 1, C, 1, 1));
+  const float alpha = 1.0f, beta = 0.0f;
+  CK(cudnnConvolutionBackwardBias(handle(), &alpha, yd, dy, &beta, bd, db));
+  cudnnDestroyTensorDescriptor(yd);
+  cudnnDestroyTensorDescriptor(bd);
+  return 0;
+}
 }

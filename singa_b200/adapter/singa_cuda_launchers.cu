@@ -15,6 +15,8 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include <cub/device/device_radix_sort.cuh>
+
 #include "sgb.h"
 
 namespace singa {
@@ -197,9 +199,213 @@ void sparsindex(const size_t n, const float* in, int* out, cudaStream_t s) {
 void generateindex(const size_t n, int* out, cudaStream_t s) {
   must(sgb_generateindex_i32(out, n, s), "generateindex");
 }
-// removezeroval / removezeroidx / sortbykey (Thrust compaction and a full sort
-// of value-index pairs) are not provided: their only caller is the
-// communicator, whose replacement selects and compacts in sgb_sparse_*.
+
+// ---- the three helpers the reference builds on Thrust (math_kernel.cu:704-727).
+// They are kept for source compatibility only: the replacement communicator
+// selects and compacts inside sgb_sparse_*, and calls none of them.  Like the
+// Thrust versions they take no workspace, so their scratch comes from the
+// stream-ordered allocator (cudaMallocAsync on `s`).
+namespace {
+constexpr int kTile = 2048, kCompactBlock = 256;
+
+}  // namespace
+
+// The compaction kernels treat the elements as 32-bit words; IS_FLOAT decides
+// whether the bit pattern of -0.0f counts as zero.
+namespace {
+template <bool IS_FLOAT>
+__device__ __forceinline__ bool nonzero(unsigned bits) {
+  return IS_FLOAT ? (bits << 1) != 0u : bits != 0u;
+}
+
+template <bool IS_FLOAT>
+__global__ void __launch_bounds__(kCompactBlock)
+tile_count_kernel(const unsigned* __restrict__ in, size_t n, unsigned* __restrict__ counts) {
+  __shared__ unsigned warp_tot[kCompactBlock / 32];
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  unsigned c = 0;
+  for (int k = threadIdx.x; k < kTile; k += kCompactBlock)
+    if (base + k < n && nonzero<IS_FLOAT>(in[base + k])) ++c;
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned t = 0;
+    for (int w = 0; w < kCompactBlock / 32; ++w) t += warp_tot[w];
+    counts[blockIdx.x] = t;
+  }
+}
+
+// Exclusive scan of the tile counts in place, one CTA; counts[tiles] = total.
+__global__ void __launch_bounds__(1024) tile_scan_kernel(unsigned* __restrict__ counts, unsigned tiles) {
+  __shared__ unsigned carry, warp_tot[32];
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (unsigned base = 0; base < tiles; base += 1024) {
+    const unsigned i = base + threadIdx.x;
+    const unsigned v = i < tiles ? counts[i] : 0u;
+    unsigned incl = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+      if ((threadIdx.x & 31) >= o) incl += t;
+    }
+    if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = incl;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      unsigned w = warp_tot[threadIdx.x], wi = w;
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, wi, o);
+        if (threadIdx.x >= o) wi += t;
+      }
+      warp_tot[threadIdx.x] = wi - w;            // exclusive prefix of the warp totals
+    }
+    __syncthreads();
+    const unsigned excl = carry + warp_tot[threadIdx.x >> 5] + incl - v;
+    if (i < tiles) counts[i] = excl;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = excl + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[tiles] = carry;
+}
+
+// Writes the non-zero elements of each tile, in order, at the tile's offset.
+template <bool IS_FLOAT>
+__global__ void __launch_bounds__(kCompactBlock)
+tile_write_kernel(const unsigned* __restrict__ in, size_t n, const unsigned* __restrict__ offsets,
+                  unsigned* __restrict__ out) {
+  __shared__ unsigned warp_base[kCompactBlock / 32], running;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  if (threadIdx.x == 0) running = offsets[blockIdx.x];
+  __syncthreads();
+  for (int k0 = 0; k0 < kTile; k0 += kCompactBlock) {
+    const size_t i = base + k0 + threadIdx.x;
+    const unsigned v = i < n ? in[i] : 0u;
+    const bool keep = i < n && nonzero<IS_FLOAT>(v);
+    const unsigned ballot = __ballot_sync(0xffffffffu, keep);
+    const unsigned lane = threadIdx.x & 31, rank = __popc(ballot & ((1u << lane) - 1u));
+    if (lane == 0) warp_base[threadIdx.x >> 5] = __popc(ballot);
+    __syncthreads();
+    unsigned before = running;
+    for (int w = 0; w < (threadIdx.x >> 5); ++w) before += warp_base[w];
+    if (keep) out[before + rank] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned t = 0;
+      for (int w = 0; w < kCompactBlock / 32; ++w) t += warp_base[w];
+      running += t;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void copy_prefix_kernel(const unsigned* __restrict__ src, const unsigned* __restrict__ total,
+                                   unsigned* __restrict__ dst) {
+  const unsigned t = *total;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < t;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
+inline void must_cuda(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "singa::cuda::%s failed: %s\n", what, cudaGetErrorString(e));
+    std::abort();
+  }
+}
+
+// Stable in-place removal of zeros from n 32-bit elements; returns the number kept when asked.
+template <bool IS_FLOAT>
+void compact_nonzero(size_t n, unsigned* data, cudaStream_t s, int* kept_host, const char* who) {
+  if (n == 0) {
+    if (kept_host) *kept_host = 0;
+    return;
+  }
+  const unsigned tiles = static_cast<unsigned>((n + kTile - 1) / kTile);
+  unsigned *tmp = nullptr, *counts = nullptr;
+  must_cuda(cudaMallocAsync(&tmp, n * sizeof(unsigned), s), who);
+  must_cuda(cudaMallocAsync(&counts, (static_cast<size_t>(tiles) + 1) * sizeof(unsigned), s), who);
+  tile_count_kernel<IS_FLOAT><<<tiles, kCompactBlock, 0, s>>>(data, n, counts);
+  tile_scan_kernel<<<1, 1024, 0, s>>>(counts, tiles);
+  tile_write_kernel<IS_FLOAT><<<tiles, kCompactBlock, 0, s>>>(data, n, counts, tmp);
+  copy_prefix_kernel<<<148 * 8, 256, 0, s>>>(tmp, counts + tiles, data);
+  must_cuda(cudaGetLastError(), who);
+  if (kept_host) {
+    unsigned kept = 0;
+    must_cuda(cudaMemcpyAsync(&kept, counts + tiles, sizeof(unsigned), cudaMemcpyDeviceToHost, s), who);
+    must_cuda(cudaStreamSynchronize(s), who);
+    *kept_host = static_cast<int>(kept);
+  }
+  must_cuda(cudaFreeAsync(tmp, s), who);
+  must_cuda(cudaFreeAsync(counts, s), who);
+}
+}  // namespace
+
+/// in[0 .. kept) = the non-zero values of in, in their original order.
+void removezeroval(const size_t n, float* in, cudaStream_t s) {
+  compact_nonzero<true>(n, reinterpret_cast<unsigned*>(in), s, nullptr, "removezeroval");
+}
+/// The same for indices; *address receives the number of non-zero entries -
+/// what the reference's caller needs.  (The reference counts zeros over the
+/// whole array after thrust::remove, whose tail is unspecified.)
+void removezeroidx(const size_t n, int* in, cudaStream_t s, int* address) {
+  compact_nonzero<false>(n, reinterpret_cast<unsigned*>(in), s, address, "removezeroidx");
+}
+
+namespace {
+// The reference's comparator orders by max((int)v, -(int)v), descending.
+__global__ void sort_keys_kernel(const float* __restrict__ key, size_t n, unsigned* __restrict__ k2,
+                                 unsigned* __restrict__ pos) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(key[i]);
+    k2[i] = static_cast<unsigned>(t > -t ? t : -t);
+    pos[i] = static_cast<unsigned>(i);
+  }
+}
+__global__ void permute_kernel(const unsigned* __restrict__ pos, size_t n, const float* __restrict__ key,
+                               const int* __restrict__ value, float* __restrict__ key_out,
+                               int* __restrict__ value_out) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    key_out[i] = key[pos[i]];
+    value_out[i] = value[pos[i]];
+  }
+}
+}  // namespace
+
+/// Sorts (key, value) pairs by the reference's comparator (absgreater on the
+/// integer-truncated keys), stably: equal keys keep their original order.
+void sortbykey(const size_t n, float* key, int* value, cudaStream_t s) {
+  if (n < 2) return;
+  if (n > 0x7fffffffu) must(SGB_ERR_SIZE, "sortbykey");
+  unsigned *k2 = nullptr, *k2_out = nullptr, *pos = nullptr, *pos_out = nullptr;
+  float* key_out = nullptr;
+  int* value_out = nullptr;
+  void* cub_tmp = nullptr;
+  size_t cub_bytes = 0;
+  const int num = static_cast<int>(n);
+  must_cuda(cub::DeviceRadixSort::SortPairsDescending(nullptr, cub_bytes, k2, k2_out, pos, pos_out, num, 0, 32, s),
+            "sortbykey");
+  must_cuda(cudaMallocAsync(&k2, n * 4, s), "sortbykey");
+  must_cuda(cudaMallocAsync(&k2_out, n * 4, s), "sortbykey");
+  must_cuda(cudaMallocAsync(&pos, n * 4, s), "sortbykey");
+  must_cuda(cudaMallocAsync(&pos_out, n * 4, s), "sortbykey");
+  must_cuda(cudaMallocAsync(&cub_tmp, cub_bytes ? cub_bytes : 4, s), "sortbykey");
+  sort_keys_kernel<<<148 * 8, 256, 0, s>>>(key, n, k2, pos);
+  must_cuda(cub::DeviceRadixSort::SortPairsDescending(cub_tmp, cub_bytes, k2, k2_out, pos, pos_out, num, 0, 32, s),
+            "sortbykey");
+  // k2 / pos are free again: reuse them for the permuted pairs
+  key_out = reinterpret_cast<float*>(k2);
+  value_out = reinterpret_cast<int*>(pos);
+  permute_kernel<<<148 * 8, 256, 0, s>>>(pos_out, n, key, value, key_out, value_out);
+  must_cuda(cudaMemcpyAsync(key, key_out, n * 4, cudaMemcpyDeviceToDevice, s), "sortbykey");
+  must_cuda(cudaMemcpyAsync(value, value_out, n * 4, cudaMemcpyDeviceToDevice, s), "sortbykey");
+  must_cuda(cudaGetLastError(), "sortbykey");
+  for (void* b : {static_cast<void*>(k2), static_cast<void*>(k2_out), static_cast<void*>(pos),
+                  static_cast<void*>(pos_out), cub_tmp})
+    must_cuda(cudaFreeAsync(b, s), "sortbykey");
+}
 
 }  // namespace cuda
 }  // namespace singa

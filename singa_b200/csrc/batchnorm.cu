@@ -30,6 +30,8 @@
 #include <cooperative_groups.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -39,6 +41,29 @@ namespace {
 
 constexpr int kBlock = 256;
 constexpr int kMaxSlices = 64;
+
+// Opts a kernel in to more than 48 KB of dynamic shared memory (and, for the
+// cluster kernels, to non-portable cluster sizes) once per device: the
+// attribute sticks to the function in that device's context, so later
+// launches - including launches under stream capture - issue no attribute
+// call.  `done` is one flag per device ordinal; ordinals beyond the table are
+// set every time.  Racing first calls from two host threads both set the
+// same attribute, which is harmless.
+template <typename K>
+int opt_in_once(K kernel, std::atomic<bool>* done, bool cluster) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && done[dev].load(std::memory_order_acquire)) return SGB_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  if (e != cudaSuccess) return note_cuda_error(e);
+  if (cluster) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return note_cuda_error(e);
+  }
+  if (tracked) done[dev].store(true, std::memory_order_release);
+  return SGB_OK;
+}
 
 struct BnShape {
   int N, C, HW;
@@ -614,14 +639,9 @@ int launch_group(const float* x, const float* dy, const float* relu_in, const fl
                  BnShape sh, cudaStream_t s) {
   auto kernel = bn_bwd_group_kernel<MASK, G>;
   const size_t smem = static_cast<size_t>(G) * sh.N * sh.HW * 8;
-  static bool attr_set[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-  if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (e != cudaSuccess) return note_cuda_error(e);
-    attr_set[dev] = true;
-  }
+  static std::atomic<bool> attr_set[64];
+  const int ready = opt_in_once(kernel, attr_set, false);
+  if (ready != SGB_OK) return ready;
   return launch_ex(kernel, dim3(sh.C / G), dim3(kBlock), smem, s, 0, true, x, dy, relu_in, scale, mean, invstd,
                    dx, dscale, dbias, sh);
 }
@@ -670,20 +690,9 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
                      const float* dy_b = nullptr, float* joined = nullptr) {
   auto kernel = bn_bwd_cluster_kernel<VEC, MASK, T, ADD>;
   const size_t smem = static_cast<size_t>(per_cta) * (VEC ? 16 : 4) * 2;
-  // Opt in to > 48 KB of dynamic shared memory once per device and kernel
-  // instantiation (the attribute sticks to the function in that context), so
-  // that later launches - including launches under stream capture - issue no
-  // attribute call.
-  static bool attr_set[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-  if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (e != cudaSuccess) return note_cuda_error(e);
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (e != cudaSuccess) return note_cuda_error(e);
-    attr_set[dev] = true;
-  }
+  static std::atomic<bool> attr_set[64];
+  const int ready = opt_in_once(kernel, attr_set, true);
+  if (ready != SGB_OK) return ready;
   return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
                    scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined,
                    option(SGB_OPT_STABLE_FORWARD_INPUTS) && option(SGB_OPT_OVERLAP_LAUNCHES) ? 1 : 0);
@@ -992,14 +1001,9 @@ int launch_fwd_cluster(const float* x, const float* scale, const float* bias, fl
                        int per_cta, cudaStream_t s) {
   auto kernel = bn_fwd_cluster_kernel<VEC, T>;
   const size_t smem = static_cast<size_t>(per_cta) * (VEC ? 16 : 4);
-  static bool attr_set[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-  if (!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (e != cudaSuccess) return note_cuda_error(e);
-    attr_set[dev] = true;
-  }
+  static std::atomic<bool> attr_set[64];
+  const int ready = opt_in_once(kernel, attr_set, false);
+  if (ready != SGB_OK) return ready;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(sh.C) * cs);
   cfg.blockDim = dim3(T);
@@ -1071,7 +1075,7 @@ static __device__ __align__(256) float2 g_bn_static_scratch[kMaxSlices * kNoAllo
 // address a kernel could use; the device address is looked up once per device
 // (with that device current) and cached here.
 float2* static_scratch_address(int* status) {
-  static float2* cached[64] = {};
+  static std::atomic<float2*> cached[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) {
@@ -1082,17 +1086,17 @@ float2* static_scratch_address(int* status) {
     *status = SGB_ERR_UNSUPPORTED;
     return nullptr;
   }
-  if (!cached[dev]) {
+  if (!cached[dev].load(std::memory_order_acquire)) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_bn_static_scratch);
     if (e != cudaSuccess || !ptr) {
       *status = note_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
       return nullptr;
     }
-    cached[dev] = static_cast<float2*>(ptr);
+    cached[dev].store(static_cast<float2*>(ptr), std::memory_order_release);
   }
   *status = SGB_OK;
-  return cached[dev];
+  return cached[dev].load(std::memory_order_acquire);
 }
 
 int bn_backward_static(const float* x, const float* dy, const float* scale, const float* mean,

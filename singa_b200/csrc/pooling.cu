@@ -54,7 +54,10 @@ pool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, PoolShape p,
     for (int h = h0; h < h1; ++h)
       for (int w = w0; w < w1; ++w) {
         const float v = xp[h * p.W + w];
-        if (v > best) best = v;
+        // a NaN in the window is the window's result (the reference's pooling
+        // descriptor asks for CUDNN_PROPAGATE_NAN, src/model/operation/pooling.h:90):
+        // the first NaN sticks, since nothing compares greater than it
+        if (v > best || v != v) best = v;
       }
     y[i] = best;
   } else {
@@ -360,7 +363,7 @@ maxpool_fwd_argmax_kernel(const float* __restrict__ x, float* __restrict__ y,
   for (int h = h0; h < h1; ++h)
     for (int w = w0; w < w1; ++w) {
       const float v = xp[h * p.W + w];
-      if (v > best) {
+      if (v > best || (v != v && best == best)) {   // first maximum, or the first NaN (which then sticks)
         best = v;
         code = ((h - hs) << 4) | (w - ws);
       }

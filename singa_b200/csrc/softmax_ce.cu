@@ -39,7 +39,13 @@ __global__ void ce_fwd_kernel(int int_target, size_t batch, size_t dim,
   size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (i >= batch) return;
   if (int_target) {
-    float pt = p[i * dim + t[i]];
+    // a label outside [0, dim) reads nothing: the sample's loss is NaN
+    const int ti = t[i];
+    if (static_cast<unsigned>(ti) >= dim) {
+      loss[i] = __int_as_float(0x7fc00000);
+      return;
+    }
+    float pt = p[i * dim + ti];
     loss[i] = -logf(fmaxf(pt, FLT_MIN));
   } else {
     float sum = 0.f;
@@ -107,6 +113,7 @@ softmax_ce_fused_kernel(const float* __restrict__ x, const int* __restrict__ t,
   for (size_t c = threadIdx.x; c < ncol; c += kBlock) s += expf(xr[c] - m);
   s = block_sum(s, sm);
   const size_t hot = static_cast<size_t>(t[row]);
+  if (hot >= ncol && threadIdx.x == 0) loss[row] = __int_as_float(0x7fc00000);   // label out of range: NaN, not stale memory
   for (size_t c = threadIdx.x; c < ncol; c += kBlock) {
     const float p = expf(xr[c] - m) / s;
     if (prob) prob[row * ncol + c] = p;
@@ -150,7 +157,12 @@ __global__ void ce_fwd_f16_kernel(int int_target, size_t batch, size_t dim,
   if (i >= batch) return;
   const __half eps = __float2half_rn(0.0000001f);
   if (int_target) {
-    const __half pt = p[i * dim + t[i]];
+    const int ti = t[i];
+    if (static_cast<unsigned>(ti) >= dim) {      // label out of range: NaN, no read
+      loss[i] = __ushort_as_half(0x7e00);
+      return;
+    }
+    const __half pt = p[i * dim + ti];
     loss[i] = __hneg(hlog(__hgt(pt, eps) ? pt : eps));
   } else {
     __half sum = __float2half_rn(0.f);

@@ -187,13 +187,24 @@ def Transform(t_storage, shape, stride):
 
 # ------------------------------------------------------------------ workspace
 _WS = {}
+_WS_RETIRED = []      # outgrown buffers: kept alive, never handed back to the allocator
 
 
 def _workspace(device, nbytes):
     """A per-device scratch buffer owned by the host layer (the C ABI never
-    allocates).  Grows monotonically; 256-byte aligned by the torch allocator."""
+    allocates); 256-byte aligned by the torch allocator.  When a larger request
+    arrives a new buffer takes over and the old one is RETIRED, not freed: its
+    address may sit in a captured CUDA graph or in work queued on another
+    stream, and must not be handed to someone else by the caching allocator.
+    A graph captured through these wrappers therefore pins the workspace it saw.
+    Growth during a stream capture is refused (it would allocate inside it)."""
     buf = _WS.get(device)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("workspace of %d bytes needed during stream capture (have %d): run the call "
+                               "once before capturing" % (nbytes, buf.numel()))
+        if buf is not None:
+            _WS_RETIRED.append(buf)
         buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
         _WS[device] = buf
     return buf

@@ -35,8 +35,7 @@ def test_argument_validation_needs_no_gpu():
 def test_launcher_library_exports_the_reference_symbols():
     """libsgb_singa.so defines the `singa::cuda::*` launchers under exactly the
     mangled names the reference's math_kernel.cu exports (list extracted from
-    the compiled reference, tests/golden/make_golden.py), except the three
-    Thrust helpers whose only caller - the communicator - is replaced."""
+    the compiled reference, tests/golden/make_golden.py): all 75 of them."""
     import os
     import subprocess
     build.build()
@@ -47,9 +46,7 @@ def test_launcher_library_exports_the_reference_symbols():
     rows = subprocess.run(["nm", "-D", "--defined-only", build.ADAPTER_LIB], capture_output=True, text=True,
                           check=True).stdout
     have = set(r.split()[2] for r in rows.splitlines() if "_ZN5singa4cuda" in r)
-    missing = sorted(want - have)
-    assert all(any(k in m for k in ("removezeroval", "removezeroidx", "sortbykey")) for m in missing), missing
-    assert len(missing) == 3
+    assert not (want - have), sorted(want - have)
     assert not (have - want), sorted(have - want)
     ctypes.CDLL(build.ADAPTER_LIB)       # resolves libsgb.so through its $ORIGIN runpath
 

@@ -177,3 +177,55 @@ def test_launcher_matches_reference_launcher(libs, sym):
             assert not bad.any(), "%s(%s): %d of %d elements differ, first at %d: %r vs %r" % (
                 name, enc, int(bad.sum()), bad.numel(), int(bad.flatten().nonzero()[0]),
                 r.flatten()[bad.flatten()][0].item(), o.flatten()[bad.flatten()][0].item())
+
+
+def _by_name(lib, needle):
+    with open(SYMS) as f:
+        sym = next(s for s in f.read().split() if needle in s)
+    return getattr(lib, sym)
+
+
+def test_compaction_and_sort_helpers_match_the_reference(libs):
+    """The three helpers the reference builds on Thrust, through their mangled
+    names on both libraries: removezeroval (same compacted prefix), sortbykey
+    (same pairs in the same order: the comparator sees integer-truncated
+    magnitudes, ties keep their original order) and removezeroidx (same
+    compacted prefix; the count is the number of non-zero entries, which is
+    what the reference's caller needs - its own count reads the unspecified
+    tail that thrust::remove leaves behind)."""
+    ref, ours = libs
+    rng = np.random.default_rng(8)
+    n = 300007
+    v = (rng.standard_normal(n) * 3).astype(np.float32)
+    v[rng.random(n) < 0.6] = 0.0
+    v[7] = -0.0
+    kept = v[v != 0]
+    outs = []
+    for lib in (ref, ours):
+        t = torch.from_numpy(v.copy()).cuda()
+        _by_name(lib, "removezeroval")(C.c_size_t(n), C.c_void_p(t.data_ptr()), None)
+        torch.cuda.synchronize()
+        outs.append(t.cpu().numpy()[:kept.size])
+    assert np.array_equal(outs[0], kept) and np.array_equal(outs[1], kept)
+
+    idx = np.where(v != 0, np.arange(1, n + 1), 0).astype(np.int32)
+    t = torch.from_numpy(idx.copy()).cuda()
+    count = C.c_int(-1)
+    _by_name(ours, "removezeroidx")(C.c_size_t(n), C.c_void_p(t.data_ptr()), None, C.byref(count))
+    torch.cuda.synchronize()
+    assert count.value == kept.size
+    assert np.array_equal(t.cpu().numpy()[:kept.size], idx[idx != 0])
+
+    for scale in (3.0, 1e-3):                      # distinct integer keys / everything ties at 0
+        key = (rng.standard_normal(n) * scale).astype(np.float32)
+        val = np.arange(1, n + 1, dtype=np.int32)
+        res = []
+        for lib in (ref, ours):
+            k, w = torch.from_numpy(key.copy()).cuda(), torch.from_numpy(val.copy()).cuda()
+            _by_name(lib, "sortbykey")(C.c_size_t(n), C.c_void_p(k.data_ptr()), C.c_void_p(w.data_ptr()), None)
+            torch.cuda.synchronize()
+            res.append((k.cpu().numpy(), w.cpu().numpy()))
+        assert np.array_equal(res[0][1], res[1][1]), "index order differs at scale %g" % scale
+        assert np.array_equal(res[0][0], res[1][0])
+        mags = np.abs(res[1][0].astype(np.int32))
+        assert (np.diff(mags) <= 0).all()

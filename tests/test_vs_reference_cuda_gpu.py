@@ -238,3 +238,51 @@ def test_avgpool_matches_cudnn_call(sw, rd, case):
     h = sw.CudnnPoolingHandle(x, (k, k), (s, s), (pd, pd), False)
     assert float((sw.GpuPoolingForward(h, x) - y).abs().max() / y.abs().max()) <= 1e-5
     assert float((sw.GpuPoolingBackward(h, dy, x, y) - dx).abs().max() / dx.abs().max()) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(64, 32, 24, 24), (64, 32, 8, 8), (3, 5, 7, 3)])
+def test_conv_bias_backward_matches_cudnn_call(sw, rd, shape):
+    """GpuConvBackwardb's library call (cudnnConvolutionBackwardBias,
+    convolution.cc:684-702) on the small CNN's two shapes and an odd one."""
+    from singa_b200 import _lib
+    L = _lib.lib()
+    N, Cc, H, W = shape
+    dy = torch.randn(shape, device="cuda")
+    want, got = torch.empty(Cc, device="cuda"), torch.empty(Cc, device="cuda")
+    assert rd.refcudnn_conv_bias_backward(N, Cc, H, W, p(dy), p(want), None) == 0
+    ws = torch.empty(max(L.sgb_conv_bias_backward_workspace_bytes(N, Cc, H * W), 256), dtype=torch.uint8, device="cuda")
+    _lib.call("sgb_conv_bias_backward_f32", dy.data_ptr(), got.data_ptr(), N, Cc, H * W, ws.data_ptr(), ws.numel(),
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    exact = dy.double().sum((0, 2, 3))
+    scale = exact.abs().max().item()
+    assert (got.double() - want.double()).abs().max().item() <= 1e-5 * scale
+    assert (got.double() - exact).abs().max().item() <= 1e-5 * scale
+
+
+def test_maxpool_forward_propagates_nan_like_cudnn(sw, rd):
+    """The reference's pooling descriptor is built with CUDNN_PROPAGATE_NAN
+    (pooling.h:90): a NaN anywhere in a window is the window's maximum."""
+    from singa_b200 import _lib
+    L = _lib.lib()
+    for k, s, pd in ((3, 2, 1), (2, 2, 0)):
+        N, Cc, H, W = 2, 3, 12, 12
+        OH = (H + 2 * pd - k) // s + 1
+        x = torch.randn(N, Cc, H, W, device="cuda")
+        x[0, 0, 2, 2] = float("nan")
+        x[1, 2, 7, 10] = float("nan")
+        x[1, 1, 0, 0] = float("nan")
+        want, got = torch.empty(N, Cc, OH, OH, device="cuda"), torch.empty(N, Cc, OH, OH, device="cuda")
+        assert rd.refcudnn_pooling(0, 1, N, Cc, H, W, OH, OH, k, k, pd, pd, s, s, p(x), p(want), None, None, None) == 0
+        _lib.call("sgb_maxpool_forward_f32", x.data_ptr(), got.data_ptr(), N, Cc, H, W, k, k, pd, pd, s, s,
+                  torch.cuda.current_stream().cuda_stream)
+        rec = torch.empty(N, Cc, OH, OH, dtype=torch.uint8, device="cuda")
+        got2 = torch.empty_like(got)
+        _lib.call("sgb_maxpool_forward_argmax_f32", x.data_ptr(), got2.data_ptr(), rec.data_ptr(), N, Cc, H, W, k, k,
+                  pd, pd, s, s, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert torch.isnan(want).any()
+        assert torch.equal(torch.isnan(got), torch.isnan(want))
+        assert torch.equal(torch.isnan(got2), torch.isnan(want))
+        keep = ~torch.isnan(want)
+        assert torch.equal(got[keep], want[keep]) and torch.equal(got2[keep], want[keep])
