@@ -172,6 +172,164 @@ def config1_leg(torch, steps=50):
     return out
 
 
+def reference_cuda_leg(torch, dist, path, rank, world, local, steps=10, warmup=2):
+    """The same ResNet-50 backward + sync + update step on the reference's OWN
+    CUDA / NCCL path, in the same run on the same GPUs: apache/singa's
+    tensor.cc + tensor_math_cuda.h + math_kernel.cu, its cuDNN batch-norm /
+    pooling operations and its unmodified communicator.cc, compiled from its
+    sources into oracle/_ref/libref_singa_cuda.so (oracle/ref_cuda_build.py) and
+    driven through its public C++ functions, one reference call per operation
+    of the UNFUSED plan (its call pattern): ReLUBackward, `+=` joins,
+    GpuBatchNormBackward / GpuPoolingBackward on their handles, SoftMax /
+    CrossEntropyFwd / SumAll / SoftmaxCrossEntropyBwd / `/= N`, Sum(axis 0),
+    DistOpt's bucket policy on Communicator::fusedSynch / synch / wait,
+    `grad /= world` and the per-tensor Axpy chain of SGD.  Eager, like the
+    reference (its operations are launched one by one from the host), timed
+    with CUDA events on the default stream its kernels use.  The inputs are
+    copies of this arm's tensors.  Returns None when the library is absent."""
+    import ctypes as C
+    lib_path = os.path.join(ROOT, "oracle", "_ref", "libref_singa_cuda.so")
+    if not os.path.exists(lib_path):
+        return None
+    from singa_b200.opt import plan_buckets
+    from singa_b200.resnet50_path import build_plan, numel
+    L = C.CDLL(lib_path)
+    for f in ("rs_tensor_new", "rs_relu_backward", "rs_add", "rs_sum_axis", "rs_sum_all", "rs_softmax",
+              "rs_cross_entropy_fwd", "rs_softmax_cross_entropy_bwd", "rs_bn_handle_new", "rs_pool_handle_new",
+              "rs_pool_backward", "rs_comm_new"):
+        getattr(L, f).restype = C.c_void_p
+    L.rs_init(local)
+    plan = build_plan(batch=BATCH, fused=False)
+    T = plan["tensors"]
+    H = {}
+
+    def new(shape, dtype=0):
+        dims = (C.c_size_t * len(shape))(*shape)
+        return C.c_void_p(L.rs_tensor_new(len(shape), dims, dtype))
+
+    def put(name, h):
+        old = H.get(name)
+        if old is not None:
+            L.rs_tensor_free(old)
+        H[name] = h
+
+    # inputs of the step: copies of this arm's device tensors
+    for name, spec in T.items():
+        if spec.kind in ("act", "stat", "syn", "param", "pgrad", "label"):
+            src = path.t[name]
+            h = new(spec.shape, 2 if spec.kind == "label" else 0)
+            L.rs_tensor_from_device(h, C.c_void_p(src.data_ptr()), C.c_size_t(src.numel() * src.element_size()))
+            H[name] = h
+    for pname in plan["params"]:
+        h = new(T[pname].shape)
+        L.rs_tensor_set(h, C.c_float(0.0))
+        H["m:" + pname] = h
+    bn_handles, pool_handles = {}, {}
+    for op in plan["ops"]:
+        a = op.args
+        if op.kind == "bn_bwd":
+            bn_handles[a["x"]] = C.c_void_p(L.rs_bn_handle_new(C.c_float(0.9), H[a["x"]]))
+        elif op.kind in ("maxpool_bwd", "avgpool_bwd"):
+            key = a.get("x", a["dx"])
+            if op.kind == "avgpool_bwd":      # the forward input only lends its shape to the handle
+                H[a["dx"] + ".shape"] = new(T[a["dx"]].shape)
+                H[a["dx"] + ".y"] = new(T[a["dy"]].shape)
+                key = a["dx"] + ".shape"
+            k, st, pd = a["kernel"], a["stride"], a["pad"]
+            pool_handles[a["dx"]] = C.c_void_p(L.rs_pool_handle_new(H[key], k[0], k[1], st[0], st[1], pd[0], pd[1],
+                                                                    1 if op.kind == "maxpool_bwd" else 0))
+    comm = None
+    if True:
+        idb = C.create_string_buffer(L.rs_nccl_id_bytes())
+        if rank == 0:
+            L.rs_nccl_id_new(idb)
+        if world > 1:
+            box = [idb.raw if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            idb = C.create_string_buffer(box[0], len(box[0]))
+        comm = C.c_void_p(L.rs_comm_new(local, world, idb, 4194304))
+    order = plan["grad_order"]
+    sizes = [numel(T["d:" + n].shape) for n in order]
+    events = plan_buckets(sizes, 2097152)
+    flush_after = {ev[1][-1]: ev for ev in events}
+    index = {n: i for i, n in enumerate(order)}
+    lr, mom, wd = C.c_float(0.1), C.c_float(0.9), C.c_float(1e-5)
+
+    def step():
+        for op in plan["ops"]:
+            a, k = op.args, op.kind
+            if k == "relu_bwd":
+                put(a["dx"], C.c_void_p(L.rs_relu_backward(H[a["dy"]], H[a["x"]])))
+            elif k == "add_out":
+                put(a["out"], C.c_void_p(L.rs_add(H[a["a"]], H[a["b"]])))
+            elif k == "bn_bwd":
+                out = (C.c_void_p * 3)()
+                L.rs_bn_backward(bn_handles[a["x"]], H[a["dy"]], H[a["x"]], H[a["scale"]], H[a["mean"]], H[a["invstd"]], out)
+                put(a["dx"], C.c_void_p(out[0]))
+                put(a["dscale"], C.c_void_p(out[1]))
+                put(a["dbias"], C.c_void_p(out[2]))
+            elif k == "maxpool_bwd":
+                put(a["dx"], C.c_void_p(L.rs_pool_backward(pool_handles[a["dx"]], H[a["dy"]], H[a["x"]], H[a["y"]])))
+            elif k == "avgpool_bwd":
+                put(a["dx"], C.c_void_p(L.rs_pool_backward(pool_handles[a["dx"]], H[a["dy"]], H[a["dx"] + ".shape"],
+                                                          H[a["dx"] + ".y"])))
+            elif k == "softmax":
+                put(a["y"], C.c_void_p(L.rs_softmax(H[a["x"]])))
+            elif k == "ce_fwd":
+                put(a["loss"], C.c_void_p(L.rs_cross_entropy_fwd(H[a["p"]], H[a["t"]])))
+            elif k == "sum_all":
+                put(a["out"], C.c_void_p(L.rs_sum_all(H[a["x"]])))
+            elif k == "ce_bwd":
+                put(a["grad"], C.c_void_p(L.rs_softmax_cross_entropy_bwd(H[a["p"]], H[a["t"]])))
+            elif k == "scale":
+                L.rs_div_scalar_inplace(H[a["x"]], C.c_float(BATCH))
+            elif k == "sum_rows":
+                put(a["v"], C.c_void_p(L.rs_sum_axis(H[a["M"]], 0)))
+            elif k == "grad_ready":
+                i = index[a["param"]]
+                ev = flush_after.get(i)
+                g = H["d:" + a["param"]]
+                if ev is not None and ev[0] == "direct":
+                    L.rs_comm_synch(comm, g)
+                    continue
+                one = (C.c_void_p * 1)(g)
+                L.rs_comm_fused_synch(comm, one, 1, 0)
+                if ev is not None:
+                    arr = (C.c_void_p * len(ev[1]))(*[H["d:" + order[j]] for j in ev[1]])
+                    L.rs_comm_fused_synch(comm, arr, len(ev[1]), 1)
+            elif k == "sync_and_update":
+                L.rs_comm_wait(comm)
+                for pname in plan["params"]:
+                    g = H["d:" + pname]
+                    L.rs_div_scalar_inplace(g, C.c_float(world))
+                    L.rs_sgd(H[pname], g, H["m:" + pname], lr, mom, wd)
+
+    for _ in range(warmup):
+        step()
+    L.rs_sync()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    L.rs_sync()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / steps * 1e3
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        tt = torch.tensor([ms, wall], dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, wall = float(tt[0]), float(tt[1])
+    L.rs_comm_free(comm)
+    return {"ms_per_step": ms, "host_ms_per_step": wall, "images_per_sec": BATCH * world / (ms / 1e3), "steps": steps,
+            "mode": "eager (the reference launches one operation at a time), unfused call pattern, CUDA events",
+            "library": "oracle/_ref/libref_singa_cuda.so: the reference's sources, compiled unmodified"}
+
+
 def workload_config(world, dist_option, fused, use_graph, pool_argmax, relu_mask=False):
     """The `config` object shared by both arms (same keys, same values)."""
     return {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
@@ -454,6 +612,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra-legs", action="store_true",
                     help="skip the fp16-sync and sparse-exchange legs that ride in the same JSON line")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="skip the leg that runs the reference's own CUDA / NCCL build of the same step")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="cap on the CTAs NCCL's kernels use (0 = default)")
     ap.add_argument("--no-register", action="store_true", help="do not register the gradient arena with NCCL")
     args = ap.parse_args()
@@ -668,8 +828,21 @@ def main():
     gc.collect()
     torch.cuda.synchronize()
 
-    # ---- configurations 4 and 5 with the same code, in the same line
+    # ---- the reference's own CUDA / NCCL path on the same step, same GPUs, same run
     extra = {}
+    if not args.no_extra_legs and not args.no_reference_cuda:
+        try:
+            rc = reference_cuda_leg(torch, dist, path, rank, world, local)
+        except Exception as e:          # the comparator is optional
+            rc = {"unavailable": str(e)[:200]}
+        if rc is not None:
+            if "ms_per_step" in rc:
+                rc["ratio_vs_this_arm"] = rc["ms_per_step"] / ms
+            extra["reference_cuda"] = rc
+        gc.collect()
+        torch.cuda.synchronize()
+
+    # ---- configurations 4 and 5 with the same code, in the same line
     if not args.no_extra_legs and not args.call_pattern:
         other = "half" if args.dist_option == "plain" else "plain"
         K2 = min(K, 50)

@@ -50,22 +50,8 @@ int sgb_version(void);
  * kernel's CTAs are scheduled while the previous kernel of the same stream
  * drains; each such kernel waits for its predecessors' completion before its
  * first access to global memory, so results and stream-order semantics are
- * unchanged.  0 restores plain launches.
- * SGB_OPT_STABLE_FORWARD_INPUTS (default 0): a promise by the caller about the
- * batch-norm backward entry points: x, the ReLU input, scale, mean and the
- * inverse standard deviation were written before the PREVIOUS kernel of the
- * stream started (they are tensors the forward pass saved - true of every call
- * an autograd backward pass makes).  With launch overlap on, the kernels then
- * read those tensors while the previous kernel drains and wait only before
- * they read dy.  Leave it 0 when a forward-side input may have been produced
- * by the kernel just before.
- * SGB_OPT_BN_CLUSTER_SIZE (default 0 = chosen per shape): forces the number of
- * CTAs that share one channel in the single-pass batch-norm kernels (1..16,
- * used when a channel fits that many CTAs' shared memory); for tuning. */
-enum sgb_option {
-  SGB_OPT_OVERLAP_LAUNCHES = 1, SGB_OPT_STABLE_FORWARD_INPUTS = 2,
-  SGB_OPT_BN_CLUSTER_SIZE = 3, SGB_OPT_COUNT_ = 4
-};
+ * unchanged.  0 restores plain launches. */
+enum sgb_option { SGB_OPT_OVERLAP_LAUNCHES = 1, SGB_OPT_COUNT_ = 2 };
 int sgb_set_option(int option, int value);
 int sgb_get_option(int option);
 

@@ -66,6 +66,14 @@ void rs_tensor_to_host_f32(void* h, float* dst) {
   c.GetValue(dst, c.Size());
 }
 void rs_tensor_set(void* h, float v) { T(h).SetValue(v); }
+// Fills the tensor from `bytes` bytes of device memory owned by someone else
+// (a plain device-to-device copy on the default stream).
+int rs_tensor_from_device(void* h, const void* src, size_t bytes) {
+  return static_cast<int>(cudaMemcpy(T(h).block()->mutable_data(), src, bytes, cudaMemcpyDeviceToDevice));
+}
+int rs_tensor_to_device(void* h, void* dst, size_t bytes) {
+  return static_cast<int>(cudaMemcpy(dst, T(h).block()->data(), bytes, cudaMemcpyDeviceToDevice));
+}
 void* rs_tensor_as_type(void* h, int dtype) {
   return own(T(h).AsType(dtype == 1 ? singa::kFloat16 : (dtype == 2 ? singa::kInt : singa::kFloat32)));
 }

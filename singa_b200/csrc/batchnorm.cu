@@ -137,15 +137,17 @@ bn_bwd_reduce_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     UnitWalk w(i0 + threadIdx.x, kBlock, hw4);
     for (int i = i0 + threadIdx.x; i < i1; i += kBlock, w.next()) {
       const size_t off = (static_cast<size_t>(w.n) * sh.C + c) * sh.HW + 4 * w.q;
-      Vec4f vx, vg;
+      Vec4f vx, vg, vm;
       vx.u = ld128(x + off);
       vg.u = ld128(dy + off);
       unsigned bits = 15u;
-      if (MASK) bits = keep4<MASK>(relu_in, off);
+      if (MASK == 1) vm.u = ld128(relu_in + off);
+      if (MASK == 2) bits = keep4<2>(relu_in, off);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float g = vg.f[k];
-        if (MASK) g = (bits >> k) & 1u ? g : 0.0f;
+        if (MASK == 1) g = vm.f[k] > 0 ? g : 0.0f;
+        if (MASK == 2) g = (bits >> k) & 1u ? g : 0.0f;
         s_dy += g;
         s_dyx += g * (vx.f[k] - mu);
       }
@@ -203,11 +205,13 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       if (VEC) {
         vx[j].u = ld128(x + off[j]);
         vg[j].u = ld128(dy + off[j]);
-        if (MASK) vm[j].i[0] = static_cast<int>(keep4<MASK>(relu_in, off[j]));
+        if (MASK == 1) vm[j].u = ld128(relu_in + off[j]);
+        if (MASK == 2) vm[j].i[0] = static_cast<int>(keep4<2>(relu_in, off[j]));
       } else {
         vx[j].f[0] = x[off[j]];
         vg[j].f[0] = dy[off[j]];
-        if (MASK) vm[j].i[0] = keep1<MASK>(relu_in, off[j]) ? 1 : 0;
+        if (MASK == 1) vm[j].f[0] = relu_in[off[j]];
+        if (MASK == 2) vm[j].i[0] = keep1<2>(relu_in, off[j]) ? 1 : 0;
       }
       w.next();
     }
@@ -247,13 +251,15 @@ bn_bwd_apply_kernel(const float* __restrict__ x, const float* __restrict__ dy,
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float g = vg[j].f[i];
-        if (MASK) g = (vm[j].i[0] >> i) & 1 ? g : 0.0f;
+        if (MASK == 1) g = vm[j].f[i] > 0 ? g : 0.0f;
+        if (MASK == 2) g = (vm[j].i[0] >> i) & 1 ? g : 0.0f;
         o.f[i] = k * (g - a - (vx[j].f[i] - mu) * b);
       }
       st128(dx + off[j], o.u);
     } else {
       float g = vg[j].f[0];
-      if (MASK) g = vm[j].i[0] & 1 ? g : 0.0f;
+      if (MASK == 1) g = vm[j].f[0] > 0 ? g : 0.0f;
+      if (MASK == 2) g = vm[j].i[0] & 1 ? g : 0.0f;
       dx[off[j]] = k * (g - a - (vx[j].f[0] - mu) * b);
     }
   }
@@ -285,8 +291,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       float* __restrict__ dx, float* __restrict__ dscale,
                       float* __restrict__ dbias, BnShape sh, int per_cta,
-                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr,
-                      int early = 0) {
+                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
   extern __shared__ __align__(16) float stage[];
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
@@ -304,12 +309,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   float* sg = stage + static_cast<size_t>(per_cta) * kW;
   const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
   const size_t chan_off = static_cast<size_t>(c) * sh.HW;
-  // `early`: the caller vouches that x, the ReLU input and the per-channel
-  // statistics were written before the previous kernel of the stream started
-  // (they are tensors saved by the forward pass), so they may be read while
-  // that kernel drains; only dy waits for it.
-  const bool prefetch = VEC && !ADD && early != 0;
-  if (!prefetch) dependency_wait();                   // first access to global memory follows
+  dependency_wait();                                  // first access to global memory follows
   const float mu = mean[c];
 
   // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
@@ -346,10 +346,6 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         }
       }
     }
-  } else if (prefetch) {
-    UnitWalk w(first, T, hwu);
-    for (int u = first; u < u1; u += T, w.next())
-      cp_async16(sx + (u - u0) * 4, x + (w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4));
   } else {
     UnitWalk w(first, T, hwu);
     for (int u = first; u < u1; u += T, w.next()) {
@@ -365,12 +361,6 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         sg[l] = g;
       }
     }
-  }
-  if (prefetch) {
-    dependency_wait();                                // the gradient is the previous kernel's output
-    UnitWalk w(first, T, hwu);
-    for (int u = first; u < u1; u += T, w.next())
-      cp_async16(sg + (u - u0) * 4, dy + (w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4));
   }
   // fused ReLU: while the copies fly, read the ReLU input and keep only the
   // sign decisions, 4 bits per unit (a share is at most 16 units per thread)
@@ -538,7 +528,7 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
     // x by asynchronous copy; dy and the ReLU input through registers, four
     // units (eight independent 16-byte loads) per round
     for (int u = threadIdx.x; u < units;) {
-      Vec4f vg[4];
+      Vec4f vg[4], vm[4];
       unsigned bits[4];
       int us[4], cnt = 0;
 #pragma unroll
@@ -547,7 +537,8 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
           const size_t off = wl.n * sample_stride + base + 4 * static_cast<size_t>(wl.q);
           cp_async16(sx + 4 * u, x + off);
           vg[j].u = ld128(dy + off);
-          bits[j] = keep4<MASK>(relu_in, off);
+          if (MASK == 1) vm[j].u = ld128(relu_in + off);
+          if (MASK == 2) bits[j] = keep4<2>(relu_in, off);
           us[j] = u;
           u += kBlock;
           wl.next();
@@ -558,7 +549,10 @@ bn_bwd_group_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       for (int j = 0; j < 4; ++j) {
         if (j < cnt) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) vg[j].f[k] = (bits[j] >> k) & 1u ? vg[j].f[k] : 0.0f;
+          for (int k = 0; k < 4; ++k) {
+            if (MASK == 1) vg[j].f[k] = vm[j].f[k] > 0 ? vg[j].f[k] : 0.0f;
+            if (MASK == 2) vg[j].f[k] = (bits[j] >> k) & 1u ? vg[j].f[k] : 0.0f;
+          }
           *reinterpret_cast<uint4*>(sg + 4 * us[j]) = vg[j].u;
         }
       }
@@ -653,14 +647,7 @@ int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int 
   constexpr int max_cs = 8;      // portable cluster size
   constexpr int fill = 0;        // >0 would split small channels further (measured slower on B200)
   const long long kPreferred = share_kb * 1024LL, kLimit = 100 * 1024;
-  const int forced = option(SGB_OPT_BN_CLUSTER_SIZE);
-  if (forced > 0 && forced <= 16) {
-    const long long share = (units_per_channel + forced - 1) / forced;
-    if (share * unit_bytes * 2 <= kLimit && share <= 8192) {
-      *per_cta = static_cast<int>(share);
-      return forced;
-    }
-  }
+
   for (int pass = 0; pass < 2; ++pass) {
     const long long cap = pass == 0 ? kPreferred : kLimit;
     for (int cs = 1; cs <= max_cs; cs *= 2) {
@@ -694,8 +681,7 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
   const int ready = opt_in_once(kernel, attr_set, true);
   if (ready != SGB_OK) return ready;
   return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
-                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined,
-                   option(SGB_OPT_STABLE_FORWARD_INPUTS) && option(SGB_OPT_OVERLAP_LAUNCHES) ? 1 : 0);
+                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined);
 }
 
 template <bool VEC, int MASK>

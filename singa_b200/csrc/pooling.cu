@@ -123,7 +123,7 @@ maxpool_bwd_band_kernel(const float* __restrict__ x, const float* __restrict__ d
         const float* row = xs + (h - xr_lo) * p.W;
         for (int w = w0; w < w1; ++w) {
           const float v = row[w];
-          if (v > best) {
+          if (v > best || (v != v && best == best)) {   // first maximum; a NaN wins and then sticks, as in cuDNN
             best = v;
             bi = h * p.W + w;
           }
@@ -195,7 +195,7 @@ maxpool_bwd_band_fast_kernel(const float* __restrict__ x, const float* __restric
           const int w = ow * S - P + j;
           if (w < 0 || w >= W) continue;
           const float v = row[w];
-          if (v > best) {
+          if (v > best || (v != v && best == best)) {   // first maximum; a NaN wins and then sticks, as in cuDNN
             best = v;
             bi = h * W + w;
           }
@@ -303,7 +303,7 @@ maxpool_bwd_k3s2p1_kernel(const float* __restrict__ x, const float* __restrict__
 #pragma unroll
       for (int j = 0; j < 3; ++j) {
         const float v = win[i * pitch + j];
-        if (v > best) {
+        if (v > best || (v != v && best == best)) {   // first maximum; a NaN wins and then sticks, as in cuDNN
           best = v;
           bi = g0 + i * W + j;
         }

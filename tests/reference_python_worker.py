@@ -18,10 +18,13 @@ from singa_b200.adapter import py_compat   # noqa: E402
 
 
 def main(variant, out_path, mode):
+    if variant == "sgb":
+        # torch ships a newer NCCL under the same soname: it must be loaded
+        # before the extension module pulls in the system one
+        import torch  # noqa: F401
     py_compat.use(variant)
     from singa import device, layer, model, opt, singa_wrap, tensor
     if variant == "sgb":
-        import torch  # noqa: F401  (loads the CUDA libraries the module needs)
         dev = device.create_cuda_gpu_on(0)
     else:
         dev = device.get_default_device()

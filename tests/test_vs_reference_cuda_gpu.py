@@ -286,3 +286,16 @@ def test_maxpool_forward_propagates_nan_like_cudnn(sw, rd):
         assert torch.equal(torch.isnan(got2), torch.isnan(want))
         keep = ~torch.isnan(want)
         assert torch.equal(got[keep], want[keep]) and torch.equal(got2[keep], want[keep])
+        # backward: cuDNN sends a window's gradient to its first NaN; so do the kernel that
+        # recomputes the winners from x and the one that reads the forward's record
+        dy = torch.ones_like(want)
+        dx_want, dx_got, dx_rec = torch.zeros_like(x), torch.zeros_like(x), torch.zeros_like(x)
+        assert rd.refcudnn_pooling(1, 1, N, Cc, H, W, OH, OH, k, k, pd, pd, s, s, p(x), p(want), p(dy), p(dx_want),
+                                   None) == 0
+        _lib.call("sgb_maxpool_backward_f32", x.data_ptr(), got.data_ptr(), dy.data_ptr(), dx_got.data_ptr(), N, Cc, H,
+                  W, k, k, pd, pd, s, s, torch.cuda.current_stream().cuda_stream)
+        _lib.call("sgb_maxpool_backward_argmax_f32", dy.data_ptr(), rec.data_ptr(), dx_rec.data_ptr(), N, Cc, H, W, k,
+                  k, pd, pd, s, s, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert torch.equal(dx_got, dx_want), "winners recomputed from x"
+        assert torch.equal(dx_rec, dx_want), "winners from the forward's record"
