@@ -273,6 +273,16 @@ __device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_sr
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Returns once at most PENDING of this thread's most recent copy groups are still in flight.
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait_pending() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+// A thread issues its copies in kCopyGroups groups, so that it can start adding
+// up the units of the first group while the later ones are still in flight
+// (a thread only ever reads back what it staged itself: no barrier needed).
+constexpr int kCopyGroups = 4;
 
 // CTA size of the single-pass kernel: 512 threads for large shares (fewer
 // serial iterations per thread), 256 for small ones.
@@ -311,6 +321,8 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const size_t chan_off = static_cast<size_t>(c) * sh.HW;
   dependency_wait();                                  // first access to global memory follows
   const float mu = mean[c];
+  // units of one copy group per thread (the same in every thread: kCopyGroups * group_units covers a share)
+  const int group_units = ((per_cta + T - 1) / T + kCopyGroups - 1) / kCopyGroups;
 
   // phase 1: stage this CTA's share (asynchronous 16-byte copies, all in flight at once)
   if (VEC && ADD) {
@@ -346,20 +358,28 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         }
       }
     }
+  } else if (VEC) {
+    UnitWalk w(first, T, hwu);
+    int u = first;
+#pragma unroll
+    for (int g = 0; g < kCopyGroups; ++g) {
+      for (int k = 0; k < group_units && u < u1; ++k, u += T, w.next()) {
+        const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4;
+        const int l = (u - u0) * 4;
+        cp_async16(sx + l, x + off);
+        cp_async16(sg + l, dy + off);
+      }
+      cp_async_commit();
+    }
   } else {
     UnitWalk w(first, T, hwu);
     for (int u = first; u < u1; u += T, w.next()) {
-      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * kW;
-      const int l = (u - u0) * kW;
-      if (VEC) {
-        cp_async16(sx + l, x + off);
-        cp_async16(sg + l, dy + off);
-      } else {
-        float g = dy[off];
-        if (MASK) g = keep1<MASK>(relu_in, off) ? g : 0.0f;
-        sx[l] = x[off];
-        sg[l] = g;
-      }
+      const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q);
+      const int l = u - u0;
+      float g = dy[off];
+      if (MASK) g = keep1<MASK>(relu_in, off) ? g : 0.0f;
+      sx[l] = x[off];
+      sg[l] = g;
     }
   }
   // fused ReLU: while the copies fly, read the ReLU input and keep only the
@@ -402,33 +422,47 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       }
     }
   }
-  if (VEC) cp_async_wait_all();
+  if (VEC && ADD) cp_async_wait_all();
 
-  // phase 2: partial sums over the share (each thread re-reads what it staged)
+  // phase 2: partial sums over the share (each thread re-reads what it staged),
+  // copy group by copy group as the groups land; the order of the additions is
+  // the order of the units, whatever the grouping
   float s_dy = 0.f, s_dyx = 0.f;
-  {
-    int slot = 0;
-    for (int u = first; u < u1; u += T, slot += 4) {
-      const int l = (u - u0) * kW;
-      if (VEC) {
+  if (VEC) {
+    int slot = 0, u = first;
+    auto sum_copy_group = [&]() {
+      for (int k = 0; k < group_units && u < u1; ++k, u += T, slot += 4) {
+        const int l = (u - u0) * 4;
         Vec4f vx, vg;
         vx.u = *reinterpret_cast<const uint4*>(sx + l);
         vg.u = *reinterpret_cast<const uint4*>(sg + l);
         if (MASK && !ADD) {
           const unsigned bits = static_cast<unsigned>(keep >> slot);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) vg.f[k] = (bits >> k) & 1u ? vg.f[k] : 0.0f;
+          for (int q = 0; q < 4; ++q) vg.f[q] = (bits >> q) & 1u ? vg.f[q] : 0.0f;
           *reinterpret_cast<uint4*>(sg + l) = vg.u;    // keep the masked gradient for phase 3
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          s_dy += vg.f[k];
-          s_dyx += vg.f[k] * (vx.f[k] - mu);
+        for (int q = 0; q < 4; ++q) {
+          s_dy += vg.f[q];
+          s_dyx += vg.f[q] * (vx.f[q] - mu);
         }
-      } else {
-        s_dy += sg[l];
-        s_dyx += sg[l] * (sx[l] - mu);
       }
+    };
+    static_assert(kCopyGroups == 4, "the waits below are written out for four groups");
+    if (!ADD) cp_async_wait_pending<3>();
+    sum_copy_group();
+    if (!ADD) cp_async_wait_pending<2>();
+    sum_copy_group();
+    if (!ADD) cp_async_wait_pending<1>();
+    sum_copy_group();
+    if (!ADD) cp_async_wait_pending<0>();
+    sum_copy_group();
+  } else {
+    for (int u = first; u < u1; u += T) {
+      const int l = u - u0;
+      s_dy += sg[l];
+      s_dyx += sg[l] * (sx[l] - mu);
     }
   }
   // one block reduction for both sums (fixed order), then every CTA pushes its
