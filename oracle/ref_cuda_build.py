@@ -133,6 +133,38 @@ def build_variant(variant, force=False):
     return lib
 
 
+GTEST_SOURCES = ["test/gtest/gtest-all.cc", "test/gtest/gtest_main.cc", "test/singa/test_tensor_math.cc",
+                 "test/singa/test_tensor.cc"]
+
+
+def gtest_binary(variant):
+    return os.path.join(OUT, "singa_gtest_" + variant)
+
+
+def build_gtests(variant, force=False):
+    """The reference's OWN unit tests - test/singa/test_tensor_math.cc and
+    test_tensor.cc with its vendored gtest - compiled unmodified and linked
+    against one of the two core builds.  Returns the binary's path (None when
+    neither the reference tree nor a prebuilt binary is present)."""
+    lib = build_variant(variant)
+    exe = gtest_binary(variant)
+    ref = lambda p: os.path.join(REFERENCE, p)
+    if lib is None or not os.path.exists(ref(GTEST_SOURCES[0])):
+        return exe if os.path.exists(exe) else None
+    if not force and not _stale(exe, [lib] + [ref(g) for g in GTEST_SOURCES]):
+        return exe
+    objdir = os.path.join(OUT, "gtest_obj_" + variant)
+    os.makedirs(objdir, exist_ok=True)
+    extra = ("-I", ref("test"))
+    with ThreadPoolExecutor(max_workers=4) as ex:
+        objs = list(ex.map(lambda g: _cxx(ref(g), os.path.join(objdir, os.path.basename(g)[:-3] + ".o"), extra),
+                           GTEST_SOURCES))
+    subprocess.check_call(["g++", "-o", exe] + objs + [lib, "-lpthread", "-L/usr/local/cuda/lib64", "-lcudart",
+                           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../singa_b200", "-Wl,-rpath," + OUT,
+                           "-Wl,-rpath," + PKG])
+    return exe
+
+
 def _cblas(obj):
     subprocess.check_call(["gcc", "-O3", "-mavx2", "-mfma", "-fopenmp", "-fPIC", "-I", SHIMS, "-c",
                            os.path.join(SHIMS, "ref_cblas.c"), "-o", obj])
@@ -143,3 +175,4 @@ if __name__ == "__main__":
     import sys
     for v in (sys.argv[1:] or ["reference"]):
         print(build_variant(v, force=True))
+        print(build_gtests(v, force=True))

@@ -109,8 +109,8 @@ def main(variant, out_path):
         R[tag + "_y"] = core.numpy(y)
         dy = core.tensor(rng.standard_normal(R[tag + "_y"].shape).astype(np.float32))
         R[tag + "_dx"] = core.numpy(core.call("rs_pool_backward", h, dy, tx, y))
+    dyc = f32(6, 32, 24, 24)              # drawn in both variants: the random stream must stay aligned
     if variant == "sgb":
-        dyc = f32(6, 32, 24, 24)
         R["conv_bias_backward"] = core.numpy(core.call("rs_conv_bias_backward", core.tensor(dyc),
                                                        core.tensor(np.zeros(32, np.float32))))
         R["conv_bias_backward_want"] = dyc.astype(np.float64).sum((0, 2, 3)).astype(np.float32)
