@@ -40,9 +40,12 @@ struct Pool {
   std::map<size_t, std::vector<void*>> free_blocks;   // by rounded size
   std::map<void*, size_t> live;                       // every block ever handed out -> rounded size
 };
+// Never destroyed: the device that owns the memory pool is itself a static
+// (Platform::UsedDevice) and finalises the pool from its destructor at process
+// exit, possibly after a function-local static here would already be gone.
 inline Pool& pool() {
-  static Pool p;
-  return p;
+  static Pool* p = new Pool;
+  return *p;
 }
 inline size_t rounded(size_t n) { return (n + 511) & ~static_cast<size_t>(511); }
 }  // namespace sgb_cnmem

@@ -301,7 +301,8 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       float* __restrict__ dx, float* __restrict__ dscale,
                       float* __restrict__ dbias, BnShape sh, int per_cta,
-                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
+                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr,
+                      int stream_stores = 0) {
   extern __shared__ __align__(16) float stage[];
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
@@ -541,171 +542,10 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         vg.u = *reinterpret_cast<const uint4*>(sg + l);
 #pragma unroll
         for (int j = 0; j < 4; ++j) o.f[j] = k_ * (vg.f[j] - am - (vx.f[j] - mu) * bm);
-        st128(dx + off, o.u);
+        if (stream_stores) st128_stream(dx + off, o.u);
+        else st128(dx + off, o.u);
       } else {
         dx[off] = k_ * (sg[l] - am - (sx[l] - mu) * bm);
-      }
-    }
-  }
-}
-
-// ---------------------------------------------- single pass, x staged only
-// Variant of the kernel above that keeps only x in shared memory: dy is read
-// twice, the first time from HBM while the sums are formed (through
-// registers), the second time - a few microseconds later, by the same SM -
-// from L2 when dx is computed.  HBM traffic is unchanged (12 B/element) while a
-// share costs half the shared memory, so twice as many CTAs are resident per SM
-// and more of them are in different phases at any moment.
-template <int MASK, int T>
-__global__ void __launch_bounds__(T)
-bn_bwd_cluster_x_kernel(const float* __restrict__ x, const float* __restrict__ dy,
-                        const float* __restrict__ relu_in, const float* __restrict__ scale,
-                        const float* __restrict__ mean, const float* __restrict__ invstd,
-                        float* __restrict__ dx, float* __restrict__ dscale,
-                        float* __restrict__ dbias, BnShape sh, int per_cta) {
-  extern __shared__ __align__(16) float stage[];
-  __shared__ float red[2 * T / 32];
-  __shared__ float2 parts[16];
-  cg::cluster_group cluster = cg::this_cluster();
-  const int cs = static_cast<int>(cluster.num_blocks());
-  const int rank = static_cast<int>(cluster.block_rank());
-  const int c = blockIdx.x / cs;
-  cluster.barrier_arrive();
-  const int hwu = sh.HW / 4;
-  const int total = sh.N * hwu;
-  const int u0 = min(rank * per_cta, total), u1 = min(u0 + per_cta, total);
-  const int first = u0 + threadIdx.x;
-  const size_t plane_stride = static_cast<size_t>(sh.C) * sh.HW;
-  const size_t chan_off = static_cast<size_t>(c) * sh.HW;
-  const int group_units = ((per_cta + T - 1) / T + kCopyGroups - 1) / kCopyGroups;   // <= 4
-  dependency_wait();
-  const float mu = mean[c];
-
-  // phase 1: x into shared memory, group by group
-  {
-    UnitWalk w(first, T, hwu);
-    int u = first;
-#pragma unroll
-    for (int g = 0; g < kCopyGroups; ++g) {
-      for (int k = 0; k < group_units && u < u1; ++k, u += T, w.next())
-        cp_async16(stage + (u - u0) * 4, x + (w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4));
-      cp_async_commit();
-    }
-  }
-  // phase 2: dy (and the ReLU decisions) through registers, one copy group of x at a time
-  float s_dy = 0.f, s_dyx = 0.f;
-  unsigned long long keep = 0;
-  {
-    UnitWalk w(first, T, hwu);
-    int u = first, slot = 0;
-    // written out four times: cp.async.wait_group takes an immediate operand
-#define SGB_BN_X_GROUP(PENDING)                                                            \
-    {                                                                                      \
-      Vec4f vg[4];                                                                         \
-      unsigned bits[4];                                                                    \
-      int ls[4], cnt = 0;                                                                  \
-      _Pragma("unroll") for (int k = 0; k < 4; ++k) {                                      \
-        bits[k] = 15u;                                                                     \
-        if (k < group_units && u < u1) {                                                   \
-          const size_t off = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4; \
-          vg[k].u = ld128(dy + off);                                                       \
-          if (MASK) bits[k] = keep4<MASK>(relu_in, off);                                   \
-          ls[k] = (u - u0) * 4;                                                            \
-          u += T;                                                                          \
-          w.next();                                                                        \
-          cnt = k + 1;                                                                     \
-        }                                                                                  \
-      }                                                                                    \
-      cp_async_wait_pending<PENDING>();                                                    \
-      _Pragma("unroll") for (int k = 0; k < 4; ++k) {                                      \
-        if (k < cnt) {                                                                     \
-          Vec4f vx;                                                                        \
-          vx.u = *reinterpret_cast<const uint4*>(stage + ls[k]);                           \
-          _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                  \
-            const float g = (bits[k] >> q) & 1u ? vg[k].f[q] : 0.0f;                       \
-            s_dy += g;                                                                     \
-            s_dyx += g * (vx.f[q] - mu);                                                   \
-          }                                                                                \
-          if (MASK) keep |= static_cast<unsigned long long>(bits[k]) << slot;              \
-          slot += 4;                                                                       \
-        }                                                                                  \
-      }                                                                                    \
-    }
-    SGB_BN_X_GROUP(3)
-    SGB_BN_X_GROUP(2)
-    SGB_BN_X_GROUP(1)
-    SGB_BN_X_GROUP(0)
-#undef SGB_BN_X_GROUP
-  }
-  {
-    constexpr int kWarps = T / 32;
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    s_dy = warp_sum(s_dy);
-    s_dyx = warp_sum(s_dyx);
-    if (lane == 0) {
-      red[wid] = s_dy;
-      red[kWarps + wid] = s_dyx;
-    }
-    __syncthreads();
-    if (wid == 0) {
-      float p0 = lane < kWarps ? red[lane] : 0.0f;
-      float p1 = lane < kWarps ? red[kWarps + lane] : 0.0f;
-      p0 = warp_sum(p0);
-      p1 = warp_sum(p1);
-      cluster.barrier_wait();
-      if (lane < cs) *cluster.map_shared_rank(&parts[rank], lane) = make_float2(p0, p1);
-    } else {
-      cluster.barrier_wait();
-    }
-  }
-  cluster.sync();
-  float a = 0.f, b = 0.f;
-  for (int r = 0; r < cs; ++r) {
-    a += parts[r].x;
-    b += parts[r].y;
-  }
-  const float r_ = invstd[c];
-  const float inv_m = 1.0f / (static_cast<float>(sh.N) * static_cast<float>(sh.HW));
-  const float ds = b * r_;
-  const float k_ = scale[c] * r_, am = a * inv_m, bm = ds * r_ * inv_m;
-  if (rank == 0 && threadIdx.x == 0) {
-    dscale[c] = ds;
-    dbias[c] = a;
-  }
-  // phase 3: dy again (an L2 hit), x from shared memory
-  release_dependents();
-  {
-    UnitWalk w(first, T, hwu);
-    int slot = 0;
-    for (int u = first; u < u1;) {
-      Vec4f vg[4];
-      size_t offs[4];
-      int ls[4], cnt = 0;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (u < u1) {
-          offs[k] = w.n * plane_stride + chan_off + static_cast<size_t>(w.q) * 4;
-          vg[k].u = ld128(dy + offs[k]);
-          ls[k] = (u - u0) * 4;
-          u += T;
-          w.next();
-          cnt = k + 1;
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (k < cnt) {
-          Vec4f vx, o;
-          vx.u = *reinterpret_cast<const uint4*>(stage + ls[k]);
-          const unsigned bits = MASK ? static_cast<unsigned>(keep >> slot) & 15u : 15u;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float g = (bits >> q) & 1u ? vg[k].f[q] : 0.0f;
-            o.f[q] = k_ * (g - am - (vx.f[q] - mu) * bm);
-          }
-          st128(dx + offs[k], o.u);
-          slot += 4;
-        }
       }
     }
   }
@@ -897,7 +737,8 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
   const int ready = opt_in_once(kernel, attr_set, true);
   if (ready != SGB_OK) return ready;
   return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
-                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined);
+                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined,
+                   getenv("SGB_BN_STREAM_STORES") ? atoi(getenv("SGB_BN_STREAM_STORES")) : 0);   // experiment
 }
 
 template <bool VEC, int MASK>
@@ -910,31 +751,6 @@ int launch_cluster(const float* x, const float* dy, const float* relu_in, const 
                                             sh, cs, per_cta, s);
   return launch_cluster_t<VEC, MASK, 256>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh,
                                           cs, per_cta, s);
-}
-
-template <int MASK, int T>
-int launch_cluster_x_t(const float* x, const float* dy, const float* relu_in, const float* scale,
-                       const float* mean, const float* invstd, float* dx, float* dscale, float* dbias,
-                       BnShape sh, int cs, int per_cta, cudaStream_t s) {
-  auto kernel = bn_bwd_cluster_x_kernel<MASK, T>;
-  static std::atomic<bool> attr_set[64];
-  const int ready = opt_in_once(kernel, attr_set, true);
-  if (ready != SGB_OK) return ready;
-  return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), static_cast<size_t>(per_cta) * 16, s, cs,
-                   true, x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, per_cta);
-}
-
-// Cluster size and share for the x-staged kernel: the smallest cluster whose
-// share of x fits `cap` bytes; 0 when a channel does not fit 8 CTAs.
-int cluster_plan_x(long long units_per_channel, long long cap, int* per_cta) {
-  for (int cs = 1; cs <= 8; cs *= 2) {
-    const long long share = (units_per_channel + cs - 1) / cs;
-    if (share * 16 <= cap && share <= 8192) {
-      *per_cta = static_cast<int>(share);
-      return cs;
-    }
-  }
-  return 0;
 }
 
 // Per-activation mode (N x D, one statistic per feature): a thread owns one
@@ -998,16 +814,6 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
       if (G == 4)
         return launch_group<MASK, 4>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
       return launch_group<MASK, 2>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
-    }
-  }
-  if (vec) {
-    static const int x_only_kb = getenv("SGB_X_ONLY_KB") ? atoi(getenv("SGB_X_ONLY_KB")) : 0;   // experiment
-    int per_cta = 0;
-    const int cs = x_only_kb > 0 ? cluster_plan_x(per_channel / 4, x_only_kb * 1024LL, &per_cta) : 0;
-    if (cs > 0) {
-      if (per_cta > 2048)
-        return launch_cluster_x_t<MASK, 512>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, cs, per_cta, s);
-      return launch_cluster_x_t<MASK, 256>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, cs, per_cta, s);
     }
   }
   {
