@@ -81,8 +81,9 @@ int sgb_add_relu_backward_f32(const float *dy_a, const float *dy_b,
 /* ReLU with a one-bit-per-element record - a forward partner (it changes what
  * the backward pass consumes, so it is opt-in): y = max(x, 0) and bit i & 31
  * of 32-bit word i >> 5 of `mask` = (x[i] > 0), the rule of cuda::relubackward
- * (math_kernel.cu:253-259).  `mask` holds sgb_relu_mask_bytes(n) bytes, 4-byte
- * aligned.  The three backward forms read the record instead of the stored
+ * (math_kernel.cu:253-259).  `mask` holds sgb_relu_mask_bytes(n) bytes (the
+ * record rounded up to whole 16-byte groups; the backward forms may read the
+ * padding, never interpret it), 4-byte aligned.  The three backward forms read the record instead of the stored
  * input (1/32 of its bytes) and give bit-identical results:
  *   relu_backward_mask      dx = bit ? dy : 0
  *   add_relu_backward_mask  dx = bit ? dy_a + dy_b : 0      (join + ReLU)
@@ -204,6 +205,13 @@ int sgb_strided_copy_f32(const float *in, float *out, size_t n, int nDim,
 int sgb_strided_copy_f16(const void *in, void *out, size_t n, int nDim,
                          const int *shape_host, const int *stride_host,
                          void *stream);
+/* The inverse: out[offset(i)] = in[i], shape/stride describing `out` (no
+ * broadcast dimension).  Used where the reference lets an elementwise op
+ * write into a transposed view through a strided cuDNN output descriptor
+ * (tensor_math_cuda.h:300-330, e.g. Exp into Transpose(x)). */
+int sgb_strided_scatter_f32(const float *in, float *out, size_t n, int nDim,
+                            const int *shape_host, const int *stride_host,
+                            void *stream);
 /* The same gather with shape/stride in DEVICE memory - the literal calling
  * convention of cuda::traverse_unary_transform (math_kernel.h:95-100), for an
  * adapter that keeps that signature. */
@@ -346,6 +354,13 @@ int sgb_bn_forward_training_f32(const float *x, const float *scale,
                                 float *y, float *save_mean, float *save_invstd,
                                 int N, int C, int HW, void *ws, size_t ws_bytes,
                                 void *stream);
+/* Diagnostic for the streaming form of the batch-norm backward kernels, whose
+ * CTAs meet through counters in device memory with bounded waits: *flags
+ * receives the sticky fault word of the current device (0 = none; bit 0 a
+ * wait ran out, bit 1 a counter table was still in use by another launch - at
+ * most eight such launches may be in flight per device).  A faulted launch
+ * stops early and its outputs are undefined.  Synchronises the device. */
+int sgb_bn_backward_faults(unsigned *flags);
 /* Batch-norm backward for callers that can neither allocate device memory nor
  * hand in a workspace.  (No counterpart in the reference: this entry point
  * exists only in this library.)  Typical callers: an operator running inside

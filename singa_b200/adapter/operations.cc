@@ -65,6 +65,7 @@ const std::vector<Tensor> GpuBatchNormBackward(const CudnnBatchNormHandle& cbnh,
 
   dx.device()->Exec(
       [=](Context* ctx) mutable {
+        (void)cudaGetLastError();   // drop an error parked by an earlier unchecked call
         check(sgb_bn_backward_f32(static_cast<const float*>(x.block()->data()),
                                   static_cast<const float*>(dy.block()->data()),
                                   static_cast<const float*>(bnScale.block()->data()),
@@ -102,6 +103,7 @@ Tensor GpuPoolingBackward(const CudnnPoolingHandle& cph, const Tensor& dy, const
       [=](Context* ctx) mutable {
         const float* g = static_cast<const float*>(dy.block()->data());
         float* out = static_cast<float*>(dx.block()->mutable_data());
+        (void)cudaGetLastError();   // drop an error parked by an earlier unchecked call
         if (is_max)
           check(sgb_maxpool_backward_f32(static_cast<const float*>(x.block()->data()),
                                          static_cast<const float*>(y.block()->data()), g, out, N, C, H, W, kh, kw,
@@ -132,6 +134,7 @@ Tensor GpuConvBackwardb(const Tensor& dy, const Tensor& b, const CudnnConvHandle
 
   dy.device()->Exec(
       [=](Context* ctx) mutable {
+        (void)cudaGetLastError();
         check(sgb_conv_bias_backward_f32(static_cast<const float*>(dy.block()->data()),
                                          static_cast<float*>(db.block()->mutable_data()), N, C, HW,
                                          ws.block()->mutable_data(), ws.Size() * sizeof(float), ctx->stream),

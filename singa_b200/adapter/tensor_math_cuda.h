@@ -41,9 +41,21 @@ namespace singa {
 namespace sgb_backend {
 
 inline void check(int status, const char* what) {
-  if (status != SGB_OK) LOG(FATAL) << what << ": " << sgb_status_string(status) << " (status " << status << ")";
+  if (status == SGB_OK) return;
+  if (status == SGB_ERR_CUDA)
+    LOG(FATAL) << what << ": " << sgb_status_string(status) << ": "
+               << cudaGetErrorString(static_cast<cudaError_t>(sgb_last_cuda_error()));
+  LOG(FATAL) << what << ": " << sgb_status_string(status) << " (status " << status << ")";
 }
-#define SGB_CALL(call) ::singa::sgb_backend::check((call), #call)
+// The library reports launch errors through the runtime's per-thread last-error
+// slot.  An error parked there by an earlier unchecked call of another library
+// (SINGA itself checks no launches) is dropped first, so that it is not taken
+// for this call's; sticky errors survive the read and are still reported.
+#define SGB_CALL(call)                               \
+  do {                                               \
+    (void)cudaGetLastError();                        \
+    ::singa::sgb_backend::check((call), #call);      \
+  } while (0)
 inline void check_cudnn_status(cudnnStatus_t status, const char* what) {
   if (status != CUDNN_STATUS_SUCCESS) LOG(FATAL) << what << ": " << cudnnGetErrorString(status);
 }
@@ -85,17 +97,37 @@ inline const T* dense(const Tensor& in, const Tensor& like, Tensor* tmp, Context
   return rd<T>(*tmp);
 }
 
-// out = f(in) for a one-input kernel: directly when the layouts agree,
-// otherwise the view is first gathered into `out` and the kernel runs in place.
+// True when the tensor's elements lie in memory in row-major order of its shape.
+inline bool row_major(const Tensor& t) { return !t.transpose() && !t.broadcasted(); }
+
+// out = f(in) for a one-input kernel: directly when the layouts agree;
+// otherwise the input view is first gathered into a dense array and the
+// kernel runs in place on it.  The dense array is `out` itself when `out` is
+// row-major; when `out` is a transposed view (the reference writes it through
+// a strided output descriptor) it is a temporary that is scattered into `out`.
 template <typename Launch>
 inline void unary_f32(const Tensor& in, Tensor* out, Context* ctx, Launch launch) {
   float* o = wr<float>(out);
   const size_t n = in.Size();
   if (in.stride() == out->stride()) {
     launch(rd<float>(in), o, n);
-  } else {
+  } else if (row_major(*out)) {
     gather<float>(in, o, n, ctx);
     launch(o, o, n);
+  } else {
+    Tensor tmp(in.shape(), in.device(), kFloat32);
+    float* d = wr<float>(&tmp);
+    if (row_major(in)) {
+      launch(rd<float>(in), d, n);
+    } else {
+      gather<float>(in, d, n, ctx);
+      launch(d, d, n);
+    }
+    const int nd = static_cast<int>(out->nDim());
+    CHECK_LE(nd, 8) << "views of more than 8 dimensions are not supported";
+    std::vector<int> shape(out->shape().begin(), out->shape().end());
+    std::vector<int> stride(out->stride().begin(), out->stride().end());
+    SGB_CALL(sgb_strided_scatter_f32(d, o, n, nd, shape.data(), stride.data(), ctx->stream));
   }
 }
 

@@ -32,6 +32,7 @@
 
 #include <atomic>
 
+#include "bn_stream.cuh"
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -301,8 +302,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       float* __restrict__ dx, float* __restrict__ dscale,
                       float* __restrict__ dbias, BnShape sh, int per_cta,
-                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr,
-                      int stream_stores = 0) {
+                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
   extern __shared__ __align__(16) float stage[];
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
@@ -542,8 +542,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         vg.u = *reinterpret_cast<const uint4*>(sg + l);
 #pragma unroll
         for (int j = 0; j < 4; ++j) o.f[j] = k_ * (vg.f[j] - am - (vx.f[j] - mu) * bm);
-        if (stream_stores) st128_stream(dx + off, o.u);
-        else st128(dx + off, o.u);
+        st128(dx + off, o.u);
       } else {
         dx[off] = k_ * (sg[l] - am - (sx[l] - mu) * bm);
       }
@@ -737,8 +736,7 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
   const int ready = opt_in_once(kernel, attr_set, true);
   if (ready != SGB_OK) return ready;
   return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
-                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined,
-                   getenv("SGB_BN_STREAM_STORES") ? atoi(getenv("SGB_BN_STREAM_STORES")) : 0);   // experiment
+                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined);
 }
 
 template <bool VEC, int MASK>
@@ -815,6 +813,13 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
         return launch_group<MASK, 4>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
       return launch_group<MASK, 2>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
     }
+  }
+  if (vec && ws && aligned16(ws) && ws_bytes >= bn_stream_workspace_bytes(N, C, HW) &&
+      (MASK != 2 || aligned16(relu_in))) {
+    static const int use_stream = getenv("SGB_BN_STREAM") ? atoi(getenv("SGB_BN_STREAM")) : 0;   // experiment
+    BnStreamPlan plan;
+    if (use_stream && bn_stream_plan(N, C, HW, MASK, &plan))
+      return bn_stream_backward(MASK, x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, N, C, HW, plan, ws, s);
   }
   {
     int per_cta = 0;
@@ -1186,6 +1191,8 @@ size_t sgb_bn_backward_workspace_bytes(int N, int C, int HW) {
   if (N <= 0 || C <= 0 || HW <= 0) return 0;
   return static_cast<size_t>(kMaxSlices) * C * sizeof(float2);
 }
+
+int sgb_bn_backward_faults(unsigned* flags) { return bn_stream_faults(flags); }
 
 int sgb_bn_backward_f32(const float* x, const float* dy, const float* scale, const float* mean,
                         const float* invstd, float* dx, float* dscale, float* dbias, int N,

@@ -12,8 +12,8 @@
 //   flush   = collective + one multi-tensor unpack (+ fp16->fp32 cast) launch
 //   sparse  = residual + select + order-preserving compaction, radix select
 //             instead of a full sort, one scatter-add launch per rank.
-// Each cross-stream edge has its own event.  No TMA multicast and no peer
-// pointers are used: remote data reaches local HBM through NCCL only.
+// Each cross-stream edge has its own event.  No kernel here touches another
+// GPU's memory: remote data reaches local HBM through NCCL only.
 #include <nccl.h>
 
 #include <atomic>

@@ -391,7 +391,8 @@ struct Dims {
   int shape[8];
   int stride[8];
 };
-template <typename T>
+// SCATTER: the strides describe `out` instead (out[offset(i)] = in[i]).
+template <typename T, bool SCATTER = false>
 __global__ void __launch_bounds__(kBlock)
 strided_copy_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, Dims d) {
   for (size_t i = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; i < n;
@@ -403,7 +404,8 @@ strided_copy_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n, Dim
       rem -= idx * accu;
       off += idx * static_cast<size_t>(d.stride[k]);
     }
-    out[i] = in[off];
+    if (SCATTER) out[off] = in[i];
+    else out[i] = in[off];
   }
 }
 
@@ -433,7 +435,7 @@ strided_copy_dev_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n,
   }
 }
 
-template <typename T>
+template <typename T, bool SCATTER = false>
 int strided_copy(const T* in, T* out, size_t n, int nDim, const int* shape_host,
                  const int* stride_host, void* stream) {
   if (n == 0) return SGB_OK;
@@ -444,13 +446,14 @@ int strided_copy(const T* in, T* out, size_t n, int nDim, const int* shape_host,
   size_t prod = 1;
   for (int k = 0; k < nDim; ++k) {
     if (shape_host[k] <= 0 || stride_host[k] < 0) return SGB_ERR_SIZE;
+    if (SCATTER && stride_host[k] == 0 && shape_host[k] > 1) return SGB_ERR_SIZE;   // a broadcast view cannot be written
     d.shape[k] = shape_host[k];
     d.stride[k] = stride_host[k];
     prod *= static_cast<size_t>(shape_host[k]);
   }
   if (prod != n) return SGB_ERR_SIZE;
   unsigned grid = capped_grid(n, kBlock, kCtasPerSm);
-  strided_copy_kernel<T><<<grid, kBlock, 0, as_stream(stream)>>>(in, out, n, d);
+  strided_copy_kernel<T, SCATTER><<<grid, kBlock, 0, as_stream(stream)>>>(in, out, n, d);
   return launch_status();
 }
 
@@ -592,7 +595,8 @@ struct FAddReluBwdMask {
 extern "C" {
 using namespace sgb;
 
-size_t sgb_relu_mask_bytes(size_t n) { return 4 * ((n + 31) / 32); }
+// Whole 16-byte groups: the batch-norm form copies the record in 16-byte units.
+size_t sgb_relu_mask_bytes(size_t n) { return 16 * ((n + 127) / 128); }
 
 int sgb_relu_forward_mask_f32(const float* x, float* y, void* mask, size_t n, void* stream) {
   if (n == 0) return SGB_OK;
@@ -765,6 +769,10 @@ int sgb_axpy_dev_alpha_f32(const float* alpha_dev, const float* x, float* y, siz
 int sgb_strided_copy_f32(const float* in, float* out, size_t n, int nDim,
                          const int* shape_host, const int* stride_host, void* stream) {
   return strided_copy<float>(in, out, n, nDim, shape_host, stride_host, stream);
+}
+int sgb_strided_scatter_f32(const float* in, float* out, size_t n, int nDim, const int* shape_host,
+                            const int* stride_host, void* stream) {
+  return strided_copy<float, true>(in, out, n, nDim, shape_host, stride_host, stream);
 }
 int sgb_strided_copy_f16(const void* in, void* out, size_t n, int nDim, const int* shape_host,
                          const int* stride_host, void* stream) {
