@@ -15,8 +15,15 @@
 // copy.  Shares are sized so that two to four CTAs are resident per SM and
 // the load phase of one overlaps the store phase of another.
 //
+// Channels too large for a cluster (e.g. 32 x 112 x 112) are also done in one
+// pass, by the streaming kernel of bn_stream.cu: persistent small CTAs take
+// 50 KB items of a channel from a ticket counter and meet through counters in
+// global memory.
+//
 // Two-pass scheme, 20 bytes of HBM traffic per element when the tensor does
-// not fit L2 (channels too large for a cluster, e.g. 32 x 112 x 112):
+// not fit L2; the fallback for planes that are not a multiple of four floats,
+// misaligned operands, more than 4096 channels, and the entry point without
+// workspace:
 //   pass 1  grid (slices, C): a CTA walks its slice of the channel's flattened
 //           (n, hw) space with 128-bit loads and leaves two partial sums in the
 //           workspace (no atomics, fixed order -> run-to-run identical);
@@ -814,13 +821,6 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
       return launch_group<MASK, 2>(x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, sh, s);
     }
   }
-  if (vec && ws && aligned16(ws) && ws_bytes >= bn_stream_workspace_bytes(N, C, HW) &&
-      (MASK != 2 || aligned16(relu_in))) {
-    static const int use_stream = getenv("SGB_BN_STREAM") ? atoi(getenv("SGB_BN_STREAM")) : 0;   // experiment
-    BnStreamPlan plan;
-    if (use_stream && bn_stream_plan(N, C, HW, MASK, &plan))
-      return bn_stream_backward(MASK, x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, N, C, HW, plan, ws, s);
-  }
   {
     int per_cta = 0;
     const int cs = cluster_plan(vec ? per_channel / 4 : per_channel, vec ? 16 : 4, &per_cta, C);
@@ -830,6 +830,14 @@ int bn_backward(const float* x, const float* dy, const float* relu_in, const flo
                  : launch_cluster<false, MASK>(x, dy, relu_in, scale, mean, invstd, dx, dscale,
                                                dbias, sh, cs, per_cta, s);
     }
+  }
+  // channels too large for a cluster: one pass over HBM with the streaming
+  // kernel where its plan applies, else two passes
+  if (vec && ws && aligned16(ws) && ws_bytes >= bn_stream_workspace_bytes(N, C, HW) &&
+      (MASK != 2 || aligned16(relu_in))) {
+    BnStreamPlan plan;
+    if (bn_stream_plan(N, C, HW, MASK, &plan))
+      return bn_stream_backward(MASK, x, dy, relu_in, scale, mean, invstd, dx, dscale, dbias, N, C, HW, plan, ws, s);
   }
   const int slices = bn_slices_for(per_channel, C, sm_count());
   if (!ws || ws_bytes < static_cast<size_t>(slices) * C * sizeof(float2) || !aligned16(ws))

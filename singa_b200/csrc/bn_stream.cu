@@ -34,8 +34,6 @@
 // flight and returns.
 #include "bn_stream.cuh"
 
-#include <stdlib.h>
-
 #include <atomic>
 
 #include "common.cuh"
@@ -43,7 +41,7 @@
 namespace sgb {
 namespace {
 
-constexpr int kMaxThreads = 256;
+constexpr int kThreads = 128;
 constexpr int kMaxCtasPerSm = 16;
 constexpr int kTables = 8;
 constexpr int kMaxChannels = 4096;
@@ -67,7 +65,7 @@ struct Tail {                         // shared memory behind the slot
   int item;                           // the CTA's next ticket
   int abort;
   float sums[2];                      // the channel's totals
-  float red[2][kMaxThreads / 32];
+  float red[2][kThreads / 32];
 };
 
 struct StreamArgs {
@@ -185,11 +183,11 @@ __device__ __forceinline__ bool poll_counter(const unsigned* ctr, unsigned want,
         return false;
       }
     }
-    __nanosleep(64);
+    if (it > 4) __nanosleep(32);
   }
 }
 
-template <int MASK, int kThreads>
+template <int MASK>
 __global__ void __launch_bounds__(kThreads) bn_bwd_stream_kernel(const StreamArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* slot = smem;
@@ -215,6 +213,10 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_stream_kernel(const StreamArg
   }
   __syncthreads();
   dependency_wait();
+  // The next kernel of the stream may be scheduled as soon as SM slots free up
+  // (it waits for this grid to complete before it touches memory): every CTA
+  // of this grid is running by the time all of them have said so.
+  release_dependents();
   if (tail->abort == 2) return;                       // nothing was issued, nothing of the table was touched
   const unsigned long long deadline = now_ticks() + kDeadlineTicks;
   const int array_floats = a.S * a.Lp;                // floats of one staged tensor in the slot
@@ -400,7 +402,6 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_stream_kernel(const StreamArg
   }
   if (warp == 0) bulk_wait_all();
   if (tid == 0) {
-    release_dependents();                             // nothing of this CTA is left to schedule
     __threadfence();
     const unsigned done = atomicAdd(&tab.finished, 1u);
     if (done == gridDim.x - 1 && ld_acquire(&g_faults) == 0u) {
@@ -419,14 +420,9 @@ int slot_bytes_of(const BnStreamPlan& p, int mask, int* mask_stride) {
   return round_up(p.arrays * p.S * p.Lp * 4 + p.S * *mask_stride, 128);
 }
 
-int env_int(const char* name, int fallback) {      // experiment knobs
-  const char* v = getenv(name);
-  return v ? atoi(v) : fallback;
-}
-
-template <int MASK, int T>
-int launch_stream_t(const StreamArgs& args, cudaStream_t s) {
-  auto kernel = bn_bwd_stream_kernel<MASK, T>;
+template <int MASK>
+int launch_stream(const StreamArgs& args, cudaStream_t s) {
+  auto kernel = bn_bwd_stream_kernel<MASK>;
   static std::atomic<bool> attr_set[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
@@ -439,13 +435,7 @@ int launch_stream_t(const StreamArgs& args, cudaStream_t s) {
   const int resident = sm_count() * args.depth;
   const int grid = args.items < resident ? args.items : resident;
   const size_t smem = static_cast<size_t>(args.slot_bytes) + sizeof(Tail);
-  return launch_ex(kernel, dim3(static_cast<unsigned>(grid)), dim3(T), smem, s, 0, true, args);
-}
-
-template <int MASK>
-int launch_stream(const StreamArgs& args, cudaStream_t s) {
-  static const int threads = env_int("SGB_BNS_THREADS", 128);
-  return threads == 256 ? launch_stream_t<MASK, 256>(args, s) : launch_stream_t<MASK, 128>(args, s);
+  return launch_ex(kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), smem, s, 0, true, args);
 }
 
 }  // namespace
@@ -453,7 +443,6 @@ int launch_stream(const StreamArgs& args, cudaStream_t s) {
 bool bn_stream_plan(int N, int C, int HW, int mask, BnStreamPlan* plan) {
   if (N < 1 || C < 1 || HW < 4 || HW % 4 != 0 || C > kMaxChannels) return false;
   BnStreamPlan p{};
-  static const int target = env_int("SGB_BNS_TARGET", kSlotTarget);
   p.P = 1;
   while (HW % p.P != 0 || (HW / p.P) % 4 != 0 || (HW / p.P) * 4 > kSlotTarget) {
     if (++p.P > 64) return false;
@@ -461,12 +450,12 @@ bool bn_stream_plan(int N, int C, int HW, int mask, BnStreamPlan* plan) {
   p.Lp = HW / p.P;
   const long long pieces = static_cast<long long>(N) * p.P;
   if (pieces > 1 << 20) return false;
-  p.S = target / (p.Lp * 4);
+  p.S = kSlotTarget / (p.Lp * 4);
   if (p.S < 1) p.S = 1;
   if (p.S > pieces) p.S = static_cast<int>(pieces);
   // enough items for every SM to get several (shape-only rule: the partition,
   // and with it the order of the additions, does not depend on the mask mode)
-  const long long want = 6LL * sm_count();
+  const long long want = 24LL * sm_count();
   while (p.S > 1 && C * ((pieces + p.S - 1) / p.S) < want && ((p.S + 1) / 2) * p.Lp * 4 >= 4096) p.S = (p.S + 1) / 2;
   p.parts = static_cast<int>((pieces + p.S - 1) / p.S);
   if (p.parts > 64) return false;                      // also bounds the workspace: 64 pairs per channel
@@ -476,8 +465,6 @@ bool bn_stream_plan(int N, int C, int HW, int mask, BnStreamPlan* plan) {
   // CTAs per SM: each takes its slot, the tail and 1 KB the system reserves, out of 228 KB
   p.depth = (228 * 1024) / (round_up(slot + static_cast<int>(sizeof(Tail)), 128) + 1024);
   if (p.depth > kMaxCtasPerSm) p.depth = kMaxCtasPerSm;
-  static const int threads = env_int("SGB_BNS_THREADS", 128);
-  if (p.depth * threads > 2048) p.depth = 2048 / threads;
   if (p.depth < 2) return false;
   *plan = p;
   return true;

@@ -277,6 +277,59 @@ def test_batchnorm_backward_resnet_stem_size(sw, oracle):
         close(host(a), b, what=name)
 
 
+@pytest.mark.parametrize("shape", [(32, 64, 112, 112), (64, 8, 56, 56), (3, 2, 300, 300), (40, 5, 64, 64)])
+def test_batchnorm_backward_channels_beyond_a_cluster(oracle, shape):
+    """Channels too large for a cluster of 8 CTAs go to the streaming kernel
+    (ticketed items, totals exchanged through counters in global memory): all
+    three mask modes against the oracle, float mask == bit record bit for bit,
+    two calls in a row identical, and no fault recorded."""
+    import ctypes
+    from singa_b200 import _lib
+    L = _lib.lib()
+    N, C = shape[0], shape[1]
+    HW = shape[2] * shape[3]
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    x = torch.randn(shape, device="cuda", generator=g) * 1.5 + 0.3
+    dy = torch.randn(shape, device="cuda", generator=g) * 1e-2
+    rin = torch.randn(shape, device="cuda", generator=g)
+    rin.view(-1)[::7] = 0.0
+    scale = torch.rand(C, device="cuda", generator=g) + 0.5
+    var, mean = torch.var_mean(x, dim=(0, 2, 3), unbiased=False)
+    invstd, mean = torch.rsqrt(var + 1e-5).contiguous(), mean.contiguous()
+    n = x.numel()
+    s = torch.cuda.current_stream().cuda_stream
+    rec = torch.zeros(L.sgb_relu_mask_bytes(n), dtype=torch.uint8, device="cuda")
+    y = torch.empty_like(rin)
+    _lib.call("sgb_relu_forward_mask_f32", rin.data_ptr(), y.data_ptr(), rec.data_ptr(), n, s)
+    ws = torch.empty(max(L.sgb_bn_backward_workspace_bytes(N, C, HW), 256), dtype=torch.uint8, device="cuda")
+    outs = {}
+    for mode in (0, 1, 2):
+        runs = []
+        for _ in range(2):
+            dx = torch.full(shape, float("nan"), device="cuda")
+            ds, db = torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+            tail = [scale.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), ds.data_ptr(), db.data_ptr(),
+                    N, C, HW, ws.data_ptr(), ws.numel(), s]
+            if mode == 0:
+                _lib.call("sgb_bn_backward_f32", x.data_ptr(), dy.data_ptr(), *tail)
+            elif mode == 1:
+                _lib.call("sgb_bn_relu_backward_f32", x.data_ptr(), dy.data_ptr(), rin.data_ptr(), *tail)
+            else:
+                _lib.call("sgb_bn_relu_backward_mask_f32", x.data_ptr(), dy.data_ptr(), rec.data_ptr(), *tail)
+            torch.cuda.synchronize()
+            runs.append((dx, ds, db))
+        assert all(torch.equal(a, b) for a, b in zip(*runs)), ("not repeatable", shape, mode)
+        gm = dy if mode == 0 else torch.where(rin > 0, dy, torch.zeros_like(dy))
+        want = oracle.bn_backward(gm.cpu().numpy(), x.cpu().numpy(), scale.cpu().numpy(), mean.cpu().numpy(),
+                                  invstd.cpu().numpy())
+        for name, a, b in zip(("dx", "dscale", "dbias"), runs[0], want):
+            close(host(a), b, what="%s %s mode %d" % (name, shape, mode))
+        outs[mode] = runs[0]
+    assert all(torch.equal(a, b) for a, b in zip(outs[1], outs[2])), ("float mask != bit record", shape)
+    flags = ctypes.c_uint(1)
+    assert L.sgb_bn_backward_faults(ctypes.byref(flags)) == 0 and flags.value == 0
+
+
 # --------------------------------------------------------------------- pooling
 def test_pooling_goldens(sw, golden):
     for key in ("maxpool_cudnn", "maxpool_api", "avgpool_api"):
