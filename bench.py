@@ -330,13 +330,13 @@ def reference_cuda_leg(torch, dist, path, rank, world, local, steps=10, warmup=2
             "library": "oracle/_ref/libref_singa_cuda.so: the reference's sources, compiled unmodified"}
 
 
-def workload_config(world, dist_option, fused, use_graph, pool_argmax, relu_mask=False):
+def workload_config(world, dist_option, fused, use_graph, pool_argmax, relu_mask=False, threshold=2097152):
     """The `config` object shared by both arms (same keys, same values)."""
     return {"workload": "resnet50_b32_224_backward_sync_update", "batch_per_gpu": BATCH,
             "global_batch": BATCH * world, "dist_option": dist_option,
             "fusion": "bn+relu, join+relu, softmax+ce+grad" if fused else "none (one kernel per reference call)",
             "cuda_graph": use_graph, "pool_argmax_record": bool(pool_argmax), "relu_bit_mask": bool(relu_mask),
-            "bucket_elems": 4194304, "threshold_elems": 2097152,
+            "bucket_elems": 4194304, "threshold_elems": int(threshold),
             "excluded": "cuDNN/cuBLAS contractions (conv, linear): stand-in gradients, rewritten every step"}
 
 
@@ -616,6 +616,10 @@ def main():
                     help="skip the leg that runs the reference's own CUDA / NCCL build of the same step")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="cap on the CTAs NCCL's kernels use (0 = default)")
     ap.add_argument("--no-register", action="store_true", help="do not register the gradient arena with NCCL")
+    ap.add_argument("--threshold-elems", type=int, default=2097152,
+                    help="DistOpt's threshold (python/singa/opt.py: backward_and_update): tensors above it are "
+                         "reduced alone, smaller ones are staged and flushed once the bucket exceeds it; the "
+                         "default is the reference's")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -667,7 +671,7 @@ def main():
             plan = mask_plan(plan)                         # ReLU decisions from the forward partner's bit record
         plan = add_wgrad_refresh(plan)                     # the contractions' weight gradients are rewritten every step
         hp = HotPathGPU(plan, communicator=communicator, world=world, seed=1000 + rank, dist_option=dist_option,
-                        pool_argmax=args.pool_argmax)
+                        pool_argmax=args.pool_argmax, threshold=args.threshold_elems)
         if multi and not args.no_register:
             communicator.register(hp.grad_arena)
         return plan, hp
@@ -882,7 +886,8 @@ def main():
         extra["config1_mlp"] = config1_leg(torch)
 
     if rank == 0:
-        config = workload_config(world, args.dist_option, fused, use_graph, args.pool_argmax, args.relu_mask)
+        config = workload_config(world, args.dist_option, fused, use_graph, args.pool_argmax, args.relu_mask,
+                                 args.threshold_elems)
         config.update({"l2": "inputs larger than L2: %.1f GB touched per step vs 126 MB" % (total_alg / 1e9),
                        "algorithmic_GB_per_step": round(total_alg / 1e9, 3),
                        "hot_path_GBps": round(total_alg / ms / 1e6, 1),

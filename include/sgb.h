@@ -509,8 +509,9 @@ int sgb_sparse_topk_f32(const float *g, float *acc, float *sum_scratch,
                         size_t n, size_t k, int mode, int32_t *idx_out,
                         float *val_out, void *ws, size_t ws_bytes,
                         void *stream);
-/* dst[idx[j]-1] += val[j] for j < count (or < *count_dev when count_dev is
- * not NULL); idx 0 = padding, skipped.  Replaces cusparseSaxpyi with
+/* dst[idx[j]-1] += val[j] for j < count, or for j < min(*count_dev, count)
+ * when count_dev is not NULL (count is then the capacity of idx / val);
+ * idx 0 = padding, skipped.  Replaces cusparseSaxpyi with
  * CUSPARSE_INDEX_BASE_ONE (communicator.cc:715-717, 753-756, 803-805; the
  * routine no longer exists in CUDA 12).  n = length of dst. */
 int sgb_scatter_add_f32(const int32_t *idx, const float *val, size_t count,
@@ -638,6 +639,22 @@ int sgb_comm_sparsification(sgb_comm *c, void *const *tensors,
                             const size_t *sizes, size_t count,
                             float *accumulation, float spars, int topk,
                             void *compute_stream);
+/* Threshold sparsification with a fixed exchange size: every rank sends
+ * exactly `capacity` (index, value) slots, the true counts travel on the
+ * device, and the host never waits for a count - so the call can sit inside a
+ * captured graph (the reference, communicator.cc:657-669, reads the counts
+ * back to size its all-gather).  Equal to sgb_comm_sparsification(topk = 0)
+ * while a rank selects at most `capacity` entries.  Entries beyond that (in
+ * index order) are not sent: with a residual buffer they stay in it and go out
+ * with a later call; without one they are lost.  sgb_comm_sparse_dropped
+ * returns how many entries this rank has held back so far (synchronises).
+ * capacity <= the communicator's buffer size, else SGB_ERR_CAPACITY. */
+int sgb_comm_sparsification_bounded(sgb_comm *c, void *const *tensors,
+                                    const size_t *sizes, size_t count,
+                                    float *accumulation, float threshold,
+                                    size_t capacity, void *compute_stream);
+int sgb_comm_sparse_dropped(sgb_comm *c, unsigned long long *dropped);
+
 
 #ifdef __cplusplus
 }

@@ -158,7 +158,7 @@ def main(argv=None):
             fn = lambda: _lib.call("sgb_avgpool_backward_f32", dy.data_ptr(), dx.data_ptr(), *h._geom(), stream)
             nbytes = 4 * (x.numel() + y.numel())
     elif a.case in ("sgd", "pack"):
-        from .resnet50_path import build_plan, numel
+        from singa_b200.resnet50_path import build_plan, numel
         plan = build_plan()
         sizes = [numel(plan["tensors"][p].shape) for p in plan["params"]]
         ps = [torch.randn(k, device=dev) for k in sizes]

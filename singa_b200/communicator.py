@@ -131,5 +131,23 @@ class Communicator(object):
         _lib.call("sgb_comm_sparsification", self._h, ptrs, sizes, n, acc,
                   float(sparsThreshold), int(bool(topK)), _stream())
 
+    def boundedSparsification(self, ts, accumulation, sparsThreshold, capacity):
+        """Threshold sparsification with a fixed exchange of `capacity` slots per
+        rank and no host wait for the counts (no counterpart in the reference,
+        whose fusedSparsification reads them back, communicator.cc:657-669).
+        Entries a rank selects beyond `capacity` stay in `accumulation`."""
+        assert ts[0].dtype == torch.float32, "sparsification supports fp32 only"
+        ptrs, sizes, n = _table(ts)
+        acc = None if accumulation is None else accumulation.data_ptr()
+        _lib.call("sgb_comm_sparsification_bounded", self._h, ptrs, sizes, n, acc, float(sparsThreshold),
+                  int(capacity), _stream())
+
+    def sparseDropped(self):
+        """Entries this rank's bounded sparsification calls have held back so far."""
+        import ctypes
+        out = ctypes.c_ulonglong(0)
+        _lib.call("sgb_comm_sparse_dropped", self._h, ctypes.byref(out))
+        return int(out.value)
+
     def wait(self):
         _lib.call("sgb_comm_wait", self._h, _stream())

@@ -72,6 +72,7 @@ struct sgb_comm {
   size_t ws_bytes = 0;
   int* nnz_dev = nullptr;      // [0] own count, [1 .. world] all ranks
   int* nnz_host = nullptr;     // pinned, world entries
+  unsigned long long* dropped_dev = nullptr;   // entries the bounded threshold form left for later calls
   int topk_mode = 1;           // 1 = the reference comparator's key, 0 = |value|
   cudaStream_t s = nullptr, c1 = nullptr, c2 = nullptr;
   bool own_streams = true;     // false after sgb_comm_use_streams: the caller's streams are not destroyed
@@ -236,6 +237,8 @@ int sparse_init(sgb_comm* c) {
   CU(cudaMalloc(&c->ws, c->ws_bytes));
   CU(cudaMalloc(&c->nnz_dev, sizeof(int) * (c->world + 1)));
   CU(cudaMallocHost(&c->nnz_host, sizeof(int) * c->world));
+  CU(cudaMalloc(&c->dropped_dev, sizeof(unsigned long long)));
+  CU(cudaMemset(c->dropped_dev, 0, sizeof(unsigned long long)));
   return SGB_OK;
 }
 
@@ -334,6 +337,7 @@ int sgb_comm_destroy(sgb_comm* c) {
   for (void* b : bufs)
     if (b) cudaFree(b);
   if (c->nnz_host) cudaFreeHost(c->nnz_host);
+  if (c->dropped_dev) cudaFree(c->dropped_dev);
   drop_ranges(c);
   cudaEvent_t evs[] = {c->ev_compute, c->ev_c1, c->ev_s, c->ev_c2, c->ev_c2_done, c->ev_host, c->prof_origin};
   for (cudaEvent_t e : evs)
@@ -620,12 +624,16 @@ int sgb_comm_fused_synch_half(sgb_comm* c, void* const* tensors, const size_t* s
   return emit(c, p.post, nullptr);
 }
 
-int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
-                            float* accumulation, float spars, int topk, void* compute_stream) {
+// capacity == 0: the reference's exchange (the payload is as long as the
+// largest count, which the host reads back).  capacity > 0 (threshold mode):
+// every rank sends exactly `capacity` slots, no host round trip.
+static int sparsify(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
+                    float* accumulation, float spars, int topk, size_t capacity, void* compute_stream) {
   if (!c) return SGB_ERR_NULL;
   OK(check_list(tensors, sizes, count));
   const size_t n = total_of(sizes, count);
   if (n > c->max_elems) return SGB_ERR_CAPACITY;
+  if (capacity > c->max_elems) return SGB_ERR_CAPACITY;
   if (n == 0) return SGB_OK;
   OK(sparse_init(c));
   const int W = c->world;
@@ -646,7 +654,15 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   auto select = [&]() -> int {
   Phase ph(c, op_name, sgb::order::kStreamC1);
   if (!in_place) OK(sgb_pack_f32(tensors, sizes, count, c->send, 0, c->c1));
-  if (!topk) {
+  if (!topk && capacity) {
+    OK(sgb::sparse_threshold_count(grad, accumulation, n, spars, c->nnz_dev, c->ws,
+                                   c->ws_bytes, c->c1));
+    // the counts travel on the device only; receivers clamp them to the capacity
+    NC(ncclAllGather(c->nnz_dev, c->nnz_dev + 1, 1, ncclInt, c->nccl, c->c1));
+    OK(sgb::sparse_threshold_write_bounded(grad, accumulation, n, spars, c->pay_send, capacity, c->dropped_dev,
+                                           c->ws, c->c1));
+    nnz_max = capacity;
+  } else if (!topk) {
     OK(sgb::sparse_threshold_count(grad, accumulation, n, spars, c->nnz_dev, c->ws,
                                    c->ws_bytes, c->c1));
     NC(ncclAllGather(c->nnz_dev, c->nnz_dev + 1, 1, ncclInt, c->nccl, c->c1));
@@ -682,6 +698,11 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   CU(cudaMemsetAsync(dense, 0, n * sizeof(float), c->c2));
   for (int r = 0; r < W && nnz_max; ++r) {  // ranks in ascending order, as the reference
     const int* seg = c->pay_recv + static_cast<size_t>(r) * 2 * nnz_max;
+    if (capacity) {                                   // fixed layout; the rank's count is read on the device
+      OK(sgb_scatter_add_f32(seg, reinterpret_cast<const float*>(seg) + capacity, capacity, c->nnz_dev + 1 + r,
+                             dense, n, c->c2));
+      continue;
+    }
     const size_t cnt = static_cast<size_t>(c->nnz_host[r]);
     OK(sgb_scatter_add_f32(seg, reinterpret_cast<const float*>(seg) + cnt, cnt, nullptr, dense,
                            n, c->c2));
@@ -691,6 +712,28 @@ int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* siz
   };
   OK(scatter());
   return emit(c, p.post, nullptr);
+}
+
+int sgb_comm_sparsification(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
+                            float* accumulation, float spars, int topk, void* compute_stream) {
+  return sparsify(c, tensors, sizes, count, accumulation, spars, topk, 0, compute_stream);
+}
+
+int sgb_comm_sparsification_bounded(sgb_comm* c, void* const* tensors, const size_t* sizes, size_t count,
+                                    float* accumulation, float threshold, size_t capacity,
+                                    void* compute_stream) {
+  if (capacity == 0) return SGB_ERR_SIZE;
+  return sparsify(c, tensors, sizes, count, accumulation, threshold, 0, capacity, compute_stream);
+}
+
+int sgb_comm_sparse_dropped(sgb_comm* c, unsigned long long* dropped) {
+  if (!c || !dropped) return SGB_ERR_NULL;
+  *dropped = 0;
+  if (!c->dropped_dev) return SGB_OK;               // no sparse call yet
+  // on the stream that runs the selection, so that every call issued so far is counted
+  CU(cudaMemcpyAsync(dropped, c->dropped_dev, sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->c1));
+  CU(cudaStreamSynchronize(c->c1));
+  return SGB_OK;
 }
 
 }  // extern "C"

@@ -291,6 +291,56 @@ thr_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t 
   }
 }
 
+// Capacity-bounded form: the payload layout is fixed, [idx(cap) | val(cap)],
+// and only the first `cap` selected entries (index order) are written.  The
+// others stay in the residual (acc keeps s there), so they are sent by a later
+// call; their number is added to *dropped.  With this the length of the
+// exchange is known on the host before the count is, and the caller needs no
+// host round trip between selection and all-gather.
+__global__ void __launch_bounds__(kBlock)
+thr_write_bounded_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t n, float thr,
+                         const unsigned* __restrict__ tile_offsets, int* __restrict__ idx_out, unsigned cap,
+                         unsigned long long* __restrict__ dropped, bool vec) {
+  __shared__ unsigned sm[33];
+  float* val_out = reinterpret_cast<float*>(idx_out) + cap;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kTile;
+  float sv[kVecPerThread][4];
+  unsigned c[kVecPerThread], excl[kVecPerThread];
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    c[r] = 0;
+    load_sum4(sum, nullptr, i, n, vec, sv[r]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[r] += (fabsf(sv[r][j]) >= thr && sv[r][j] != 0.0f) ? 1u : 0u;
+  }
+  tile_exclusive(c, excl, sm);
+  const unsigned tile_off = tile_offsets[blockIdx.x];
+  unsigned lost = 0;
+#pragma unroll
+  for (int r = 0; r < kVecPerThread; ++r) {
+    if (!c[r]) continue;                                  // untouched vectors already hold their residual
+    const size_t i = base + (static_cast<size_t>(r) * kBlock + threadIdx.x) * 4;
+    unsigned pos = tile_off + excl[r];
+    bool sent = false;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (fabsf(sv[r][j]) >= thr && sv[r][j] != 0.0f) {
+        if (pos < cap) {
+          idx_out[pos] = static_cast<int>(i + j + 1);
+          val_out[pos] = sv[r][j];
+          sv[r][j] = 0.0f;                                // sent: leaves the residual
+          sent = true;
+        } else {
+          ++lost;                                         // over capacity: stays in the residual
+        }
+        ++pos;
+      }
+    if (acc && sent) store4(acc, i, n, vec, sv[r]);
+  }
+  if (lost) atomicAdd(dropped, static_cast<unsigned long long>(lost));
+}
+
 // ---------------------------------------------------------------- top-K mode
 // mode 0 "magnitude": key = bits of |s| (monotonic in |s| for non-NaN);
 // mode 1 "compat":    key = |(int)s|, the value the reference's comparator
@@ -554,7 +604,12 @@ topk_write_kernel(const float* __restrict__ sum, float* __restrict__ acc, size_t
 __global__ void __launch_bounds__(kBlock)
 scatter_add_kernel(const int* __restrict__ idx, const float* __restrict__ val, size_t count,
                    const int* __restrict__ count_dev, float* __restrict__ dst, size_t n) {
-  const size_t m = count_dev ? static_cast<size_t>(*count_dev) : count;
+  size_t m = count;
+  if (count_dev) {                                  // the host count is then the capacity of idx / val
+    const int dv = *count_dev;
+    const size_t d = dv > 0 ? static_cast<size_t>(dv) : 0;
+    m = d < count ? d : count;
+  }
   for (size_t j = blockIdx.x * static_cast<size_t>(kBlock) + threadIdx.x; j < m;
        j += static_cast<size_t>(gridDim.x) * kBlock) {
     const int i = idx[j];
@@ -598,6 +653,18 @@ int sparse_threshold_write_packed(const float* g, float* acc, size_t n, float th
   Workspace w = carve(ws, n);
   const unsigned tiles = static_cast<unsigned>(tiles_of(n));
   thr_write_kernel<<<tiles, kBlock, 0, s>>>(acc ? acc : g, acc, n, thr, w.tile_counts, payload, nullptr, w.state, aligned16(g) && (!acc || aligned16(acc)));
+  return launch_status();
+}
+
+int sparse_threshold_write_bounded(const float* g, float* acc, size_t n, float thr, int* payload, size_t cap,
+                                   unsigned long long* dropped_dev, void* ws, cudaStream_t s) {
+  if (n == 0) return SGB_OK;
+  if (cap == 0 || cap > 0x7fffffffu || !dropped_dev) return SGB_ERR_SIZE;
+  Workspace w = carve(ws, n);
+  const unsigned tiles = static_cast<unsigned>(tiles_of(n));
+  thr_write_bounded_kernel<<<tiles, kBlock, 0, s>>>(acc ? acc : g, acc, n, thr, w.tile_counts, payload,
+                                                    static_cast<unsigned>(cap), dropped_dev,
+                                                    aligned16(g) && (!acc || aligned16(acc)));
   return launch_status();
 }
 

@@ -15,4 +15,10 @@ int sparse_threshold_count(const float* g, float* acc, size_t n, float thr, int*
 int sparse_threshold_write_packed(const float* g, float* acc, size_t n, float thr, int* payload,
                                   void* ws, cudaStream_t s);
 
+// Phase 2, capacity-bounded: payload [idx(cap) | val(cap)]; selected entries
+// beyond the first `cap` (index order) stay in the residual and are counted in
+// *dropped_dev (a device counter the caller owns).
+int sparse_threshold_write_bounded(const float* g, float* acc, size_t n, float thr, int* payload, size_t cap,
+                                   unsigned long long* dropped_dev, void* ws, cudaStream_t s);
+
 }  // namespace sgb

@@ -122,6 +122,70 @@ def main():
             assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), accs[rank].view(np.uint32)), \
                 ("residual", topk, mode, step)
 
+    # (e2) the capacity-bounded threshold exchange (no host wait for the counts)
+    thr = 2e-3
+    # ample capacity: bit for bit the reference's exchange, over three steps with residuals
+    accs = [np.zeros(n, np.float32) for _ in range(world)]
+    d_acc = torch.zeros(n, device="cuda")
+    for step in range(3):
+        gs = [(np.random.default_rng(500 + 20 * r + step).standard_normal(n) * 1e-3).astype(np.float32)
+              for r in range(world)]
+        g = dev(gs[rank])
+        comm.boundedSparsification([g], d_acc, thr, n)
+        comm.wait()
+        torch.cuda.synchronize()
+        dense, accs, _ = ocomm.sparse_threshold_step(gs, accs, thr)
+        assert np.array_equal(g.cpu().numpy().view(np.uint32), dense.view(np.uint32)), ("bounded dense", step)
+        assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), accs[rank].view(np.uint32)), ("bounded acc", step)
+    assert comm.sparseDropped() == 0
+    # tight capacity: every rank sends its first `cap` selected entries (index order), the rest stay behind
+    cap = 1000
+    gs = [(np.random.default_rng(900 + r).standard_normal(n) * 1e-3).astype(np.float32) for r in range(world)]
+    d_acc = torch.zeros(n, device="cuda")
+    g = dev(gs[rank])
+    comm.boundedSparsification([g], d_acc, thr, cap)
+    comm.wait()
+    torch.cuda.synchronize()
+    want_dense = np.zeros(n, np.float32)
+    for r in range(world):                                  # ranks in ascending order, as the scatter runs
+        sel = np.flatnonzero(np.abs(gs[r]) >= np.float32(thr))
+        sent = sel[:cap]
+        want_dense[sent] += gs[r][sent]
+        if r == rank:
+            want_acc = gs[r].copy()
+            want_acc[sent] = 0.0
+            held_back = len(sel) - len(sent)
+    assert held_back > 0
+    assert np.array_equal(g.cpu().numpy().view(np.uint32), want_dense.view(np.uint32)), "bounded dense, tight capacity"
+    assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), want_acc.view(np.uint32)), "bounded acc, tight capacity"
+    assert comm.sparseDropped() == held_back, (comm.sparseDropped(), held_back)
+    # inside a captured graph: two replays with fresh gradients equal two eager calls
+    side = torch.cuda.Stream()
+    g_buf, acc_buf = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    fresh = [dev((np.random.default_rng(1300 + 10 * k + rank).standard_normal(n) * 1e-3).astype(np.float32))
+             for k in range(2)]
+    with torch.cuda.stream(side):
+        comm.boundedSparsification([g_buf], acc_buf, thr, n)   # warm-up outside capture
+        comm.wait()
+        side.synchronize()
+        acc_buf.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+            comm.boundedSparsification([g_buf], acc_buf, thr, n)
+            comm.wait()
+    torch.cuda.synchronize()
+    e_acc = torch.zeros(n, device="cuda")
+    for k in range(2):
+        g_buf.copy_(fresh[k])
+        graph.replay()
+        torch.cuda.synchronize()
+        e_g = fresh[k].clone()
+        comm.boundedSparsification([e_g], e_acc, thr, n)
+        comm.wait()
+        torch.cuda.synchronize()
+        assert torch.equal(g_buf, e_g) and torch.equal(acc_buf, e_acc), ("graph replay", k)
+    del graph
+
     # (g) DistOpt.backward_and_partial_update through the real communicator:
     # local SGD-momentum updates, then one partition of the parameters averaged
     from oracle import cpu as ocpu
