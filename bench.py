@@ -27,7 +27,7 @@ METRIC = "resnet50_backward_sync_update_images_per_sec"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the batch-norm
 # backward kernels, averaged per call over one step, from the ncu capture
 # summarised in profiles/bench_resnet50_launch_list.md (fused / call-pattern plan).
-NCU_BN_TRAFFIC_PER_CALL = {True: 77.8e6, False: 65.5e6}
+NCU_BN_TRAFFIC_PER_CALL = {True: 71.8e6, False: 61.6e6}
 BATCH = 32
 CPU_SAMPLE_BATCH = 8
 
@@ -388,6 +388,8 @@ def sparse_leg(torch, dist, comm, rank, world, workload, n, K, W, sampler=None):
     ranks, elements/s of the whole job, roofline of the step)."""
     multi = world > 1
     topk = workload == "sparse_topk"
+    bounded = workload == "sparse_threshold_bounded"   # fixed exchange of 0.2 n slots, no host wait for the counts
+    capacity = n // 5
     spars = 0.01 if topk else 2e-3
     fresh = min(K, 20)                       # distinct gradients held on the device (0.4 GB each at 1e8)
     gen = torch.Generator(device="cuda")
@@ -400,7 +402,10 @@ def sparse_leg(torch, dist, comm, rank, world, workload, n, K, W, sampler=None):
 
     def step(k):
         work.copy_(grads[k % fresh])         # the exchange overwrites its input with the dense result
-        comm.sparsification(work, acc, spars, topk)
+        if bounded:
+            comm.boundedSparsification([work], acc, spars, capacity)
+        else:
+            comm.sparsification(work, acc, spars, topk)
         comm.wait()
 
     def barrier():
@@ -444,6 +449,7 @@ def sparse_leg(torch, dist, comm, rank, world, workload, n, K, W, sampler=None):
             "topk_mode": "compat" if topk else None, "steps": K, "warmup": W, "fresh_gradients": fresh,
             "ms_per_step": ex_ms, "elements_per_sec": n * world / (ex_ms / 1e3),
             "loop_ms_incl_gradient_copy": ms, "dense_nonzeros_after_last_step": nnz, "clocks": clocks,
+            "capacity": capacity if bounded else None, "held_back": comm.sparseDropped() if bounded else None,
             "roofline": {"bound": "hbm", "achieved": round(alg / ex_ms / 1e6, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(alg / ex_ms / 1e6 / peak, 4), "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_bytes_per_step": alg}}
@@ -598,7 +604,7 @@ def main():
     ap.add_argument("--dist-option", default="plain", choices=["plain", "half"])
     ap.add_argument("--call-pattern", action="store_true",
                     help="one kernel per reference call (no cross-op fusion)")
-    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "sparse_topk", "sparse_threshold"],
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "sparse_topk", "sparse_threshold", "sparse_threshold_bounded"],
                     help="resnet50 (headline) or the sparse gradient exchange microbench: a flat 1e8-element "
                          "fp32 gradient N(0, 1e-3^2), residual accumulation on, top-K ratio 0.01 / threshold 2e-3")
     ap.add_argument("--elements", type=int, default=100000000)
@@ -795,7 +801,9 @@ def main():
     bn_launches = sum(1 for o in plan["ops"] if o.kind in bn_keys)
     achieved = bn_bytes / bn_ms / 1e6
     captured_plan = fused and not args.relu_mask
-    roofline = {"bound": "hbm", "kernel": "batch-norm backward (reduce + apply)", "achieved": round(achieved, 1),
+    roofline = {"bound": "hbm",
+                "kernel": "batch-norm backward (cluster, streaming and channel-group kernels: all 53 calls)",
+                "achieved": round(achieved, 1),
                 "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "traffic": NCU_BN_TRAFFIC_PER_CALL[fused] if (captured_plan or not fused) else None,
                 "traffic_source": "ncu capture summarised in profiles/bench_resnet50_launch_list.md (a constant, "
@@ -865,10 +873,10 @@ def main():
         comm.close()
         comm = new_comm(args.elements)
         legs = {}
-        for wl in ("sparse_topk", "sparse_threshold"):
+        for wl in ("sparse_topk", "sparse_threshold", "sparse_threshold_bounded"):
             r = sparse_leg(torch, dist, comm, rank, world, wl, args.elements, 20, 3)
             legs[wl] = {k: r[k] for k in ("spars", "topk_mode", "steps", "ms_per_step", "elements_per_sec",
-                                          "dense_nonzeros_after_last_step", "roofline")}
+                                          "dense_nonzeros_after_last_step", "roofline", "capacity", "held_back")}
             if multi and wl == "sparse_topk":      # all-gather: every GPU receives the (W-1) payloads of its peers
                 pay = 8.0 * _lib.lib().sgb_topk_count(r["spars"], args.elements)
                 legs[wl]["nvlink_lower_bound_ms"] = round((world - 1) * pay / 900e9 * 1e3, 5)
