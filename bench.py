@@ -28,6 +28,24 @@ METRIC = "resnet50_backward_sync_update_images_per_sec"
 # backward kernels, averaged per call over one step, from the ncu capture
 # summarised in profiles/bench_resnet50_launch_list.md (fused / call-pattern plan).
 NCU_BN_TRAFFIC_PER_CALL = {True: 71.8e6, False: 61.6e6}
+
+
+def _traffic_from_summary():
+    """Reads the two "... = X MB per call." lines of the committed launch-list
+    summary (fused plan first, call-pattern plan second), so that the constant
+    follows the capture; the literals above are the fallback."""
+    import re
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles", "bench_resnet50_launch_list.md")
+    try:
+        found = re.findall(r"Batch-norm backward: \d+ calls, [\d.]+ MB of DRAM traffic per step = ([\d.]+) MB per call",
+                           open(path).read())
+        if len(found) == 2:
+            return {True: float(found[0]) * 1e6, False: float(found[1]) * 1e6}
+    except OSError:
+        pass
+    return NCU_BN_TRAFFIC_PER_CALL
+
+
 BATCH = 32
 CPU_SAMPLE_BATCH = 8
 
@@ -805,7 +823,7 @@ def main():
                 "kernel": "batch-norm backward (cluster, streaming and channel-group kernels: all 53 calls)",
                 "achieved": round(achieved, 1),
                 "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                "traffic": NCU_BN_TRAFFIC_PER_CALL[fused] if (captured_plan or not fused) else None,
+                "traffic": _traffic_from_summary()[fused] if (captured_plan or not fused) else None,
                 "traffic_source": "ncu capture summarised in profiles/bench_resnet50_launch_list.md (a constant, "
                                   "not measured in this run)",
                 "peak_kind": peak_kind, "launches_per_step": bn_launches,

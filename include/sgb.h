@@ -361,6 +361,13 @@ int sgb_bn_forward_training_f32(const float *x, const float *scale,
  * most eight such launches may be in flight per device).  A faulted launch
  * stops early and its outputs are undefined.  Synchronises the device. */
 int sgb_bn_backward_faults(unsigned *flags);
+/* How the streaming form would cut an (N, C, HW) problem (host arithmetic
+ * only, no device work): returns 1 and fills plan6 = {pieces per plane, floats
+ * per piece, pieces per item, items per channel, CTAs per SM, staged tensors
+ * per item}, or 0 when the streaming form does not apply (it is used for
+ * channels that do not fit a thread-block cluster).  mask: 0 none, 1 ReLU
+ * input, 2 ReLU bit record. */
+int sgb_bn_backward_stream_plan(int N, int C, int HW, int mask, int *plan6);
 /* Batch-norm backward for callers that can neither allocate device memory nor
  * hand in a workspace.  (No counterpart in the reference: this entry point
  * exists only in this library.)  Typical callers: an operator running inside

@@ -1202,6 +1202,19 @@ size_t sgb_bn_backward_workspace_bytes(int N, int C, int HW) {
 
 int sgb_bn_backward_faults(unsigned* flags) { return bn_stream_faults(flags); }
 
+int sgb_bn_backward_stream_plan(int N, int C, int HW, int mask, int* plan6) {
+  if (!plan6) return SGB_ERR_NULL;
+  BnStreamPlan p;
+  if (!bn_stream_plan(N, C, HW, mask, &p)) return 0;
+  plan6[0] = p.P;
+  plan6[1] = p.Lp;
+  plan6[2] = p.S;
+  plan6[3] = p.parts;
+  plan6[4] = p.depth;
+  plan6[5] = p.arrays;
+  return 1;
+}
+
 int sgb_bn_backward_f32(const float* x, const float* dy, const float* scale, const float* mean,
                         const float* invstd, float* dx, float* dscale, float* dbias, int N,
                         int C, int HW, void* ws, size_t ws_bytes, void* stream) {
