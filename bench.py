@@ -838,6 +838,13 @@ def main():
              "tolerance": "1e-5 fp32, 1e-3 x world fp16, relative to the largest expected sum"}
     tl = timeline(torch, path, comm)
     launches_per_step = kernel_launches(path)
+    # sticky fault word of the streaming batch-norm kernel (bounded waits between its CTAs): 0 on every rank
+    import ctypes
+    flags = ctypes.c_uint(0)
+    _lib.call("sgb_bn_backward_faults", ctypes.byref(flags))
+    bn_faults = int(max_over_ranks(float(flags.value)))
+    if bn_faults:
+        raise SystemExit("bench.py: the streaming batch-norm kernel recorded fault flags %d" % bn_faults)
 
     nvlink = None
     if multi:
@@ -924,7 +931,8 @@ def main():
             "ms_per_step": ms, "step_ms": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": config,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * K,
-            "roofline": roofline, "roofline_by_family": fam, "sync_check": check, "nvlink": nvlink,
+            "roofline": roofline, "roofline_by_family": fam, "sync_check": check, "bn_faults": bn_faults,
+            "nvlink": nvlink,
             "timeline": tl, "cpu_baseline": cpu_baseline,
         }
         line.update(extra)

@@ -114,6 +114,26 @@ def sparse_threshold_step(rank_grads, rank_accs, thr):
     return dense, (None if rank_accs is None else new_accs), payloads
 
 
+def sparse_threshold_bounded_step(rank_grads, rank_accs, thr, capacity):
+    """The capacity-bounded threshold exchange (an addition of this library, no
+    counterpart in the reference): the selection rule of valSparsAllReduce
+    (communicator.cc:619-680), but every rank sends only its first `capacity`
+    selected entries in index order; the others stay in the residual (or are
+    lost when there is none).  Returns (dense_sum, new_accs, held_back per rank)."""
+    payloads, new_accs, held = [], [], []
+    for r, g in enumerate(rank_grads):
+        acc = None if rank_accs is None else rank_accs[r]
+        idx, val, acc2 = cpu.sparse_threshold(g, acc, thr)
+        keep = min(len(idx), int(capacity))
+        if acc2 is not None and keep < len(idx):
+            acc2[idx[keep:] - 1] = val[keep:]          # not sent: back into the residual, bit for bit
+        payloads.append((idx[:keep], val[:keep]))
+        new_accs.append(acc2)
+        held.append(len(idx) - keep)
+    dense = _reduce_payloads(rank_grads[0].size, payloads)
+    return dense, (None if rank_accs is None else new_accs), held
+
+
 def sparse_topk_step(rank_grads, rank_accs, ratio, mode="magnitude"):
     """One topKSparsAllReduce (communicator.cc:721-807) for all ranks:
     s = g + acc; the K = ceil(ratio*n) entries with the largest key are sent;

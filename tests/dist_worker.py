@@ -138,27 +138,25 @@ def main():
         assert np.array_equal(g.cpu().numpy().view(np.uint32), dense.view(np.uint32)), ("bounded dense", step)
         assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), accs[rank].view(np.uint32)), ("bounded acc", step)
     assert comm.sparseDropped() == 0
-    # tight capacity: every rank sends its first `cap` selected entries (index order), the rest stay behind
+    # tight capacity over two steps: every rank sends its first `cap` selections (index order), the others
+    # stay in the residual and compete again in the next step
     cap = 1000
-    gs = [(np.random.default_rng(900 + r).standard_normal(n) * 1e-3).astype(np.float32) for r in range(world)]
+    accs = [np.zeros(n, np.float32) for _ in range(world)]
     d_acc = torch.zeros(n, device="cuda")
-    g = dev(gs[rank])
-    comm.boundedSparsification([g], d_acc, thr, cap)
-    comm.wait()
-    torch.cuda.synchronize()
-    want_dense = np.zeros(n, np.float32)
-    for r in range(world):                                  # ranks in ascending order, as the scatter runs
-        sel = np.flatnonzero(np.abs(gs[r]) >= np.float32(thr))
-        sent = sel[:cap]
-        want_dense[sent] += gs[r][sent]
-        if r == rank:
-            want_acc = gs[r].copy()
-            want_acc[sent] = 0.0
-            held_back = len(sel) - len(sent)
-    assert held_back > 0
-    assert np.array_equal(g.cpu().numpy().view(np.uint32), want_dense.view(np.uint32)), "bounded dense, tight capacity"
-    assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), want_acc.view(np.uint32)), "bounded acc, tight capacity"
-    assert comm.sparseDropped() == held_back, (comm.sparseDropped(), held_back)
+    total_held = 0
+    for step in range(2):
+        gs = [(np.random.default_rng(900 + 20 * r + step).standard_normal(n) * 1e-3).astype(np.float32)
+              for r in range(world)]
+        g = dev(gs[rank])
+        comm.boundedSparsification([g], d_acc, thr, cap)
+        comm.wait()
+        torch.cuda.synchronize()
+        dense, accs, held = ocomm.sparse_threshold_bounded_step(gs, accs, thr, cap)
+        assert held[rank] > 0
+        total_held += held[rank]
+        assert np.array_equal(g.cpu().numpy().view(np.uint32), dense.view(np.uint32)), ("tight dense", step)
+        assert np.array_equal(d_acc.cpu().numpy().view(np.uint32), accs[rank].view(np.uint32)), ("tight acc", step)
+    assert comm.sparseDropped() == total_held, (comm.sparseDropped(), total_held)
     # inside a captured graph: two replays with fresh gradients equal two eager calls
     side = torch.cuda.Stream()
     g_buf, acc_buf = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
