@@ -36,6 +36,7 @@
 
 #include <atomic>
 
+#include "bulk_copy.cuh"
 #include "common.cuh"
 
 namespace sgb {
@@ -89,47 +90,6 @@ struct StreamArgs {
   unsigned tag;
 };
 
-// ------------------------------------------------------------------ PTX
-__device__ __forceinline__ unsigned smem_addr(const void* p) {
-  return static_cast<unsigned>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* b, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(b)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect(unsigned long long* b, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* b, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_addr(b)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// global -> shared, completion (bytes) counted on an mbarrier of this CTA
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_addr(dst)),
-               "l"(src), "r"(bytes), "r"(smem_addr(bar))
-               : "memory");
-}
-// shared -> global, tracked by the issuing thread's bulk group
-__device__ __forceinline__ void bulk_store(void* dst, const void* src, unsigned bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_addr(src)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// generic-proxy writes to shared memory become visible to the bulk-copy engine
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // Deadlines are counted in SM clock cycles (clock64 is a cheap register read;
 // the global nanosecond timer costs microseconds per read).
 __device__ __forceinline__ unsigned long long now_ticks() { return static_cast<unsigned long long>(clock64()); }
@@ -198,7 +158,7 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_stream_kernel(const StreamArg
   if (tid == 0) {
     mbar_init(&tail->full, 1);
     tail->abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_mbarrier_init();
     dependency_wait();                                // first access to global memory follows
     // both requests travel together; a ticket drawn from a table that turns
     // out to be another launch's is reported as a fault (both launches are void)
