@@ -40,7 +40,6 @@
 #include <atomic>
 
 #include "bn_stream.cuh"
-#include "bulk_copy.cuh"
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -296,16 +295,6 @@ constexpr int kCopyGroups = 4;
 // CTA size of the single-pass kernel: 512 threads for large shares (fewer
 // serial iterations per thread), 256 for small ones.
 
-// Sticky fault word of the cluster kernel's bulk-copy form: bit 0 = a wait for
-// landed copies ran out of iterations (the outputs of that launch are void).
-__device__ unsigned g_cluster_faults;
-
-__device__ __forceinline__ void wait_landed(unsigned long long* bar) {
-  for (unsigned it = 0; it < (1u << 24); ++it)
-    if (mbar_try_wait(bar, 0)) return;
-  atomicOr(&g_cluster_faults, 1u);
-}
-
 // grid.x = C * CS with cluster dimension CS: the CS CTAs of a cluster share
 // channel blockIdx.x / CS.  A "unit" is one float4 (VEC) or one float.
 // Dynamic shared memory: 2 * per_cta units (x share, then dy share).
@@ -320,10 +309,8 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       const float* __restrict__ mean, const float* __restrict__ invstd,
                       float* __restrict__ dx, float* __restrict__ dscale,
                       float* __restrict__ dbias, BnShape sh, int per_cta,
-                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr,
-                      int bulk = 0) {
+                      const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
   extern __shared__ __align__(16) float stage[];
-  __shared__ unsigned long long landed[kCopyGroups];   // bulk form: one mbarrier per copy group
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
   cg::cluster_group cluster = cg::this_cluster();
@@ -331,14 +318,6 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   const int rank = static_cast<int>(cluster.block_rank());
   const int c = blockIdx.x / cs;
   cluster.barrier_arrive();                           // matched by barrier_wait before the exchange
-  if (VEC && !ADD && bulk) {
-    if (threadIdx.x == 0) {
-#pragma unroll
-      for (int g = 0; g < kCopyGroups; ++g) mbar_init(&landed[g], 1);
-      fence_mbarrier_init();
-    }
-    __syncthreads();
-  }
   constexpr int kW = VEC ? 4 : 1;                     // floats per unit
   const int hwu = sh.HW / kW;                         // units per plane
   const int total = sh.N * hwu;
@@ -384,32 +363,6 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
           for (int k = 0; k < 4; ++k) g.f[k] = vr[j].f[k] > 0 ? (va[j].f[k] + vb[j].f[k]) : 0.0f;
           *reinterpret_cast<uint4*>(sg + ls[j]) = g.u;
           st128(joined + offs[j], g.u);
-        }
-      }
-    }
-  } else if (VEC && bulk) {
-    // bulk form: warp 0 issues one bulk copy per (copy group, plane) piece of the
-    // share and tensor; a copy group is a contiguous range of group_units * T units
-    if (threadIdx.x < 32) {
-      const int lane = threadIdx.x;
-      const int span = group_units * T;
-      if (lane < kCopyGroups) {
-        const int g0 = min(u0 + lane * span, u1), g1 = min(u0 + (lane + 1) * span, u1);
-        mbar_arrive_expect(&landed[lane], static_cast<unsigned>(g1 - g0) * 32u);   // x and dy, 16 bytes per unit
-      }
-      __syncwarp();
-      if (u1 > u0) {
-        const int n_first = u0 / hwu, n_last = (u1 - 1) / hwu;
-        for (int n = n_first + lane; n <= n_last; n += 32) {
-          const int a = max(u0, n * hwu), b = min(u1, (n + 1) * hwu);
-          for (int g = (a - u0) / span; g <= (b - 1 - u0) / span; ++g) {
-            const int ua = max(a, u0 + g * span), ub = min(b, u0 + (g + 1) * span);
-            const size_t off = n * plane_stride + chan_off + static_cast<size_t>(ua - n * hwu) * 4;
-            const int l = (ua - u0) * 4;
-            const unsigned bytes = static_cast<unsigned>(ub - ua) * 16u;
-            bulk_load(sx + l, x + off, bytes, &landed[g]);
-            bulk_load(sg + l, dy + off, bytes, &landed[g]);
-          }
         }
       }
     }
@@ -525,22 +478,14 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       }
     };
     static_assert(kCopyGroups == 4, "the waits below are written out for four groups");
-    if (!ADD && bulk) {
-#pragma unroll
-      for (int g = 0; g < kCopyGroups; ++g) {
-        wait_landed(&landed[g]);
-        sum_copy_group();
-      }
-    } else {
-      if (!ADD) cp_async_wait_pending<3>();
-      sum_copy_group();
-      if (!ADD) cp_async_wait_pending<2>();
-      sum_copy_group();
-      if (!ADD) cp_async_wait_pending<1>();
-      sum_copy_group();
-      if (!ADD) cp_async_wait_pending<0>();
-      sum_copy_group();
-    }
+    if (!ADD) cp_async_wait_pending<3>();
+    sum_copy_group();
+    if (!ADD) cp_async_wait_pending<2>();
+    sum_copy_group();
+    if (!ADD) cp_async_wait_pending<1>();
+    sum_copy_group();
+    if (!ADD) cp_async_wait_pending<0>();
+    sum_copy_group();
   } else {
     for (int u = first; u < u1; u += T) {
       const int l = u - u0;
@@ -797,9 +742,8 @@ int launch_cluster_t(const float* x, const float* dy, const float* relu_in, cons
   static std::atomic<bool> attr_set[64];
   const int ready = opt_in_once(kernel, attr_set, true);
   if (ready != SGB_OK) return ready;
-  static const int bulk = getenv("SGB_BN_BULK") ? atoi(getenv("SGB_BN_BULK")) : 0;   // experiment
   return launch_ex(kernel, dim3(static_cast<unsigned>(sh.C) * cs), dim3(T), smem, s, cs, true, x, dy, relu_in,
-                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined, (VEC && !ADD) ? bulk : 0);
+                   scale, mean, invstd, dx, dscale, dbias, sh, per_cta, dy_b, joined);
 }
 
 template <bool VEC, int MASK>
@@ -1256,16 +1200,7 @@ size_t sgb_bn_backward_workspace_bytes(int N, int C, int HW) {
   return static_cast<size_t>(kMaxSlices) * C * sizeof(float2);
 }
 
-int sgb_bn_backward_faults(unsigned* flags) {
-  if (!flags) return SGB_ERR_NULL;
-  unsigned streaming = 0, cluster = 0;
-  const int st = bn_stream_faults(&streaming);
-  if (st != SGB_OK) return st;
-  cudaError_t e = cudaMemcpyFromSymbol(&cluster, g_cluster_faults, sizeof(unsigned));
-  if (e != cudaSuccess) return note_cuda_error(e);
-  *flags = streaming | (cluster << 8);
-  return SGB_OK;
-}
+int sgb_bn_backward_faults(unsigned* flags) { return bn_stream_faults(flags); }
 
 int sgb_bn_backward_stream_plan(int N, int C, int HW, int mask, int* plan6) {
   if (!plan6) return SGB_ERR_NULL;
