@@ -134,7 +134,8 @@ def build_variant(variant, force=False):
 
 
 GTEST_SOURCES = ["test/gtest/gtest-all.cc", "test/gtest/gtest_main.cc", "test/singa/test_tensor_math.cc",
-                 "test/singa/test_tensor.cc"]
+                 "test/singa/test_tensor.cc", "test/singa/test_cross_entropy.cc",
+                 "src/model/loss/softmax_cross_entropy.cc"]
 
 
 def gtest_binary(variant):
@@ -142,9 +143,10 @@ def gtest_binary(variant):
 
 
 def build_gtests(variant, force=False):
-    """The reference's OWN unit tests - test/singa/test_tensor_math.cc and
-    test_tensor.cc with its vendored gtest - compiled unmodified and linked
-    against one of the two core builds.  Returns the binary's path (None when
+    """The reference's OWN unit tests - test/singa/test_tensor_math.cc,
+    test_tensor.cc and test_cross_entropy.cc (with the loss layer it drives,
+    src/model/loss/softmax_cross_entropy.cc) and its vendored gtest - compiled
+    unmodified and linked against one of the two core builds.  Returns the binary's path (None when
     neither the reference tree nor a prebuilt binary is present)."""
     lib = build_variant(variant)
     exe = gtest_binary(variant)

@@ -1,11 +1,14 @@
 """The reference's OWN unit tests on this repository's back end.  apache/singa's
-test/singa/test_tensor_math.cc and test_tensor.cc, with its vendored gtest,
-are compiled unmodified (oracle/ref_cuda_build.py) and linked once against the
+test/singa/test_tensor_math.cc, test_tensor.cc and test_cross_entropy.cc (with
+the loss layer it drives, src/model/loss/softmax_cross_entropy.cc) and its
+vendored gtest are compiled unmodified (oracle/ref_cuda_build.py) and linked
+once against the
 reference's CUDA core and once against the same core with the replacement
 tensor_math_cuda.h plugged in.  Every `*Cuda` case (tensor math on a CudaGPU
 device: L2, Mult, row / column broadcasts, SumRows / SumColumns, strided Exp,
 concatenation, row / column copies, RowMax, Broadcast, SoftPlus / SoftSign,
-AsType) must pass on both; the Cpp cases ride along."""
+AsType; the loss layer's forward / backward with integer and array targets)
+must pass on both; the Cpp cases ride along."""
 import os
 import subprocess
 
@@ -30,4 +33,4 @@ def test_reference_unit_tests_pass(variant):
     assert r.returncode == 0, tail
     assert "[  PASSED  ]" in r.stdout and "FAILED" not in r.stdout, tail
     ran = [ln for ln in r.stdout.splitlines() if ln.startswith("[       OK ]")]
-    assert sum("Cuda" in ln for ln in ran) >= 23, tail
+    assert sum("Cuda" in ln for ln in ran) >= 27, tail
