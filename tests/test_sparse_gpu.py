@@ -48,6 +48,25 @@ def test_threshold_nothing_and_everything(sw):
     assert np.array_equal(idx.cpu().numpy(), np.arange(1, 10001, dtype=np.int32))
 
 
+def test_threshold_selector_repeats_on_a_multi_wave_size(sw):
+    """Many calls in a row on a size of several waves of tiles give the same
+    payload every time, unaligned buffers included."""
+    n = 10000019
+    rng = np.random.default_rng(1)
+    g_host = (rng.standard_normal(n + 1) * 1e-3).astype(np.float32)
+    for shift in (0, 1):                       # shift 1: 4-byte aligned only (scalar loads)
+        g = dev(g_host)[shift:shift + n]
+        first = None
+        for _ in range(5):
+            idx, val = sw.sparse_threshold(g, None, 2e-3)
+            got = (idx.cpu().numpy(), val.cpu().numpy().view(np.uint32))
+            if first is None:
+                first = got
+                want = np.flatnonzero(np.abs(g_host[shift:shift + n]) >= np.float32(2e-3)) + 1
+                assert np.array_equal(got[0], want.astype(np.int32))
+            assert np.array_equal(got[0], first[0]) and np.array_equal(got[1], first[1])
+
+
 @pytest.mark.parametrize("n", SIZES)
 @pytest.mark.parametrize("mode", ["magnitude", "compat"])
 def test_topk_index_set_values_residual(sw, n, mode):
