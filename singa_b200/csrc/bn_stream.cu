@@ -90,8 +90,8 @@ struct StreamArgs {
   unsigned tag;
 };
 
-// Deadlines are counted in SM clock cycles (clock64 is a cheap register read;
-// the global nanosecond timer costs microseconds per read).
+// Deadlines are counted in SM clock cycles (a plain register read, local to
+// the SM the CTA runs on).
 __device__ __forceinline__ unsigned long long now_ticks() { return static_cast<unsigned long long>(clock64()); }
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
   unsigned v;
