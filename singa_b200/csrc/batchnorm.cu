@@ -40,6 +40,7 @@
 #include <atomic>
 
 #include "bn_stream.cuh"
+#include "bulk_copy.cuh"
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -295,6 +296,10 @@ constexpr int kCopyGroups = 4;
 // CTA size of the single-pass kernel: 512 threads for large shares (fewer
 // serial iterations per thread), 256 for small ones.
 
+// Sticky fault word of the cluster kernel's exchange: bit 0 = the wait for the
+// peers' pairs ran out of iterations (that launch's outputs are void).
+__device__ unsigned g_cluster_faults;
+
 // grid.x = C * CS with cluster dimension CS: the CS CTAs of a cluster share
 // channel blockIdx.x / CS.  A "unit" is one float4 (VEC) or one float.
 // Dynamic shared memory: 2 * per_cta units (x share, then dy share).
@@ -311,12 +316,17 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                       float* __restrict__ dbias, BnShape sh, int per_cta,
                       const float* __restrict__ dy_b = nullptr, float* __restrict__ joined = nullptr) {
   extern __shared__ __align__(16) float stage[];
+  __shared__ unsigned long long pairs_in;          // mbarrier: counts the peers' pairs as they land
   __shared__ float red[2 * T / 32];
   __shared__ float2 parts[16];   // (sum dy, sum dy*(x-mean)) of every CTA of the cluster
   cg::cluster_group cluster = cg::this_cluster();
   const int cs = static_cast<int>(cluster.num_blocks());
   const int rank = static_cast<int>(cluster.block_rank());
   const int c = blockIdx.x / cs;
+  if (threadIdx.x == 0) {
+    mbar_init(&pairs_in, 1);
+    fence_mbarrier_init();                            // visible to the peers once the cluster barrier completes
+  }
   cluster.barrier_arrive();                           // matched by barrier_wait before the exchange
   constexpr int kW = VEC ? 4 : 1;                     // floats per unit
   const int hwu = sh.HW / kW;                         // units per plane
@@ -495,8 +505,8 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
   }
   // one block reduction for both sums (fixed order), then every CTA pushes its
   // pair into the slot `parts[rank]` of all peers through distributed shared
-  // memory; after one cluster barrier each CTA owns a full copy, so nobody
-  // reads a peer's memory afterwards and CTAs can retire independently.
+  // memory; each CTA then owns a full copy, so nobody reads a peer's memory
+  // afterwards.
   {
     constexpr int kWarps = T / 32;
     static_assert(kWarps <= 32, "one warp finishes the reduction");
@@ -514,12 +524,30 @@ bn_bwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ dy,
       p0 = warp_sum(p0);
       p1 = warp_sum(p1);
       cluster.barrier_wait();                       // peers have started: their memory is addressable
-      if (lane < cs) *cluster.map_shared_rank(&parts[rank], lane) = make_float2(p0, p1);
+      // every pair travels as one asynchronous 8-byte store that also signals the receiver's
+      // mbarrier: no second cluster barrier, a CTA goes on as soon as its cs pairs are in
+      if (lane == 0) mbar_arrive_expect(&pairs_in, 8u * static_cast<unsigned>(cs));
+      if (lane < cs) {
+        unsigned remote_slot, remote_bar;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_slot) : "r"(smem_addr(&parts[rank])), "r"(lane));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_addr(&pairs_in)), "r"(lane));
+        const unsigned long long bits = (static_cast<unsigned long long>(__float_as_uint(p1)) << 32) |
+                                        static_cast<unsigned long long>(__float_as_uint(p0));
+        asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b64 [%0], %1, [%2];" ::"r"(remote_slot),
+                     "l"(bits), "r"(remote_bar)
+                     : "memory");
+      }
     } else {
       cluster.barrier_wait();
     }
   }
-  cluster.sync();
+  // No CTA writes to a peer after this point and none exits before all pairs
+  // addressed to it have landed, so the CTAs retire independently.
+  {
+    bool in = false;
+    for (unsigned it = 0; it < (1u << 24) && !in; ++it) in = mbar_try_wait(&pairs_in, 0);
+    if (!in) atomicOr(&g_cluster_faults, 1u);
+  }
 
   float a = 0.f, b = 0.f;
   for (int r = 0; r < cs; ++r) {                    // rank order: same totals in every CTA
@@ -1200,7 +1228,16 @@ size_t sgb_bn_backward_workspace_bytes(int N, int C, int HW) {
   return static_cast<size_t>(kMaxSlices) * C * sizeof(float2);
 }
 
-int sgb_bn_backward_faults(unsigned* flags) { return bn_stream_faults(flags); }
+int sgb_bn_backward_faults(unsigned* flags) {
+  if (!flags) return SGB_ERR_NULL;
+  unsigned streaming = 0, cluster = 0;
+  const int st = bn_stream_faults(&streaming);
+  if (st != SGB_OK) return st;
+  cudaError_t e = cudaMemcpyFromSymbol(&cluster, g_cluster_faults, sizeof(unsigned));
+  if (e != cudaSuccess) return note_cuda_error(e);
+  *flags = streaming | (cluster << 8);
+  return SGB_OK;
+}
 
 int sgb_bn_backward_stream_plan(int N, int C, int HW, int mask, int* plan6) {
   if (!plan6) return SGB_ERR_NULL;
