@@ -734,7 +734,7 @@ int launch_group(const float* x, const float* dy, const float* relu_in, const fl
 // returns 0 when a channel does not fit 8 CTAs' shared memory.
 int cluster_plan(long long units_per_channel, int unit_bytes, int* per_cta, int channels) {
   constexpr int share_kb = 50;   // preferred staging per CTA
-  constexpr int max_cs = 8;      // portable cluster size
+  constexpr int max_cs = 8;      // portable cluster size (16-CTA clusters with 50 KB shares measured slower)
   constexpr int fill = 0;        // >0 would split small channels further (measured slower on B200)
   const long long kPreferred = share_kb * 1024LL, kLimit = 100 * 1024;
 
