@@ -680,7 +680,7 @@ def main():
             dist.broadcast_object_list(box, src=0)
         return Communicator(local, world, NcclIdHolder(box[0]), buffSize=buff, max_ctas=args.nccl_max_ctas)
 
-    comm = new_comm(4194304)
+    comm = new_comm(max(4194304, 2 * args.threshold_elems))   # a bucket holds at most threshold + one tensor <= threshold
 
     K, W = max(args.steps, 1), max(args.warmup, 3)
     WARM_REPLAYS = 10            # untimed graph replays (NCCL included) before the timed region, whatever W is
