@@ -638,7 +638,10 @@ def main():
                     help="skip the fp16-sync and sparse-exchange legs that ride in the same JSON line")
     ap.add_argument("--no-reference-cuda", action="store_true",
                     help="skip the leg that runs the reference's own CUDA / NCCL build of the same step")
-    ap.add_argument("--nccl-max-ctas", type=int, default=0, help="cap on the CTAs NCCL's kernels use (0 = default)")
+    ap.add_argument("--nccl-max-ctas", type=int, default=16,
+                    help="cap on the CTAs NCCL's kernels use at more than one GPU (ncclCommInitRankConfig maxCTAs; "
+                         "0 = NCCL's default).  16 measured -1.7 %% step time at 2 GPUs, neutral at 4, -2.0 %% at 8: "
+                         "fewer CTAs taken from the HBM-bound backward kernels while the collectives still hide")
     ap.add_argument("--no-register", action="store_true", help="do not register the gradient arena with NCCL")
     ap.add_argument("--threshold-elems", type=int, default=2097152,
                     help="DistOpt's threshold (python/singa/opt.py: backward_and_update): tensors above it are "
@@ -674,11 +677,12 @@ def main():
     if multi:
         dist.init_process_group("gloo", rank=rank, world_size=world)
 
-    def new_comm(buff):
+    def new_comm(buff, cap=True):
         box = [NcclIdHolder().id if rank == 0 else None]
         if multi:
             dist.broadcast_object_list(box, src=0)
-        return Communicator(local, world, NcclIdHolder(box[0]), buffSize=buff, max_ctas=args.nccl_max_ctas)
+        return Communicator(local, world, NcclIdHolder(box[0]), buffSize=buff,
+                            max_ctas=args.nccl_max_ctas if (multi and cap) else 0)
 
     comm = new_comm(max(4194304, 2 * args.threshold_elems))   # a bucket holds at most threshold + one tensor <= threshold
 
@@ -896,7 +900,7 @@ def main():
         gc.collect()
         torch.cuda.empty_cache()
         comm.close()
-        comm = new_comm(args.elements)
+        comm = new_comm(args.elements, cap=False)     # bandwidth-bound payloads: NCCL's own CTA count
         legs = {}
         for wl in ("sparse_topk", "sparse_threshold", "sparse_threshold_bounded"):
             r = sparse_leg(torch, dist, comm, rank, world, wl, args.elements, 20, 3)
@@ -925,7 +929,7 @@ def main():
                        "algorithmic_GB_per_step": round(total_alg / 1e9, 3),
                        "hot_path_GBps": round(total_alg / ms / 1e6, 1),
                        "warm_graph_replays": WARM_REPLAYS if use_graph else 0,
-                       "nccl_max_ctas": args.nccl_max_ctas, "arena_registered": bool(multi and not args.no_register)})
+                       "nccl_max_ctas": args.nccl_max_ctas if multi else 0, "arena_registered": bool(multi and not args.no_register)})
         line = {
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms, "step_ms": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
